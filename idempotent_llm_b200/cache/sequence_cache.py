@@ -1,0 +1,230 @@
+"""The cache: a slot for each live sequence; keys and values for each cache entry
+in pages of ``PAGE_TOKENS`` tokens; per-sequence state of fixed size beside them.
+
+Layout.  Cache entries (one per schedule entry that writes keys) with the same
+need -- same kind, heads, head size and window -- form a *group* with storage
+of its own: ``k, v : [entries, pages, kv_heads, PAGE_TOKENS, head_dim]``.
+A sequence's keys are found through the group's block table
+``table[slot, i] -> page``.
+
+* ``full`` groups draw pages from a pool sized by ``max_tokens`` (each live
+  sequence's length rounded up to a page), as they are needed.
+* ``window`` groups keep the last ``ring`` tokens of every sequence (``ring`` =
+  the window rounded up to whole pages); key ``j`` lives at ring position
+  ``j % ring``.  Their pages are fixed per slot, so their table never changes.
+
+A key is written once and only read afterwards (the reference's rule,
+src/detllm/model.py:15-17), reads are bounded by the sequence's length, so a
+slot that is given back needs no clearing: only its length and its state are
+reset.  The reference instead keeps one dense buffer per layer with one length
+for the whole batch and a validity mask (src/detllm/model.py:67-102).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .slots import CacheError, FreeList
+from .spec import PAGE_TOKENS, CacheNeed
+
+
+def _ceil_div(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+@dataclass
+class KVView:
+    """What a kernel needs to address one cache entry's keys and values."""
+
+    k: torch.Tensor            # [pages, kv_heads, PAGE_TOKENS, head_dim] of this entry
+    v: torch.Tensor
+    table: torch.Tensor        # int32 [max_seqs, pages_per_seq], on the device
+    ring: int                  # 0: position j is stored at j; else at j % ring
+    n_kv_heads: int
+    head_dim: int
+    window: Optional[int]
+
+
+class KVGroup:
+    def __init__(self, need: CacheNeed, entries: Sequence[int], max_tokens: int, max_seqs: int,
+                 max_seq_len: int, dtype: torch.dtype, device):
+        self.need = need
+        self.entries = list(entries)
+        self.index = {c: i for i, c in enumerate(self.entries)}
+        self.kind = need.kind
+        if need.kind == "window":
+            self.ring = _ceil_div(need.window, PAGE_TOKENS) * PAGE_TOKENS
+            self.pages_per_seq = self.ring // PAGE_TOKENS
+            self.n_pages = self.pages_per_seq * max_seqs
+            self.pool = None
+        elif need.kind == "full":
+            self.ring = 0
+            self.pages_per_seq = _ceil_div(max_seq_len, PAGE_TOKENS)
+            self.n_pages = _ceil_div(max_tokens, PAGE_TOKENS)
+            self.pool = FreeList(self.n_pages, "cache page")
+        else:
+            raise CacheError(f"unknown cache kind {need.kind!r}")
+        shape = (len(self.entries), self.n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim)
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        pin = torch.device(device).type == "cuda"
+        self.table_host = torch.zeros((max_seqs, self.pages_per_seq), dtype=torch.int32,
+                                      pin_memory=pin)
+        if self.kind == "window":
+            base = torch.arange(max_seqs, dtype=torch.int32)[:, None] * self.pages_per_seq
+            self.table_host.copy_(base + torch.arange(self.pages_per_seq, dtype=torch.int32)[None, :])
+        self.table = self.table_host.to(device)
+        self.pages_of: Dict[int, List[int]] = {}
+        self._dirty: List[Tuple[int, int, int]] = []
+
+    # pages ------------------------------------------------------------------
+    def pages_needed(self, slot: int, new_len: int) -> int:
+        if self.kind != "full":
+            return 0
+        return max(0, _ceil_div(new_len, PAGE_TOKENS) - len(self.pages_of.get(slot, ())))
+
+    def grow(self, slot: int, new_len: int) -> int:
+        """Give ``slot`` the pages that ``new_len`` tokens need; returns how many were added."""
+        n = self.pages_needed(slot, new_len)
+        if n == 0:
+            return 0
+        mine = self.pages_of.setdefault(slot, [])
+        first = len(mine)
+        for _ in range(n):
+            p = self.pool.take()
+            self.table_host[slot, len(mine)] = p
+            mine.append(p)
+        self._dirty.append((slot, first, n))
+        return n
+
+    def shrink(self, slot: int, n: int) -> None:
+        """Undo the last ``n`` pages given to ``slot`` (after a failed reservation)."""
+        mine = self.pages_of.get(slot, [])
+        for _ in range(n):
+            self.pool.give_back(mine.pop())
+
+    def release(self, slot: int) -> None:
+        if self.kind == "full":
+            for p in self.pages_of.pop(slot, []):
+                self.pool.give_back(p)
+
+    def flush(self) -> None:
+        for slot, first, n in self._dirty:
+            self.table[slot, first:first + n].copy_(self.table_host[slot, first:first + n],
+                                                    non_blocking=True)
+        self._dirty.clear()
+
+    def view(self, cache_id: int) -> KVView:
+        i = self.index[cache_id]
+        return KVView(k=self.k[i], v=self.v[i], table=self.table, ring=self.ring,
+                      n_kv_heads=self.need.n_kv_heads, head_dim=self.need.head_dim,
+                      window=self.need.window)
+
+
+class SequenceCache:
+    """Slots, pages and per-sequence state for one model on one device.
+
+    ``needs`` maps a cache id (``RunEntry.cache``) to the ``CacheNeed`` its mixer
+    declares.  ``max_tokens`` is the most tokens live sequences hold at any
+    time, each length rounded up to ``PAGE_TOKENS``.
+    """
+
+    def __init__(self, needs: Dict[int, CacheNeed], max_tokens: int, dtype: torch.dtype, device,
+                 max_seqs: Optional[int] = None, max_seq_len: Optional[int] = None):
+        if max_tokens <= 0:
+            raise CacheError("max_tokens must be positive")
+        self.page_tokens = PAGE_TOKENS
+        n_pages = _ceil_div(max_tokens, PAGE_TOKENS)
+        self.max_tokens = n_pages * PAGE_TOKENS
+        self.max_seqs = max_seqs if max_seqs is not None else min(n_pages, 256)
+        self.max_seq_len = max_seq_len if max_seq_len is not None else self.max_tokens
+        self.max_seq_len = min(self.max_seq_len, self.max_tokens)
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.slots = FreeList(self.max_seqs, "sequence slot")
+        self._length = [0] * self.max_seqs
+        by_key: Dict[tuple, List[int]] = {}
+        key_need: Dict[tuple, CacheNeed] = {}
+        for cid in sorted(needs):
+            need = needs[cid]
+            if need.kind != "none":
+                by_key.setdefault(need.group_key(), []).append(cid)
+                key_need[need.group_key()] = need
+        self.groups: List[KVGroup] = [
+            KVGroup(key_need[k], ids, self.max_tokens, self.max_seqs, self.max_seq_len, dtype, device)
+            for k, ids in by_key.items()]
+        self._group_of = {cid: g for g in self.groups for cid in g.entries}
+        self.state: Dict[int, torch.Tensor] = {}
+        for cid, need in needs.items():
+            if need.state_shape is not None:
+                self.state[cid] = torch.zeros((self.max_seqs,) + tuple(need.state_shape),
+                                              dtype=need.state_dtype, device=device)
+
+    # slots ------------------------------------------------------------------
+    def alloc_slot(self) -> int:
+        s = self.slots.take()
+        self._length[s] = 0
+        for st in self.state.values():
+            st[s].zero_()
+        return s
+
+    def free_slot(self, slot: int) -> None:
+        self.slots.give_back(slot)      # raises if not held, before anything is released
+        for g in self.groups:
+            g.release(slot)
+        self._length[slot] = 0
+
+    def length(self, slot: int) -> int:
+        if not self.slots.is_held(slot):
+            raise CacheError(f"sequence slot {slot} is not held")
+        return self._length[slot]
+
+    def live_slots(self) -> List[int]:
+        return self.slots.held()
+
+    # growth -----------------------------------------------------------------
+    def reserve(self, wanted: Sequence[Tuple[int, int]]) -> None:
+        """Make room so that each ``(slot, new_length)`` can be written.  All or nothing."""
+        for slot, new_len in wanted:
+            if not self.slots.is_held(slot):
+                raise CacheError(f"sequence slot {slot} is not held")
+            if new_len > self.max_seq_len:
+                raise CacheError(f"a sequence of {new_len} tokens exceeds the cache's limit of "
+                                 f"{self.max_seq_len} tokens per sequence")
+        for g in self.groups:
+            if g.kind == "full":
+                need = sum(g.pages_needed(s, n) for s, n in wanted)
+                if need > g.pool.n_free:
+                    raise CacheError(
+                        f"the cache is full: {need} more pages of {PAGE_TOKENS} tokens are needed, "
+                        f"{g.pool.n_free} of {g.n_pages} are free (max_tokens={self.max_tokens})")
+        for g in self.groups:
+            for s, n in wanted:
+                g.grow(s, n)
+
+    def set_length(self, slot: int, new_len: int) -> None:
+        self._length[slot] = new_len
+
+    def flush(self) -> None:
+        """Bring the device's block tables up to date (before kernels read them)."""
+        for g in self.groups:
+            g.flush()
+
+    # views ------------------------------------------------------------------
+    def view(self, cache_id: int) -> Optional[KVView]:
+        g = self._group_of.get(cache_id)
+        return None if g is None else g.view(cache_id)
+
+    def state_of(self, cache_id: int) -> Optional[torch.Tensor]:
+        return self.state.get(cache_id)
+
+    # accounting (tests) -----------------------------------------------------
+    def pages_held(self) -> int:
+        return sum(g.pool.n_held for g in self.groups if g.pool is not None)
+
+    def bytes(self) -> int:
+        n = sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups)
+        return n + sum(s.numel() * s.element_size() for s in self.state.values())

@@ -1,0 +1,251 @@
+// Attention for steps of one token per sequence, bound by reading the cache.
+//
+// Grid (chunk, kv-head, sequence).  A chunk is 256 keys at absolute positions
+// [256 c, 256 c + 256): four pages, one per warp.  A block serves all q-heads of its
+// kv-head (GT at a time), so keys and values are read from memory once per group.
+// Each row of head_dim elements is split over LPR lanes in 16-byte pieces; a warp-wide
+// load covers 32 / LPR keys.  Scores, the running maximum, the exponentials and the
+// context are 32-bit.  Every chunk writes an unnormalised partial (max, sum, context)
+// to scratch; a second kernel merges a sequence's chunks in ascending order.  Which
+// keys form a chunk and in which order everything is added depend on the sequence's
+// length only: a sequence's result is the same alone or in any batch.
+//
+// Masked keys (beyond the length, or before the window) give p = 0 exactly and are left
+// out of the maximum (src/detllm/ops/di_softmax.py:45-58 does this with an integer
+// sentinel; ops/fused_attn.py:47-115 is the reference's own decode kernel: one program
+// per (batch, q-head), three passes over a capacity-wide cache).
+#include "common.cuh"
+
+#define AD_CHUNK 256
+#define AD_WARPS 4
+#define AD_ITERS 8            // warp-wide loads in flight per group
+
+struct DecodeArgs {
+    const T* q; T* out;
+    KVAddr cache;
+    const int* slots; const int* kv_len;
+    float* part_o;            // [n_seqs, n_q, n_chunks, hd]
+    float* part_ml;           // [n_seqs, n_q, n_chunks, 2]
+    int n_seqs, n_q, n_kv, n_chunks;
+    float scale_log2; int window;
+};
+
+template <int HD, int GT>
+__global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeArgs a) {
+    constexpr int VEC = Vec16<T>::N;
+    constexpr int LPR = HD / VEC;            // lanes per row
+    constexpr int RPI = 32 / LPR;            // rows (keys) per warp-wide load
+    constexpr int GROUP = AD_ITERS * RPI;    // keys per group
+    static_assert(LPR >= 1 && LPR <= 32 && (LPR & (LPR - 1)) == 0, "head_dim / 16 bytes must be a power of two <= 32");
+    static_assert(IDM_PAGE % GROUP == 0 || GROUP > IDM_PAGE, "page is a whole number of groups");
+    __shared__ float sm_m[AD_WARPS][GT], sm_l[AD_WARPS][GT];
+    __shared__ float sm_o[AD_WARPS][GT][HD];
+
+    const int chunk = blockIdx.x, g = blockIdx.y, s = blockIdx.z;
+    const int len = a.kv_len[s];
+    const int lo = a.window > 0 ? max(0, len - a.window) : 0;
+    if (chunk * AD_CHUNK >= len || (chunk + 1) * AD_CHUNK <= lo) return;      // nothing to see here
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / LPR, li = lane % LPR;
+    const int group_heads = a.n_q / a.n_kv;
+    const int kb = chunk * AD_CHUNK + wib * IDM_PAGE;                        // this warp's page of keys
+    const bool warp_live = kb < len && kb + IDM_PAGE > lo;
+    const T* kpage = nullptr; const T* vpage = nullptr;
+    if (warp_live) {
+        const size_t off = kv_offset(a.cache, a.slots[s], kb, g);
+        kpage = a.cache.k + off; vpage = a.cache.v + off;
+    }
+    for (int h0 = 0; h0 < group_heads; h0 += GT) {
+        float q[GT][VEC], acc[GT][VEC], m[GT], l[GT];
+#pragma unroll
+        for (int h = 0; h < GT; ++h) {
+            Vec16<T> qv; qv.load(a.q + ((size_t)s * a.n_q + g * group_heads + h0 + h) * HD + li * VEC);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) { q[h][e] = qv.get(e) * a.scale_log2; acc[h][e] = 0.f; }
+            m[h] = -INFINITY; l[h] = 0.f;
+        }
+        if (warp_live) {
+            constexpr int KEYS = IDM_PAGE;
+            for (int k0 = 0; k0 < KEYS; k0 += GROUP) {
+                if (kb + k0 >= len || kb + k0 + GROUP <= lo) continue;       // warp-uniform
+                Vec16<T> kv[AD_ITERS];
+#pragma unroll
+                for (int it = 0; it < AD_ITERS; ++it) {
+                    const int r = k0 + it * RPI + sub;
+                    if (r < KEYS) kv[it].load(kpage + (size_t)r * HD + li * VEC);
+                }
+                float sc[AD_ITERS][GT];
+#pragma unroll
+                for (int it = 0; it < AD_ITERS; ++it) {
+                    const int r = k0 + it * RPI + sub;
+                    const int j = kb + r;
+                    const bool ok = r < KEYS && j < len && j >= lo;
+#pragma unroll
+                    for (int h = 0; h < GT; ++h) {
+                        float d = 0.f;
+                        if (r < KEYS) {
+#pragma unroll
+                            for (int e = 0; e < VEC; ++e) d = fmaf(q[h][e], kv[it].get(e), d);
+                        }
+#pragma unroll
+                        for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                        sc[it][h] = ok ? d : -INFINITY;
+                    }
+                }
+                // values of the same keys
+#pragma unroll
+                for (int it = 0; it < AD_ITERS; ++it) {
+                    const int r = k0 + it * RPI + sub;
+                    if (r < KEYS) kv[it].load(vpage + (size_t)r * HD + li * VEC);
+                }
+#pragma unroll
+                for (int h = 0; h < GT; ++h) {
+                    float gm = sc[0][h];
+#pragma unroll
+                    for (int it = 1; it < AD_ITERS; ++it) gm = fmaxf(gm, sc[it][h]);
+#pragma unroll
+                    for (int o = LPR; o < 32; o <<= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, o));
+                    const float m_new = fmaxf(m[h], gm);            // finite: the group holds a live key
+                    const float alpha = exp2f(m[h] - m_new);
+                    m[h] = m_new;
+                    float ps = 0.f;
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) acc[h][e] *= alpha;
+#pragma unroll
+                    for (int it = 0; it < AD_ITERS; ++it) {
+                        const float p = sc[it][h] == -INFINITY ? 0.f : exp2f(sc[it][h] - m_new);
+                        ps += p;
+                        if (p != 0.f) {
+#pragma unroll
+                            for (int e = 0; e < VEC; ++e) acc[h][e] = fmaf(p, kv[it].get(e), acc[h][e]);
+                        }
+                    }
+                    l[h] = l[h] * alpha + ps;
+                }
+            }
+        }
+        // lanes of different `sub` hold different keys of the same dims: add them up
+#pragma unroll
+        for (int h = 0; h < GT; ++h) {
+#pragma unroll
+            for (int o = LPR; o < 32; o <<= 1) {
+                l[h] += __shfl_xor_sync(0xffffffffu, l[h], o);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], o);
+            }
+        }
+        __syncthreads();                                  // previous pass's readers are done
+        if (lane < LPR) {
+#pragma unroll
+            for (int h = 0; h < GT; ++h) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) sm_o[wib][h][li * VEC + e] = acc[h][e];
+                if (lane == 0) { sm_m[wib][h] = m[h]; sm_l[wib][h] = l[h]; }
+            }
+        }
+        __syncthreads();
+        // merge the four warps in ascending order and write the chunk's partial
+        for (int idx = threadIdx.x; idx < GT * HD; idx += AD_WARPS * 32) {
+            const int h = idx / HD, d = idx % HD;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, sm_m[w][h]);
+            float o = 0.f, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < AD_WARPS; ++w) {
+                const float f = sm_m[w][h] == -INFINITY ? 0.f : exp2f(sm_m[w][h] - M);
+                o += f * sm_o[w][h][d];
+                L += f * sm_l[w][h];
+            }
+            const size_t row = ((size_t)s * a.n_q + g * group_heads + h0 + h) * a.n_chunks + chunk;
+            a.part_o[row * HD + d] = o;
+            if (d == 0) { a.part_ml[row * 2] = M; a.part_ml[row * 2 + 1] = L; }
+        }
+    }
+}
+
+// out[s, head, :] = sum_c 2^(m_c - M) o_c / sum_c 2^(m_c - M) l_c over the sequence's chunks, ascending.
+__global__ void attention_decode_merge_kernel(DecodeArgs a, int hd) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= a.n_seqs * a.n_q) return;
+    const int s = warp / a.n_q;
+    const int len = a.kv_len[s];
+    const int lo = a.window > 0 ? max(0, len - a.window) : 0;
+    const int c0 = lo / AD_CHUNK, c1 = (len - 1) / AD_CHUNK;
+    const size_t row0 = (size_t)warp * a.n_chunks;
+    float M = -INFINITY;
+    for (int c = c0; c <= c1; ++c) M = fmaxf(M, a.part_ml[(row0 + c) * 2]);
+    float L = 0.f;
+    float acc[IDM_MAX_HEAD_DIM / 32];
+#pragma unroll
+    for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) acc[i] = 0.f;
+    for (int c = c0; c <= c1; ++c) {
+        const float mc = a.part_ml[(row0 + c) * 2];
+        const float f = mc == -INFINITY ? 0.f : exp2f(mc - M);
+        L += f * a.part_ml[(row0 + c) * 2 + 1];
+#pragma unroll
+        for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < hd) acc[i] += f * a.part_o[(row0 + c) * hd + d];
+        }
+    }
+    const float inv = 1.0f / L;
+    T* orow = a.out + (size_t)warp * hd;
+#pragma unroll
+    for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < hd) from_f32(orow[d], acc[i] * inv);
+    }
+}
+
+template <int HD>
+static int launch_decode(const DecodeArgs& a, int group_heads, cudaStream_t stream) {
+    dim3 grid(a.n_chunks, a.n_kv, a.n_seqs);
+    if (group_heads % 4 == 0) attention_decode_kernel<HD, 4><<<grid, AD_WARPS * 32, 0, stream>>>(a);
+    else if (group_heads % 2 == 0) attention_decode_kernel<HD, 2><<<grid, AD_WARPS * 32, 0, stream>>>(a);
+    else attention_decode_kernel<HD, 1><<<grid, AD_WARPS * 32, 0, stream>>>(a);
+    return 0;
+}
+
+// 1 if this library has the kernel for the head size, else 0 (the caller then uses the general kernel)
+extern "C" int idm_attention_decode_supports(int hd) {
+    constexpr int VEC = Vec16<T>::N;
+    return hd == VEC * 2 || hd == VEC * 4 || hd == VEC * 8 || hd == VEC * 16 || (hd == VEC * 32 && hd <= 256);
+}
+
+// floats of scratch for the partials: part_o then part_ml
+extern "C" long long idm_attention_decode_scratch_floats(int n_seqs, int n_q, int n_chunks, int hd) {
+    return (long long)n_seqs * n_q * n_chunks * (hd + 2);
+}
+
+extern "C" int idm_attention_decode(const void* q, void* out, void* k_pool, void* v_pool, const int* table,
+                                    int table_stride, int ring, const int* slots, const int* kv_len,
+                                    float* scratch, int n_seqs, int n_q, int n_kv, int hd, int max_kv_len,
+                                    float scale, int window, cudaStream_t stream) {
+    if (n_seqs == 0) return 0;
+    IDM_REQUIRE(idm_attention_decode_supports(hd), "attention_decode: head_dim=%d has no kernel here", hd);
+    IDM_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention_decode: %d q-heads are no multiple of %d kv-heads", n_q, n_kv);
+    IDM_REQUIRE(max_kv_len > 0 && n_seqs <= 65535 && n_kv <= 65535, "attention_decode: bad sizes");
+    DecodeArgs a;
+    a.q = (const T*)q; a.out = (T*)out;
+    a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
+    a.slots = slots; a.kv_len = kv_len;
+    a.n_seqs = n_seqs; a.n_q = n_q; a.n_kv = n_kv;
+    a.n_chunks = (max_kv_len + AD_CHUNK - 1) / AD_CHUNK;
+    a.part_o = scratch;
+    a.part_ml = scratch + (size_t)n_seqs * n_q * a.n_chunks * hd;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.window = window;
+    const int gh = n_q / n_kv;
+    constexpr int VEC = Vec16<T>::N;
+    if (hd == VEC * 2) launch_decode<VEC * 2>(a, gh, stream);
+    else if (hd == VEC * 4) launch_decode<VEC * 4>(a, gh, stream);
+    else if (hd == VEC * 8) launch_decode<VEC * 8>(a, gh, stream);
+    else if (hd == VEC * 16) launch_decode<VEC * 16>(a, gh, stream);
+    else launch_decode<(VEC * 32 <= 256 ? VEC * 32 : 256)>(a, gh, stream);
+    IDM_LAUNCH_CHECK("attention_decode");
+    const int warps = n_seqs * n_q;
+    attention_decode_merge_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(a, hd);
+    IDM_LAUNCH_CHECK("attention_decode_merge");
+    return 0;
+}

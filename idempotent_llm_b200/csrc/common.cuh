@@ -1,0 +1,105 @@
+// Shared helpers of the hand-written sm_100a kernels.
+//
+// Each shared library is compiled for ONE storage type T (activations, weights
+// and cache): -DIDM_BF16 gives __nv_bfloat16, -DIDM_F32 gives float.  All
+// arithmetic (norm statistics, rotation, scores, softmax, residual sums) is in
+// 32-bit whatever T is.  Entry points are plain C functions taking device
+// pointers and a stream; they return 0 or record a message (idm_last_error)
+// and return non-zero.  Nothing here allocates device memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#if defined(IDM_BF16)
+typedef __nv_bfloat16 T;
+#define IDM_DTYPE_NAME "bfloat16"
+#elif defined(IDM_F32)
+typedef float T;
+#define IDM_DTYPE_NAME "float32"
+#else
+#error "compile with -DIDM_BF16 or -DIDM_F32"
+#endif
+
+#define IDM_PAGE 64          // tokens per cache page (must match cache/spec.py)
+#define IDM_MAX_HEAD_DIM 256
+
+// ---------------------------------------------------------------- errors
+int idm_fail(const char* fmt, ...);   // records the message, returns 1
+
+#define IDM_REQUIRE(cond, ...) \
+    do { if (!(cond)) return idm_fail(__VA_ARGS__); } while (0)
+
+#define IDM_LAUNCH_CHECK(name) \
+    do { cudaError_t e_ = cudaGetLastError(); \
+         if (e_ != cudaSuccess) return idm_fail("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
+    } while (0)
+
+// ----------------------------------------------------------- conversions
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ void from_f32(float& dst, float v) { dst = v; }
+__device__ __forceinline__ void from_f32(__nv_bfloat16& dst, float v) { dst = __float2bfloat16_rn(v); }
+
+// 16-byte vector of T: 8 bfloat16 or 4 float
+template <typename U> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    float4 raw;
+    __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ float get(int i) const { return (&raw.x)[i]; }
+};
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    uint4 raw;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ float get(int i) const {
+        uint32_t w = (&raw.x)[i >> 1];
+        return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
+    }
+};
+
+// ------------------------------------------------------------ reductions
+// Fixed-order reductions: xor butterflies inside a warp, then the warps' values
+// added in ascending order.  The order depends on the block size only.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// all threads of the block get the sum; `scratch` holds >= 32 floats
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[w] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; ++i) t += scratch[i];
+    return t;
+}
+
+// ------------------------------------------------------- cache addressing
+// One cache entry: pools [pages, kv_heads, IDM_PAGE, head_dim]; a sequence's
+// pages through table[slot * table_stride + i]; key j sits at ring position
+// (ring ? j % ring : j).
+struct KVAddr {
+    T* k;
+    T* v;
+    const int* table;
+    int table_stride;
+    int ring;
+    int n_kv;
+    int hd;
+};
+__device__ __forceinline__ size_t kv_offset(const KVAddr& c, int slot, int j, int kv_head) {
+    const int r = c.ring ? (j % c.ring) : j;
+    const int page = c.table[(size_t)slot * c.table_stride + (r / IDM_PAGE)];
+    return (((size_t)page * c.n_kv + kv_head) * IDM_PAGE + (r % IDM_PAGE)) * (size_t)c.hd;
+}

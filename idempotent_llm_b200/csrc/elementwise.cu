@@ -1,0 +1,248 @@
+// Embedding, residual-add + RMS norm, rotary table, q/k norm + rotation + cache
+// write, ring write, SwiGLU.  Memory-bound kernels; everything that follows a
+// matrix product reads its 32-bit partial sums and adds them in ascending order.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+// h[t, :] = table[tokens[t], :]  (a pure lookup, no scaling: src/detllm/model.py:246-249)
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                             float* __restrict__ h, int hidden) {
+    const int t = blockIdx.x;
+    const T* row = table + (size_t)tokens[t] * hidden;
+    float* out = h + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_f32(row[i]);
+}
+
+extern "C" int idm_embed(const int* tokens, const void* table, float* h, int n_tokens, int hidden,
+                         cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(n_tokens > 0 && hidden > 0, "embed: bad sizes n_tokens=%d hidden=%d", n_tokens, hidden);
+    embed_kernel<<<n_tokens, 256, 0, stream>>>(tokens, (const T*)table, h, hidden);
+    IDM_LAUNCH_CHECK("embed");
+    return 0;
+}
+
+// ------------------------------------------------------- residual add + RMSNorm
+// rows == nullptr: for every token row r: h[r] += sum_p delta[p][r] (stored), x[r] = norm(h[r]).
+// rows != nullptr: for i < n_rows: v = h[rows[i]] + sum_p delta[p][rows[i]] (not stored), x[i] = norm(v).
+// norm(v) = v / sqrt(mean(v^2) + eps) * gamma, in 32-bit.  One block per row; the block
+// size is fixed, so the reduction order depends on `hidden` only.
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
+                                   size_t partial_stride, const float* __restrict__ gamma, float eps,
+                                   T* __restrict__ x, const int* __restrict__ rows, int hidden) {
+    __shared__ float scratch[32];
+    extern __shared__ float vals[];            // the row, kept between the two passes
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float* hr = h + (size_t)r * hidden;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = hr[c];
+        for (int p = 0; p < n_partials; ++p) v += delta[p * partial_stride + (size_t)r * hidden + c];
+        if (!rows && n_partials) hr[c] = v;
+        vals[c] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    T* xr = x + (size_t)i * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) from_f32(xr[c], vals[c] * inv * gamma[c]);
+}
+
+extern "C" int idm_add_rmsnorm(float* h, const float* delta, int n_partials, long long partial_stride,
+                               const float* gamma, float eps, void* x, const int* rows, int n_rows,
+                               int hidden, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    IDM_REQUIRE(hidden > 0 && n_rows > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    IDM_REQUIRE((size_t)hidden * 4 <= 160 * 1024, "add_rmsnorm: hidden=%d does not fit shared memory", hidden);
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    add_rmsnorm_kernel<<<n_rows, 256, smem, stream>>>(h, delta, delta ? n_partials : 0,
+                                                      (size_t)partial_stride, gamma, eps, (T*)x, rows, hidden);
+    IDM_LAUNCH_CHECK("add_rmsnorm");
+    return 0;
+}
+
+// ---------------------------------------------------------------- rotary table
+// cs[t, j] = (cos, sin)(positions[t] * inv_freq[j]), angle and functions in 64-bit,
+// rounded to 32-bit (src/detllm/ops/rope.py:25-35 builds its table the same way).
+__global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                  float2* __restrict__ cs, int n_tokens, int half) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * half) return;
+    const int t = i / half, j = i % half;
+    double s, c;
+    sincos((double)positions[t] * inv_freq[j], &s, &c);
+    cs[i] = make_float2((float)c, (float)s);
+}
+
+extern "C" int idm_rope_table(const int* positions, const double* inv_freq, float* cs, int n_tokens,
+                              int half, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(half > 0, "rope_table: bad half=%d", half);
+    const int n = n_tokens * half;
+    rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, inv_freq, (float2*)cs, n_tokens, half);
+    IDM_LAUNCH_CHECK("rope_table");
+    return 0;
+}
+
+// ------------------------------------------- q/k norm + rotation + cache write
+// One warp per (token, head) over the n_q + 2 n_kv heads of the fused projection.
+// q and k heads: RMS norm over head_dim with a weight of shape [head_dim] shared by
+// all heads (src/detllm/model.py:208-215), then rotation of pairs (d, d + hd/2)
+// by the token's position (src/detllm/ops/rope.py:47-55); v heads are copied.
+// q goes to q_out [N, n_q, hd]; k and v go to the cache at the token's position
+// and/or to packed buffers k_new, v_new [N, n_kv, hd].
+struct QkvArgs {
+    const float* qkv; int n_partials; size_t partial_stride;
+    int n_tokens, n_q, n_kv, hd;
+    const float* gq; const float* gk; float eps;
+    const float2* cs;
+    T* q_out; T* k_new; T* v_new;
+    KVAddr cache; int write_cache;
+    const int* token_seq; const int* positions; const int* slots;
+};
+
+__global__ void qkv_finish_kernel(QkvArgs a) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const int heads = a.n_q + 2 * a.n_kv;
+    if (warp >= a.n_tokens * heads) return;
+    const int t = warp / heads, head = warp % heads;
+    const int half = a.hd >> 1;
+    const size_t row = (size_t)t * heads * a.hd + (size_t)head * a.hd;
+    constexpr int MAXP = IDM_MAX_HEAD_DIM / 64;   // pairs per lane
+    float x1[MAXP], x2[MAXP];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+        const int j = lane + 32 * i;
+        x1[i] = x2[i] = 0.f;
+        if (j < half) {
+            for (int p = 0; p < a.n_partials; ++p) {
+                x1[i] += a.qkv[p * a.partial_stride + row + j];
+                x2[i] += a.qkv[p * a.partial_stride + row + j + half];
+            }
+            ss += x1[i] * x1[i] + x2[i] * x2[i];
+        }
+    }
+    const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
+    T* dst_a = nullptr; T* dst_b = nullptr;
+    if (is_q) {
+        dst_a = a.q_out + ((size_t)t * a.n_q + head) * a.hd;
+    } else {
+        const int g = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
+        if (a.write_cache) {
+            const size_t off = kv_offset(a.cache, a.slots[a.token_seq[t]], a.positions[t], g);
+            dst_a = (is_k ? a.cache.k : a.cache.v) + off;
+        }
+        T* packed = is_k ? a.k_new : a.v_new;
+        if (packed) dst_b = packed + ((size_t)t * a.n_kv + g) * a.hd;
+    }
+    const float* gamma = is_q ? a.gq : (is_k ? a.gk : nullptr);
+    float inv = 1.f;
+    if (gamma) {
+        ss = warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)a.hd + a.eps);
+    }
+    const bool rotate = (is_q || is_k) && a.cs != nullptr;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+        const int j = lane + 32 * i;
+        if (j < half) {
+            float u = x1[i], w = x2[i];
+            if (gamma) { u = u * inv * gamma[j]; w = w * inv * gamma[j + half]; }
+            if (rotate) {
+                const float2 c = a.cs[(size_t)t * half + j];
+                const float ru = u * c.x - w * c.y;
+                const float rw = w * c.x + u * c.y;
+                u = ru; w = rw;
+            }
+            if (dst_a) { from_f32(dst_a[j], u); from_f32(dst_a[j + half], w); }
+            if (dst_b) { from_f32(dst_b[j], u); from_f32(dst_b[j + half], w); }
+        }
+    }
+}
+
+extern "C" int idm_qkv_finish(const float* qkv, int n_partials, long long partial_stride, int n_tokens,
+                              int n_q, int n_kv, int hd, const float* gq, const float* gk, float eps,
+                              const float* cs, void* q_out, void* k_new, void* v_new,
+                              void* k_pool, void* v_pool, const int* table, int table_stride, int ring,
+                              const int* token_seq, const int* positions, const int* slots,
+                              cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(hd > 0 && hd % 2 == 0 && hd <= IDM_MAX_HEAD_DIM,
+                "qkv_finish: head_dim=%d must be even and at most %d", hd, IDM_MAX_HEAD_DIM);
+    IDM_REQUIRE(n_q > 0 && n_kv >= 0 && n_partials >= 1, "qkv_finish: bad head counts %d/%d", n_q, n_kv);
+    QkvArgs a;
+    a.qkv = qkv; a.n_partials = n_partials; a.partial_stride = (size_t)partial_stride;
+    a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd;
+    a.gq = gq; a.gk = gk; a.eps = eps; a.cs = (const float2*)cs;
+    a.q_out = (T*)q_out; a.k_new = (T*)k_new; a.v_new = (T*)v_new;
+    a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
+    a.write_cache = k_pool != nullptr;
+    a.token_seq = token_seq; a.positions = positions; a.slots = slots;
+    const long long warps = (long long)n_tokens * (n_q + 2 * n_kv);
+    qkv_finish_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(a);
+    IDM_LAUNCH_CHECK("qkv_finish");
+    return 0;
+}
+
+// ------------------------------------------------------------------ ring write
+// After a windowed layer's attention: the step's keys and values go into the ring.
+// Only a sequence's last `ring` tokens are written (earlier ones would be overwritten
+// by later ones of the same step; each ring position gets exactly one writer).
+__global__ void kv_write_ring_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new, KVAddr c,
+                                     const int* __restrict__ token_seq, const int* __restrict__ positions,
+                                     const int* __restrict__ slots, const int* __restrict__ kv_len,
+                                     int n_tokens) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_tokens * c.n_kv) return;
+    const int t = warp / c.n_kv, g = warp % c.n_kv;
+    const int s = token_seq[t], pos = positions[t];
+    if (c.ring && pos < kv_len[s] - c.ring) return;
+    const size_t off = kv_offset(c, slots[s], pos, g);
+    const size_t src = ((size_t)t * c.n_kv + g) * c.hd;
+    for (int d = lane; d < c.hd; d += 32) { c.k[off + d] = k_new[src + d]; c.v[off + d] = v_new[src + d]; }
+}
+
+extern "C" int idm_kv_write_ring(const void* k_new, const void* v_new, void* k_pool, void* v_pool,
+                                 const int* table, int table_stride, int ring, const int* token_seq,
+                                 const int* positions, const int* slots, const int* kv_len, int n_tokens,
+                                 int n_kv, int hd, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    KVAddr c{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
+    const long long warps = (long long)n_tokens * n_kv;
+    kv_write_ring_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(
+        (const T*)k_new, (const T*)v_new, c, token_seq, positions, slots, kv_len, n_tokens);
+    IDM_LAUNCH_CHECK("kv_write_ring");
+    return 0;
+}
+
+// ---------------------------------------------------------------------- SwiGLU
+// y[t, i] = g * sigmoid(g) * u with g = gu[t, i], u = gu[t, inter + i]
+// (src/detllm/ops/di_swiglu.py:43-45; float form tests/test_ops.py:240-242).
+__global__ void swiglu_kernel(const float* __restrict__ gu, int n_partials, size_t partial_stride,
+                              T* __restrict__ y, int inter, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / inter, c = i % inter;
+    const size_t base = t * 2 * (size_t)inter + c;
+    float g = 0.f, u = 0.f;
+    for (int p = 0; p < n_partials; ++p) {
+        g += gu[p * partial_stride + base];
+        u += gu[p * partial_stride + base + inter];
+    }
+    from_f32(y[i], g / (1.0f + expf(-g)) * u);
+}
+
+extern "C" int idm_swiglu(const float* gu, int n_partials, long long partial_stride, void* y, int n_tokens,
+                          int inter, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(inter > 0 && n_partials >= 1, "swiglu: bad sizes");
+    const size_t total = (size_t)n_tokens * inter;
+    swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(gu, n_partials, (size_t)partial_stride,
+                                                                      (T*)y, inter, total);
+    IDM_LAUNCH_CHECK("swiglu");
+    return 0;
+}

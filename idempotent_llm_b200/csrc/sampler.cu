@@ -1,0 +1,61 @@
+// Token choice from 32-bit logits: argmax (temperature 0) or Gumbel-max sampling from
+// softmax(logits / T).  Ties go to the lowest token id (src/detllm/model.py:482-490).
+// The uniform numbers are a pure function of (row key, token id), so a row's choice
+// does not depend on the rest of the batch.  (max, lowest id) is associative and
+// commutative, so the thread layout cannot change the result.
+#include "common.cuh"
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+__device__ __forceinline__ void better(float& bs, int& bi, float s, int i) {
+    if (s > bs || (s == bs && i < bi)) { bs = s; bi = i; }
+}
+
+__global__ void sample_kernel(const float* __restrict__ logits, int V, float temperature,
+                              const long long* __restrict__ keys, int* __restrict__ out) {
+    __shared__ float ss[32];
+    __shared__ int si[32];
+    const int row = blockIdx.x;
+    const float* lg = logits + (size_t)row * V;
+    const unsigned long long key = keys ? (unsigned long long)keys[row] : 0ull;
+    const float inv_t = temperature > 0.f ? 1.0f / temperature : 1.0f;
+    float bs = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+        float s = lg[v];
+        if (s != s) s = -INFINITY;                      // a NaN never wins
+        if (temperature > 0.f) {
+            const unsigned long long bits = mix64(key ^ ((unsigned long long)v * 0xD1342543DE82EF95ull));
+            const float u = ((float)(bits >> 40) + 0.5f) * (1.0f / 16777216.0f);
+            s = s * inv_t - logf(-logf(u));
+        }
+        better(bs, bi, s, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        better(bs, bi, os, oi);
+    }
+    if ((threadIdx.x & 31) == 0) { ss[threadIdx.x >> 5] = bs; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) better(bs, bi, ss[w], si[w]);
+        out[row] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+extern "C" int idm_sample(const float* logits, int n_rows, int V, float temperature, const long long* keys,
+                          int* out, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    IDM_REQUIRE(V > 0, "sample: empty vocabulary");
+    IDM_REQUIRE(!(temperature > 0.f) || keys != nullptr, "sample: temperature > 0 needs row keys");
+    sample_kernel<<<n_rows, 1024, 0, stream>>>(logits, V, temperature, keys, out);
+    IDM_LAUNCH_CHECK("sample");
+    return 0;
+}

@@ -1,0 +1,80 @@
+"""What one step runs: the packed tokens of a batch and where they sit.
+
+Tokens of all sequences are packed one after another (no padding);
+``cu_q[i] .. cu_q[i+1]`` are sequence i's tokens.  The reference pads to a
+rectangle and masks (src/detllm/model.py:8-17, 259-266); here padding never
+enters the computation.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List
+
+import torch
+
+
+@dataclass
+class StepContext:
+    n_tokens: int
+    n_seqs: int
+    tokens: torch.Tensor       # int32 [N]  token ids
+    token_seq: torch.Tensor    # int32 [N]  index of the token's sequence within this step
+    positions: torch.Tensor    # int32 [N]  absolute position of the token in its sequence
+    cu_q: torch.Tensor         # int32 [n_seqs + 1]
+    slots: torch.Tensor        # int32 [n_seqs]  cache slot of each sequence
+    q_start: torch.Tensor      # int32 [n_seqs]  sequence length before this step
+    kv_len: torch.Tensor       # int32 [n_seqs]  sequence length after this step
+    max_q_len: int
+    max_kv_len: int            # an upper bound is enough (sizes grids; kernels read kv_len)
+    single_token: bool         # every sequence brings exactly one token
+    host_q_lens: List[int]
+    host_slots: List[int]
+    memo: Dict = field(default_factory=dict)   # per-step shared tables (position encodings)
+
+
+def pack_step_host(slots: List[int], starts: List[int], token_lists: List[List[int]]):
+    """Host-side packing: returns one int32 tensor holding, back to back,
+    tokens[N], token_seq[N], positions[N], cu_q[S+1], slots[S], q_start[S], kv_len[S]."""
+    n_seq = len(slots)
+    q_lens = [len(t) for t in token_lists]
+    n = sum(q_lens)
+    buf = torch.empty(3 * n + 4 * n_seq + 1, dtype=torch.int32)
+    toks = buf[0:n]
+    tseq = buf[n:2 * n]
+    pos = buf[2 * n:3 * n]
+    o = 3 * n
+    cu = buf[o:o + n_seq + 1]
+    sl = buf[o + n_seq + 1:o + 2 * n_seq + 1]
+    qs = buf[o + 2 * n_seq + 1:o + 3 * n_seq + 1]
+    kl = buf[o + 3 * n_seq + 1:o + 4 * n_seq + 1]
+    off = 0
+    cu[0] = 0
+    for i, (t, st) in enumerate(zip(token_lists, starts)):
+        L = len(t)
+        if L:
+            toks[off:off + L] = torch.as_tensor(t, dtype=torch.int32)
+            tseq[off:off + L] = i
+            pos[off:off + L] = torch.arange(st, st + L, dtype=torch.int32)
+        off += L
+        cu[i + 1] = off
+        sl[i] = slots[i]
+        qs[i] = st
+        kl[i] = st + L
+    return buf, n, q_lens
+
+
+def context_from_packed(dev_buf: torch.Tensor, n: int, slots: List[int], q_lens: List[int],
+                        starts: List[int], max_kv_len=None) -> StepContext:
+    n_seq = len(slots)
+    o = 3 * n
+    return StepContext(
+        n_tokens=n, n_seqs=n_seq,
+        tokens=dev_buf[0:n], token_seq=dev_buf[n:2 * n], positions=dev_buf[2 * n:3 * n],
+        cu_q=dev_buf[o:o + n_seq + 1], slots=dev_buf[o + n_seq + 1:o + 2 * n_seq + 1],
+        q_start=dev_buf[o + 2 * n_seq + 1:o + 3 * n_seq + 1],
+        kv_len=dev_buf[o + 3 * n_seq + 1:o + 4 * n_seq + 1],
+        max_q_len=max(q_lens) if q_lens else 0,
+        max_kv_len=max_kv_len if max_kv_len is not None else max(s + q for s, q in zip(starts, q_lens)),
+        single_token=all(q == 1 for q in q_lens),
+        host_q_lens=list(q_lens), host_slots=list(slots))

@@ -1,0 +1,163 @@
+"""The step function and what it stands on: model, cache, decode graphs.
+
+One ``step`` runs only the tokens it is given, as one packed batch, against
+what earlier steps left in the cache, and returns 32-bit logits at the wanted
+places.  A batch's sequences start together with unequal lengths (all prompts
+in one step), then bring one token each; any other mix of lengths runs too.
+The reference's ``forward`` (src/detllm/model.py:220-286) takes a padded
+rectangle plus positions and returns logits at every position; its
+``GraphedDecode.step`` (src/detllm/graphed.py:111-132) replays one captured
+graph per decode step, which ``Engine`` does per batch size.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache import CacheError, SequenceCache
+from .assembly import CausalLM, cache_needs
+from .batch import StepContext, context_from_packed, pack_step_host
+
+
+class _DecodeGraph:
+    """A captured single-token step for a fixed number of sequences."""
+
+    def __init__(self, engine: "Engine", n_seqs: int):
+        self.n = n_seqs
+        dev = engine.device
+        self.size = 7 * n_seqs + 1 + n_seqs
+        self.host = torch.zeros(self.size, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.zeros(self.size, dtype=torch.int32, device=dev)
+        self.graph = None
+        self.logits = None
+        self.uploaded = None            # event: the last host->device copy of `host` is done
+
+    def run(self, engine: "Engine", packed: torch.Tensor, slots, q_lens, starts) -> torch.Tensor:
+        if self.uploaded is not None:
+            self.uploaded.synchronize()
+        self.host.copy_(packed)
+        self.dev.copy_(self.host, non_blocking=True)
+        if self.uploaded is None:
+            self.uploaded = torch.cuda.Event()
+        self.uploaded.record()
+        if self.graph is None:
+            ctx = context_from_packed(self.dev, self.n, slots, q_lens, starts,
+                                      max_kv_len=engine.cache.max_seq_len)
+            rows = self.dev[7 * self.n + 1:]
+            for _ in range(2):                       # warm-up outside capture (lazy library state)
+                ctx.memo.clear()
+                engine.model.forward(ctx, engine.cache, rows)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            ctx.memo.clear()
+            with torch.cuda.graph(g, pool=engine._graph_pool):
+                self.logits = engine.model.forward(ctx, engine.cache, rows)
+            if engine._graph_pool is None:
+                engine._graph_pool = g.pool()
+            self.graph = g
+        self.graph.replay()
+        return self.logits
+
+
+class Engine:
+    def __init__(self, model: CausalLM, max_tokens: int, max_seqs: Optional[int] = None,
+                 max_seq_len: Optional[int] = None, use_graph: bool = True):
+        self.model = model
+        self.rt = model.rt
+        self.device = model.rt.device
+        self.spec = model.spec
+        if max_seq_len is None:
+            max_seq_len = min(max_tokens, model.spec.max_positions)
+        self.cache = SequenceCache(cache_needs(model.spec), max_tokens, model.rt.dtype, self.device,
+                                   max_seqs=max_seqs, max_seq_len=max_seq_len)
+        self.use_graph = use_graph and self.device.type == "cuda"
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._graph_pool = None
+        self._pinned: Dict[int, torch.Tensor] = {}
+        self.steps_run = 0
+
+    # slots ------------------------------------------------------------------
+    def open(self) -> int:
+        """Take a slot for a new sequence."""
+        return self.cache.alloc_slot()
+
+    def close(self, slot: int) -> None:
+        """Give a finished sequence's slot and pages back."""
+        self.cache.free_slot(slot)
+
+    # the step function --------------------------------------------------------
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """Run one step.  ``entries``: (slot, this step's tokens) per sequence.
+        ``want[i]``: places among sequence i's tokens whose logits are returned
+        (default: the last one).  Returns ``[n_wanted, vocab]`` float32 on the
+        device, ordered by entry, then by ``want``."""
+        if not entries:
+            raise ValueError("a step needs at least one sequence")
+        slots = [int(s) for s, _ in entries]
+        toks = [list(t) for _, t in entries]
+        if len(set(slots)) != len(slots):
+            raise ValueError("a slot appears twice in one step")
+        V = self.spec.vocab_size
+        for s, t in zip(slots, toks):
+            if not t:
+                raise ValueError(f"slot {s} brings no token")
+            bad = [x for x in t if not 0 <= x < V]
+            if bad:
+                raise ValueError(f"token id {bad[0]} is outside the vocabulary [0, {V})")
+        if want is None:
+            want = [[len(t) - 1] for t in toks]
+        if len(want) != len(toks):
+            raise ValueError("want must have one list per entry")
+        rows, off = [], 0
+        for t, w in zip(toks, want):
+            for j in w:
+                if not 0 <= j < len(t):
+                    raise ValueError(f"wanted place {j} is outside the entry's {len(t)} tokens")
+                rows.append(off + j)
+            off += len(t)
+        starts = [self.cache.length(s) for s in slots]
+        self.cache.reserve([(s, st + len(t)) for s, st, t in zip(slots, starts, toks)])
+        packed, n, q_lens = pack_step_host(slots, starts, toks)
+        self.cache.flush()
+        single = all(q == 1 for q in q_lens)
+        if single and self.use_graph:
+            g = self._graphs.get(len(slots))
+            if g is None:
+                g = self._graphs[len(slots)] = _DecodeGraph(self, len(slots))
+            full = torch.cat([packed, torch.arange(len(slots), dtype=torch.int32)])
+            logits = g.run(self, full, slots, q_lens, starts)
+            if rows != list(range(len(slots))):
+                logits = logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows \
+                    else logits[:0]
+        else:
+            full = torch.cat([packed, torch.tensor(rows, dtype=torch.int32)])
+            dev = self._upload(full)
+            ctx = context_from_packed(dev, n, slots, q_lens, starts)
+            logits = self.model.forward(ctx, self.cache, dev[packed.numel():])
+        for s, st, t in zip(slots, starts, toks):
+            self.cache.set_length(s, st + len(t))
+        self.steps_run += 1
+        return logits
+
+    def _upload(self, host: torch.Tensor) -> torch.Tensor:
+        if self.device.type != "cuda":
+            return host.to(self.device)
+        n = host.numel()
+        cap = 1 << max(6, (n - 1).bit_length())
+        pin = self._pinned.get(cap)
+        if pin is None:
+            pin = self._pinned[cap] = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+        else:
+            torch.cuda.current_stream().synchronize()   # the previous upload from this buffer is done
+        pin[:n].copy_(host)
+        return pin[:n].to(self.device, non_blocking=True)
+
+    # sampling -----------------------------------------------------------------
+    def sample(self, logits: torch.Tensor, temperature: float, seed: int,
+               request_ids: Sequence[int], steps: Sequence[int]) -> List[int]:
+        """Pick one token per row of ``logits``; see ``sampling.sampler``."""
+        from ..sampling.sampler import sample_tokens
+        return sample_tokens(self.rt.kernels, logits, temperature, seed, request_ids, steps)

@@ -1,0 +1,261 @@
+"""Python side of the CUDA kernels: shape checks, output allocation, the call.
+
+``Kernels(dtype, device)`` loads the library compiled for that storage dtype
+(``float32`` or ``bfloat16``) and exposes one method per kernel.  Every method
+checks what the kernel cannot check itself and raises ``KernelError`` with the
+library's message when a launch is refused.  There is no CPU path: constructing
+``Kernels`` without a CUDA device raises.
+
+Matrix products: the 32-bit library has its own FMA kernel (no tensor cores, no
+reduced-precision mode).  In bfloat16 the product goes to the library GEMM that
+torch wraps (cuBLASLt), as the reference sends every matrix product to
+``torch._int_mm`` (src/detllm/backends.py:88-135); outputs are 32-bit.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+_DT = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+class Kernels:
+    def __init__(self, dtype: torch.dtype, device):
+        device = torch.device(device)
+        if dtype not in _DT:
+            raise KernelError(f"no kernels for dtype {dtype}; float32 and bfloat16 exist")
+        if device.type != "cuda" or not torch.cuda.is_available():
+            raise KernelError("the kernels run on a CUDA device only; there is no CPU path")
+        cap = torch.cuda.get_device_capability(device)
+        if cap[0] != 10:
+            raise KernelError(f"the kernels are compiled for sm_100a; this device is sm_{cap[0]}{cap[1]}")
+        self.dtype = dtype
+        self.device = device
+        self.lib = build.load(_DT[dtype])
+        self.launches = 0                     # kernels of this library launched so far
+        self._scratch = {}
+        self._retired = []
+        L = self.lib
+        for name in ("idm_embed", "idm_add_rmsnorm", "idm_rope_table", "idm_qkv_finish", "idm_kv_write_ring",
+                     "idm_swiglu", "idm_sample", "idm_attention_generic", "idm_attention_decode",
+                     "idm_attention_decode_supports"):
+            getattr(L, name).restype = c_int
+        L.idm_attention_decode_scratch_floats.restype = c_longlong
+        if dtype == torch.float32:
+            L.idm_gemm_f32.restype = c_int
+        self.page = L.idm_page_tokens()
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self):
+        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _check(self, rc: int, n_launches: int = 1):
+        if rc != 0:
+            raise KernelError(self.lib.idm_last_error().decode())
+        self.launches += n_launches
+
+    def _need(self, t: torch.Tensor, dtype, what: str):
+        if t.dtype != dtype or not t.is_cuda or not t.is_contiguous():
+            raise KernelError(f"{what}: expected a contiguous CUDA tensor of {dtype}, got {t.dtype} "
+                              f"{'cuda' if t.is_cuda else 'cpu'} contiguous={t.is_contiguous()}")
+
+    def scratch(self, key: str, n_floats: int) -> torch.Tensor:
+        """A 32-bit scratch buffer that only grows (its address is stable across steps once large enough)."""
+        buf = self._scratch.get(key)
+        if buf is None or buf.numel() < n_floats:
+            # a captured graph may still point at the old buffer: it is kept, never freed
+            self._retired.append(buf)
+            buf = self._scratch[key] = torch.empty(max(n_floats, 1), dtype=torch.float32, device=self.device)
+        return buf
+
+    # ------------------------------------------------------------------ kernels
+    def embed(self, tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        self._need(tokens, torch.int32, "embed tokens")
+        self._need(table, self.dtype, "embed table")
+        n, hidden = tokens.numel(), table.shape[1]
+        h = torch.empty((n, hidden), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_embed(c_void_p(_p(tokens)), c_void_p(_p(table)), c_void_p(_p(h)),
+                                       c_int(n), c_int(hidden), self._stream()))
+        return h
+
+    def add_rmsnorm(self, h, delta, gamma, eps: float, rows=None) -> torch.Tensor:
+        self._need(h, torch.float32, "residual stream")
+        self._need(gamma, torch.float32, "norm weight")
+        n, hidden = h.shape
+        if gamma.numel() != hidden:
+            raise KernelError(f"norm weight has {gamma.numel()} elements, rows have {hidden}")
+        P, stride = 0, 0
+        if delta is not None:
+            self._need(delta, torch.float32, "delta")
+            if delta.dim() != 3 or tuple(delta.shape[1:]) != (n, hidden):
+                raise KernelError(f"delta {tuple(delta.shape)} does not match the stream {(n, hidden)}")
+            P, stride = delta.shape[0], n * hidden
+        if rows is not None:
+            self._need(rows, torch.int32, "rows")
+        n_out = n if rows is None else rows.numel()
+        x = torch.empty((n_out, hidden), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_add_rmsnorm(c_void_p(_p(h)), c_void_p(_p(delta)), c_int(P), c_longlong(stride),
+                                             c_void_p(_p(gamma)), c_float(eps), c_void_p(_p(x)),
+                                             c_void_p(_p(rows)), c_int(n_out), c_int(hidden), self._stream()))
+        return x
+
+    def rope_table(self, positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+        self._need(positions, torch.int32, "positions")
+        self._need(inv_freq, torch.float64, "inv_freq")
+        n, half = positions.numel(), inv_freq.numel()
+        cs = torch.empty((n, half, 2), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_rope_table(c_void_p(_p(positions)), c_void_p(_p(inv_freq)), c_void_p(_p(cs)),
+                                            c_int(n), c_int(half), self._stream()))
+        return cs
+
+    def qkv_finish(self, qkv, n_q, n_kv, hd, q_gamma, k_gamma, eps, cs, ctx, kv, keep_new: bool):
+        """Norm + rotation of q and k heads; k, v to the cache entry ``kv`` (if given) and/or to packed
+        buffers (``keep_new``).  Returns (q [N, n_q, hd], k_new, v_new)."""
+        self._need(qkv, torch.float32, "qkv")
+        P, n, width = qkv.shape
+        if width != (n_q + 2 * n_kv) * hd:
+            raise KernelError(f"qkv rows have {width} elements, expected {(n_q + 2 * n_kv) * hd}")
+        if cs is not None and tuple(cs.shape) != (n, hd // 2, 2):
+            raise KernelError(f"rotary table {tuple(cs.shape)} does not match {(n, hd // 2, 2)}")
+        for gmm in (q_gamma, k_gamma):
+            if gmm is not None and gmm.numel() != hd:
+                raise KernelError("q/k norm weight must have head_dim elements")
+        q = torch.empty((n, n_q, hd), dtype=self.dtype, device=self.device)
+        k_new = v_new = None
+        if keep_new and n_kv:
+            k_new = torch.empty((n, n_kv, hd), dtype=self.dtype, device=self.device)
+            v_new = torch.empty((n, n_kv, hd), dtype=self.dtype, device=self.device)
+        if kv is not None:
+            self._check_kv(kv, n_kv, hd)
+        self._check(self.lib.idm_qkv_finish(
+            c_void_p(_p(qkv)), c_int(P), c_longlong(n * width), c_int(n), c_int(n_q), c_int(n_kv), c_int(hd),
+            c_void_p(_p(q_gamma)), c_void_p(_p(k_gamma)), c_float(eps), c_void_p(_p(cs)),
+            c_void_p(_p(q)), c_void_p(_p(k_new)), c_void_p(_p(v_new)),
+            c_void_p(_p(kv.k) if kv is not None else None), c_void_p(_p(kv.v) if kv is not None else None),
+            c_void_p(_p(kv.table) if kv is not None else None),
+            c_int(kv.table.shape[1] if kv is not None else 0), c_int(kv.ring if kv is not None else 0),
+            c_void_p(_p(ctx.token_seq)), c_void_p(_p(ctx.positions)), c_void_p(_p(ctx.slots)), self._stream()))
+        return q, k_new, v_new
+
+    def _check_kv(self, kv, n_kv, hd):
+        if kv.k.dtype != self.dtype or kv.k.shape[1:] != (n_kv, self.page, hd) or not kv.k.is_contiguous():
+            raise KernelError(f"cache entry {tuple(kv.k.shape)} {kv.k.dtype} does not fit "
+                              f"[pages, {n_kv}, {self.page}, {hd}] {self.dtype}")
+
+    def kv_write_ring(self, k_new, v_new, kv, ctx) -> None:
+        n, n_kv, hd = k_new.shape
+        self._check_kv(kv, n_kv, hd)
+        self._check(self.lib.idm_kv_write_ring(
+            c_void_p(_p(k_new)), c_void_p(_p(v_new)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)),
+            c_void_p(_p(kv.table)), c_int(kv.table.shape[1]), c_int(kv.ring), c_void_p(_p(ctx.token_seq)),
+            c_void_p(_p(ctx.positions)), c_void_p(_p(ctx.slots)), c_void_p(_p(ctx.kv_len)), c_int(n),
+            c_int(n_kv), c_int(hd), self._stream()))
+
+    def attention(self, q, kv, ctx, k_new, v_new, scale: float, window) -> torch.Tensor:
+        """Causal attention of the step's queries over the cache entry; returns [N, n_q * hd]."""
+        self._need(q, self.dtype, "q")
+        n, n_q, hd = q.shape
+        self._check_kv(kv, kv.n_kv_heads, hd)
+        out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
+        w = int(window) if window else 0
+        if ctx.single_token and k_new is None and self.lib.idm_attention_decode_supports(c_int(hd)):
+            return self.attention_decode(q, kv, ctx.slots, ctx.kv_len, ctx.max_kv_len, scale, w, out)
+        self._check(self.lib.idm_attention_generic(
+            c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_void_p(_p(kv.table)),
+            c_int(kv.table.shape[1]), c_int(kv.ring), c_void_p(_p(k_new)), c_void_p(_p(v_new)),
+            c_void_p(_p(ctx.token_seq)), c_void_p(_p(ctx.positions)), c_void_p(_p(ctx.slots)),
+            c_void_p(_p(ctx.q_start)), c_void_p(_p(ctx.cu_q)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads),
+            c_int(hd), c_float(scale), c_int(w), self._stream()))
+        return out
+
+    def attention_generic(self, q, kv, ctx, k_new, v_new, scale: float, window) -> torch.Tensor:
+        """The general kernel, whatever the step's shape (tests compare the special kernels with it)."""
+        n, n_q, hd = q.shape
+        out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_attention_generic(
+            c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_void_p(_p(kv.table)),
+            c_int(kv.table.shape[1]), c_int(kv.ring), c_void_p(_p(k_new)), c_void_p(_p(v_new)),
+            c_void_p(_p(ctx.token_seq)), c_void_p(_p(ctx.positions)), c_void_p(_p(ctx.slots)),
+            c_void_p(_p(ctx.q_start)), c_void_p(_p(ctx.cu_q)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads),
+            c_int(hd), c_float(scale), c_int(int(window) if window else 0), self._stream()))
+        return out
+
+    def attention_decode(self, q, kv, slots, kv_len, max_kv_len: int, scale: float, window: int,
+                         out=None) -> torch.Tensor:
+        """One query per sequence against its cached keys (split over chunks of 256 keys, then merged)."""
+        n, n_q, hd = q.shape
+        if out is None:
+            out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
+        n_chunks = -(-max_kv_len // 256)
+        need = self.lib.idm_attention_decode_scratch_floats(c_int(n), c_int(n_q), c_int(n_chunks), c_int(hd))
+        scratch = self.scratch("attention_decode", need)
+        self._check(self.lib.idm_attention_decode(
+            c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_void_p(_p(kv.table)),
+            c_int(kv.table.shape[1]), c_int(kv.ring), c_void_p(_p(slots)), c_void_p(_p(kv_len)),
+            c_void_p(_p(scratch)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads), c_int(hd), c_int(max_kv_len),
+            c_float(scale), c_int(window), self._stream()), 2)
+        return out
+
+    def swiglu(self, gu: torch.Tensor) -> torch.Tensor:
+        self._need(gu, torch.float32, "gate-up")
+        P, n, two_i = gu.shape
+        if two_i % 2:
+            raise KernelError("gate-up rows must have an even number of elements")
+        y = torch.empty((n, two_i // 2), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_swiglu(c_void_p(_p(gu)), c_int(P), c_longlong(n * two_i), c_void_p(_p(y)),
+                                        c_int(n), c_int(two_i // 2), self._stream()))
+        return y
+
+    def gemm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """``x [M, K] . w [N, K]^T`` -> 32-bit partial sums ``[P, M, N]`` (their sum over P is the product)."""
+        self._need(x, self.dtype, "gemm input")
+        self._need(w, self.dtype, "gemm weight")
+        M, Kd = x.shape
+        N, K2 = w.shape
+        if Kd != K2:
+            raise KernelError(f"gemm: input rows have {Kd} elements, weight rows {K2}")
+        if self.dtype == torch.float32:
+            out = torch.empty((1, M, N), dtype=torch.float32, device=self.device)
+            self._check(self.lib.idm_gemm_f32(c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(out)), c_int(M),
+                                              c_int(N), c_int(Kd), self._stream()))
+            return out
+        return self._gemm_library(x, w)
+
+    def _gemm_library(self, x, w):
+        if M_is_zero(x):
+            return torch.empty((1, 0, w.shape[0]), dtype=torch.float32, device=self.device)
+        try:
+            out = torch.mm(x, w.t(), out_dtype=torch.float32)
+        except (TypeError, RuntimeError):
+            out = torch.mm(x, w.t()).to(torch.float32)
+        return out.unsqueeze(0)
+
+    def sample(self, logits: torch.Tensor, temperature: float, keys: Optional[torch.Tensor]) -> torch.Tensor:
+        self._need(logits, torch.float32, "logits")
+        B, V = logits.shape
+        if keys is not None:
+            self._need(keys, torch.int64, "row keys")
+            if keys.numel() != B:
+                raise KernelError("one key per row")
+        out = torch.empty((B,), dtype=torch.int32, device=self.device)
+        self._check(self.lib.idm_sample(c_void_p(_p(logits)), c_int(B), c_int(V), c_float(temperature),
+                                        c_void_p(_p(keys)), c_void_p(_p(out)), self._stream()))
+        return out
+
+
+def M_is_zero(x) -> bool:
+    return x.shape[0] == 0

@@ -1,0 +1,81 @@
+"""Causal grouped-query attention over the sequence cache (a mixer).
+
+Order of operations as the reference runs them (src/detllm/model.py:303-412):
+q/k/v projections without bias; per (token, head) RMS norm over head_dim with
+one weight of shape [head_dim] shared by all heads (model.py:200-216); rotary
+encoding after the norm; k and v written once into the cache (model.py:338-343);
+scores q.k / sqrt(head_dim) of q-head h against kv-head h // group
+(model.py:170; ops/fused_attn.py:60); softmax over the allowed keys, masked keys
+contributing exactly nothing (ops/di_softmax.py:41-61); context; heads merged
+as channel = head * head_dim + d (model.py:170-172); output projection.
+The three projections are one matrix here (rows concatenated; no dot product
+changes).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.spec import CacheNeed
+from ..weights.loader import TensorDecl
+from .base import MIXERS, POSITIONS, Mixer
+
+
+@MIXERS.register("attention")
+class GQAAttention(Mixer):
+    @classmethod
+    def declare(cls, spec, prefix):
+        p = prefix + "self_attn."
+        q_rows, kv_rows = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
+        d = [TensorDecl(p + "q_proj.weight", (q_rows, spec.hidden))]
+        if not spec.kv_from_other:
+            d += [TensorDecl(p + "k_proj.weight", (kv_rows, spec.hidden)),
+                  TensorDecl(p + "v_proj.weight", (kv_rows, spec.hidden))]
+        d.append(TensorDecl(p + "o_proj.weight", (spec.hidden, q_rows)))
+        if spec.qk_norm:
+            d.append(TensorDecl(p + "q_norm.weight", (spec.head_dim,), init="one_plus_normal"))
+            if not spec.kv_from_other:
+                d.append(TensorDecl(p + "k_norm.weight", (spec.head_dim,), init="one_plus_normal"))
+        return d
+
+    @classmethod
+    def cache_need(cls, spec) -> CacheNeed:
+        return CacheNeed(kind="window" if spec.window else "full", n_kv_heads=spec.n_kv_heads,
+                         head_dim=spec.head_dim, window=spec.window)
+
+    def __init__(self, spec, weights, prefix, rt):
+        if spec.n_heads % spec.n_kv_heads:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        self.spec = spec
+        self.rt = rt
+        p = prefix + "self_attn."
+        mats = [weights[p + "q_proj.weight"]]
+        if not spec.kv_from_other:
+            mats += [weights[p + "k_proj.weight"], weights[p + "v_proj.weight"]]
+        self.w_qkv = torch.cat([m.to(rt.dtype) for m in mats], dim=0).contiguous()
+        self.w_o = weights[p + "o_proj.weight"].to(rt.dtype).contiguous()
+        self.q_gamma = self.k_gamma = None
+        if spec.qk_norm:
+            self.q_gamma = weights[p + "q_norm.weight"].to(torch.float32).contiguous()
+            if not spec.kv_from_other:
+                self.k_gamma = weights[p + "k_norm.weight"].to(torch.float32).contiguous()
+        self.position = None
+        if spec.position is not None:
+            self.position = POSITIONS.get(spec.position.kind)(spec.position, weights, prefix, rt)
+
+    def forward(self, x, ctx, kv, state, writes_cache: bool):
+        s, K = self.spec, self.rt.kernels
+        if writes_cache == s.kv_from_other:
+            raise ValueError("a mixer with its own k/v must write its cache entry; one without must not")
+        qkv = K.gemm(x, self.w_qkv)                                   # [P, N, (n_q [+ 2 n_kv]) * hd]
+        cs = self.position.tables(ctx) if self.position is not None else None
+        windowed = kv.ring > 0
+        q, k_new, v_new = K.qkv_finish(
+            qkv, s.n_heads, 0 if s.kv_from_other else s.n_kv_heads, s.head_dim,
+            self.q_gamma, self.k_gamma, s.qk_norm_eps, cs, ctx,
+            kv if (writes_cache and not windowed) else None,
+            keep_new=writes_cache and windowed)
+        o = K.attention(q, kv, ctx, k_new, v_new, s.softmax_scale, s.window)  # [N, n_q * hd]
+        if writes_cache and windowed:
+            K.kv_write_ring(k_new, v_new, kv, ctx)
+        return K.gemm(o, self.w_o)                                    # [P, N, hidden]

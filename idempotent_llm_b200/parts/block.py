@@ -1,0 +1,35 @@
+"""Pre-norm residual block: ``h += mixer(norm(h)); h += feed_forward(norm(h))``
+(reference: src/detllm/model.py:303-427).  The residual stream stays 32-bit;
+each part's output is handed on as a pending delta, which the next norm adds in
+the same kernel that norms."""
+
+from __future__ import annotations
+
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block
+
+
+@BLOCKS.register("prenorm")
+class PreNormBlock(Block):
+    @classmethod
+    def declare(cls, spec, prefix=None):
+        p = spec.prefix
+        return (NORMS.get(spec.mixer_norm.kind).declare(spec.mixer_norm, p + "input_layernorm.")
+                + MIXERS.get(spec.mixer.kind).declare(spec.mixer, p)
+                + NORMS.get(spec.feed_forward_norm.kind).declare(spec.feed_forward_norm,
+                                                                 p + "post_attention_layernorm.")
+                + FEED_FORWARDS.get(spec.feed_forward.kind).declare(spec.feed_forward, p))
+
+    def __init__(self, spec, weights, prefix, rt):
+        p = spec.prefix
+        self.spec = spec
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, weights, p + "input_layernorm.", rt)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, weights, p, rt)
+        self.feed_forward_norm = NORMS.get(spec.feed_forward_norm.kind)(
+            spec.feed_forward_norm, weights, p + "post_attention_layernorm.", rt)
+        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, weights, p, rt)
+
+    def forward(self, h, pending, ctx, kv, state, writes_cache: bool):
+        x = self.mixer_norm.forward(h, pending, ctx)
+        a = self.mixer.forward(x, ctx, kv, state, writes_cache)
+        x = self.feed_forward_norm.forward(h, a, ctx)
+        return h, self.feed_forward.forward(x, ctx)
