@@ -59,3 +59,34 @@ extern "C" int idm_sample(const float* logits, int n_rows, int V, float temperat
     IDM_LAUNCH_CHECK("sample");
     return 0;
 }
+
+// After a captured single-token step: feed the chosen tokens back and move every sequence one
+// position on, all on the device, so that steps can follow one another without the host
+// (the reference's GraphedDecode keeps ids, positions and the write offset in device buffers the
+// same way, src/detllm/graphed.py:111-132).  history[step, :] records the chosen tokens.
+__global__ void decode_advance_kernel(int* tokens, int* positions, int* q_start, int* kv_len,
+                                      const int* sampled, int* history, int* step_counter, int n_seqs,
+                                      int max_history) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int step = *step_counter;
+    if (i < n_seqs) {
+        const int t = sampled[i];
+        tokens[i] = t;
+        positions[i] += 1;
+        q_start[i] += 1;
+        kv_len[i] += 1;
+        if (step < max_history) history[(size_t)step * n_seqs + i] = t;
+    }
+    __syncthreads();
+    if (blockIdx.x == 0 && threadIdx.x == 0) *step_counter = step + 1;   // grid is one block (n_seqs <= 1024)
+}
+
+extern "C" int idm_decode_advance(int* tokens, int* positions, int* q_start, int* kv_len, const int* sampled,
+                                  int* history, int* step_counter, int n_seqs, int max_history,
+                                  cudaStream_t stream) {
+    IDM_REQUIRE(n_seqs > 0 && n_seqs <= 1024, "decode_advance: %d sequences (at most 1024)", n_seqs);
+    decode_advance_kernel<<<1, 1024, 0, stream>>>(tokens, positions, q_start, kv_len, sampled, history,
+                                                  step_counter, n_seqs, max_history);
+    IDM_LAUNCH_CHECK("decode_advance");
+    return 0;
+}

@@ -56,6 +56,8 @@ class CausalLM:
         self.blocks = [BLOCKS.get(layer.kind)(layer, weights, layer.prefix, rt) for layer in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, weights,
                                                           spec.final_norm_prefix, rt)
+        self.graph_safe = all(getattr(part, "graph_safe", True) for b in self.blocks
+                              for part in vars(b).values())
 
     def forward(self, ctx, cache, want_rows: torch.Tensor) -> torch.Tensor:
         """Run the step's tokens; returns 32-bit logits ``[len(want_rows), vocab]``."""

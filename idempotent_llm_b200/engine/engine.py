@@ -61,6 +61,73 @@ class _DecodeGraph:
         return self.logits
 
 
+class DecodeSession:
+    """Greedy decoding of a fixed batch without the host in the loop: one captured graph holds the
+    model's single-token step, the argmax and the feedback of the chosen tokens, so ``run(n)`` is
+    ``n`` graph replays back to back (the reference's steady-state decode, scripts/bench.py:28-43:
+    ``greedy_pick(gd.step(cur))`` per step, synchronised only at the end).  Pages for all ``n``
+    steps are reserved beforehand; reads stay bounded by each sequence's length on the device."""
+
+    def __init__(self, engine: "Engine", slots: Sequence[int], first_tokens: Sequence[int], max_steps: int):
+        self.engine, self.slots, self.max_steps = engine, [int(s) for s in slots], max_steps
+        cache, dev = engine.cache, engine.device
+        B = self.n = len(self.slots)
+        self.starts = [cache.length(s) for s in self.slots]
+        cache.reserve([(s, st + max_steps) for s, st in zip(self.slots, self.starts)])
+        cache.flush()
+        packed, n, q_lens = pack_step_host(self.slots, self.starts, [[int(t)] for t in first_tokens])
+        full = torch.cat([packed, torch.arange(B, dtype=torch.int32)])
+        self.dev = full.to(dev)
+        self.history = torch.zeros((max_steps, B), dtype=torch.int32, device=dev)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.ctx = context_from_packed(self.dev, B, self.slots, q_lens, self.starts,
+                                       max_kv_len=cache.max_seq_len)
+        self.rows = self.dev[7 * B + 1:]
+        self.steps_done = 0
+        self.launches_per_step = 0
+        backup = self.dev.clone()
+        K = engine.rt.kernels
+        for _ in range(2):
+            self._one_step()
+        torch.cuda.synchronize()
+        self.dev.copy_(backup)                    # warm-up moved the positions on; start again
+        self.counter.zero_()
+        g = torch.cuda.CUDAGraph()
+        before = K.launches
+        with torch.cuda.graph(g, pool=engine._graph_pool):
+            self._one_step()
+        self.launches_per_step = K.launches - before
+        if engine._graph_pool is None:
+            engine._graph_pool = g.pool()
+        self.graph = g
+
+    def _one_step(self):
+        e, K, B = self.engine, self.engine.rt.kernels, self.n
+        self.ctx.memo.clear()
+        logits = e.model.forward(self.ctx, e.cache, self.rows)
+        picked = K.sample(logits, 0.0, None)
+        d = self.dev
+        K.decode_advance(d[0:B], d[2 * B:3 * B], d[5 * B + 1:6 * B + 1], d[6 * B + 1:7 * B + 1], picked,
+                         self.history, self.counter)
+
+    def run(self, n_steps: int) -> None:
+        if self.steps_done + n_steps > self.max_steps:
+            raise ValueError(f"the session was opened for {self.max_steps} steps")
+        for _ in range(n_steps):
+            self.graph.replay()
+        self.steps_done += n_steps
+
+    def tokens(self) -> torch.Tensor:
+        """Chosen tokens so far, ``[steps, sequences]`` (device -> host copy; synchronises)."""
+        return self.history[:self.steps_done].cpu()
+
+    def finish(self) -> None:
+        """Hand the sequences back to the engine's own bookkeeping at their new lengths."""
+        torch.cuda.synchronize()
+        for s, st in zip(self.slots, self.starts):
+            self.engine.cache.set_length(s, st + self.steps_done)
+
+
 class Engine:
     def __init__(self, model: CausalLM, max_tokens: int, max_seqs: Optional[int] = None,
                  max_seq_len: Optional[int] = None, use_graph: bool = True):
@@ -123,7 +190,7 @@ class Engine:
         packed, n, q_lens = pack_step_host(slots, starts, toks)
         self.cache.flush()
         single = all(q == 1 for q in q_lens)
-        if single and self.use_graph:
+        if single and self.use_graph and getattr(self.model, "graph_safe", True):
             g = self._graphs.get(len(slots))
             if g is None:
                 g = self._graphs[len(slots)] = _DecodeGraph(self, len(slots))
@@ -154,6 +221,10 @@ class Engine:
             torch.cuda.current_stream().synchronize()   # the previous upload from this buffer is done
         pin[:n].copy_(host)
         return pin[:n].to(self.device, non_blocking=True)
+
+    def decode_session(self, slots: Sequence[int], first_tokens: Sequence[int], max_steps: int) -> DecodeSession:
+        """A device-side greedy decode loop over ``slots`` (see ``DecodeSession``)."""
+        return DecodeSession(self, slots, first_tokens, max_steps)
 
     # sampling -----------------------------------------------------------------
     def sample(self, logits: torch.Tensor, temperature: float, seed: int,

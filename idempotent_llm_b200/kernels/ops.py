@@ -20,7 +20,7 @@ from typing import Optional
 
 import torch
 
-from . import build
+from . import builder
 
 _DT = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
 
@@ -45,14 +45,14 @@ class Kernels:
             raise KernelError(f"the kernels are compiled for sm_100a; this device is sm_{cap[0]}{cap[1]}")
         self.dtype = dtype
         self.device = device
-        self.lib = build.load(_DT[dtype])
+        self.lib = builder.load(_DT[dtype])
         self.launches = 0                     # kernels of this library launched so far
         self._scratch = {}
         self._retired = []
         L = self.lib
         for name in ("idm_embed", "idm_add_rmsnorm", "idm_rope_table", "idm_qkv_finish", "idm_kv_write_ring",
                      "idm_swiglu", "idm_sample", "idm_attention_generic", "idm_attention_decode",
-                     "idm_attention_decode_supports"):
+                     "idm_attention_decode_supports", "idm_decode_advance"):
             getattr(L, name).restype = c_int
         L.idm_attention_decode_scratch_floats.restype = c_longlong
         if dtype == torch.float32:
@@ -172,7 +172,10 @@ class Kernels:
         self._check_kv(kv, kv.n_kv_heads, hd)
         out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
         w = int(window) if window else 0
-        if ctx.single_token and k_new is None and self.lib.idm_attention_decode_supports(c_int(hd)):
+        # 32-bit keeps ONE kernel for prompts and single tokens, so its logits are the same bits
+        # however a sequence is cut into steps; bfloat16 takes the bandwidth-bound decode kernel
+        if (self.dtype != torch.float32 and ctx.single_token and k_new is None
+                and self.lib.idm_attention_decode_supports(c_int(hd))):
             return self.attention_decode(q, kv, ctx.slots, ctx.kv_len, ctx.max_kv_len, scale, w, out)
         self._check(self.lib.idm_attention_generic(
             c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_void_p(_p(kv.table)),
@@ -255,6 +258,15 @@ class Kernels:
         self._check(self.lib.idm_sample(c_void_p(_p(logits)), c_int(B), c_int(V), c_float(temperature),
                                         c_void_p(_p(keys)), c_void_p(_p(out)), self._stream()))
         return out
+
+
+    def decode_advance(self, tokens, positions, q_start, kv_len, sampled, history, step_counter) -> None:
+        """tokens <- sampled; positions, q_start, kv_len += 1; history[step] <- sampled; step += 1."""
+        n = tokens.numel()
+        self._check(self.lib.idm_decode_advance(
+            c_void_p(_p(tokens)), c_void_p(_p(positions)), c_void_p(_p(q_start)), c_void_p(_p(kv_len)),
+            c_void_p(_p(sampled)), c_void_p(_p(history)), c_void_p(_p(step_counter)), c_int(n),
+            c_int(history.shape[0]), self._stream()))
 
 
 def M_is_zero(x) -> bool:

@@ -59,6 +59,9 @@ class GQAAttention(Mixer):
             self.q_gamma = weights[p + "q_norm.weight"].to(torch.float32).contiguous()
             if not spec.kv_from_other:
                 self.k_gamma = weights[p + "k_norm.weight"].to(torch.float32).contiguous()
+        if spec.kv_from_other and spec.window:
+            raise ValueError("a mixer that reads another layer's windowed cache is not built: a prompt's "
+                             "own keys are not all in the ring")
         self.position = None
         if spec.position is not None:
             self.position = POSITIONS.get(spec.position.kind)(spec.position, weights, prefix, rt)
@@ -69,7 +72,10 @@ class GQAAttention(Mixer):
             raise ValueError("a mixer with its own k/v must write its cache entry; one without must not")
         qkv = K.gemm(x, self.w_qkv)                                   # [P, N, (n_q [+ 2 n_kv]) * hd]
         cs = self.position.tables(ctx) if self.position is not None else None
-        windowed = kv.ring > 0
+        # A windowed layer's ring cannot hold a whole prompt, so a step of several tokens reads its
+        # own keys from packed buffers and writes the ring afterwards.  A single token overwrites
+        # position p - ring only, which lies outside its window, so it is written first like any key.
+        windowed = kv.ring > 0 and not ctx.single_token
         q, k_new, v_new = K.qkv_finish(
             qkv, s.n_heads, 0 if s.kv_from_other else s.n_kv_heads, s.head_dim,
             self.q_gamma, self.k_gamma, s.qk_norm_eps, cs, ctx,

@@ -48,6 +48,10 @@ class Runtime:
 
 
 class Part:
+    # False for a part that synchronises with the host inside ``forward`` (reads device values):
+    # a model with such a part runs its single-token steps without CUDA graphs.
+    graph_safe = True
+
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
         return []

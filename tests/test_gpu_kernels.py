@@ -1,0 +1,308 @@
+"""Each kernel alone against a plain 64-bit PyTorch restatement of its formula, at sizes other
+than the tiny models' (GPU).  Attention inputs are built so that faults show: one far key is
+made to stand out, keys outside the allowed range carry NaN."""
+
+import math
+
+import pytest
+import torch
+
+import helpers
+from idempotent_llm_b200.cache import CacheNeed, SequenceCache
+from idempotent_llm_b200.engine.batch import context_from_packed, pack_step_host
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# one rounding to the storage dtype plus 32-bit arithmetic
+KTOL = {"float32": 3e-6, "bfloat16": 6e-3}
+
+
+@pytest.fixture(scope="module")
+def kernels():
+    from idempotent_llm_b200.kernels import Kernels
+    made = {}
+
+    def get(dtype):
+        if dtype not in made:
+            made[dtype] = Kernels(DT[dtype], "cuda:0")
+        return made[dtype]
+    return get
+
+
+def _randn(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed), dtype=torch.float64) * scale
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(kernels, dtype):
+    K = kernels(dtype)
+    table = _randn(1003, 72, seed=1).to(DT[dtype]).cuda()
+    ids = torch.tensor([0, 1002, 5, 5, 77], dtype=torch.int32).cuda()
+    h = K.embed(ids, table)
+    assert h.dtype == torch.float32 and torch.equal(h, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden,eps", [(72, 1e-5), (1024, 1e-6), (5120, 1e-6), (13, 0.1)])
+def test_add_rmsnorm(kernels, dtype, hidden, eps):
+    K = kernels(dtype)
+    n = 37
+    h0, gamma = _randn(n, hidden, seed=2, scale=3.0).float(), (1 + _randn(hidden, seed=3, scale=0.2)).float()
+    delta = _randn(3, n, hidden, seed=4).float()
+
+    def ref(v):
+        v = v.double()
+        return v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps) * gamma.double()
+    h = h0.clone().cuda()
+    x = K.add_rmsnorm(h, None, gamma.cuda(), eps)
+    assert torch.equal(h.cpu(), h0) and helpers.rel_err(x, ref(h0)) < KTOL[dtype]
+    x = K.add_rmsnorm(h, delta.cuda(), gamma.cuda(), eps)
+    summed = ((h0 + delta[0]) + delta[1]) + delta[2]
+    assert torch.equal(h.cpu(), summed), "the residual sum is 32-bit, partials added in ascending order"
+    assert helpers.rel_err(x, ref(summed)) < KTOL[dtype]
+    rows = torch.tensor([36, 0, 7], dtype=torch.int32).cuda()
+    h2 = h0.clone().cuda()
+    xr = K.add_rmsnorm(h2, delta.cuda(), gamma.cuda(), eps, rows=rows)
+    assert torch.equal(h2.cpu(), h0), "selected rows leave the stream untouched"
+    assert torch.equal(xr, x[rows.long()])
+
+
+def test_rope_table(kernels):
+    K = kernels("float32")
+    pos = torch.tensor([0, 1, 63, 4095, 40959], dtype=torch.int32)
+    j = torch.arange(0, 64, dtype=torch.float64)
+    inv = 1e6 ** (-2.0 * j / 128)
+    cs = K.rope_table(pos.cuda(), inv.cuda()).cpu()
+    ang = pos.double()[:, None] * inv[None, :]
+    assert (cs[..., 0].double() - torch.cos(ang)).abs().max() < 1e-7       # 32-bit rounding of an exact value
+    assert (cs[..., 1].double() - torch.sin(ang)).abs().max() < 1e-7
+
+
+def _cache_with(K, dtype, n_kv, hd, window, lens, seed, max_tokens=64 * 64):
+    """A one-entry cache whose slots hold random keys/values for positions < lens[i]; returns
+    (cache, slots, k_ref, v_ref) with references [len, n_kv, hd] per sequence in 64-bit."""
+    need = CacheNeed("window" if window else "full", n_kv, hd, window=window)
+    cache = SequenceCache({0: need}, max_tokens, DT[dtype], "cuda:0", max_seqs=len(lens) + 2)
+    # poison: nothing outside the allowed keys may be read
+    for g in cache.groups:
+        g.k.fill_(float("nan")); g.v.fill_(float("nan"))
+    cache.alloc_slot()                                   # shift slot numbers away from 0
+    slots, ks, vs = [], [], []
+    kv = cache.view(0)
+    for i, L in enumerate(lens):
+        s = cache.alloc_slot()
+        cache.reserve([(s, L)]); cache.set_length(s, L); cache.flush()
+        k = _randn(L, n_kv, hd, seed=seed + 2 * i).to(DT[dtype])
+        v = _randn(L, n_kv, hd, seed=seed + 2 * i + 1).to(DT[dtype])
+        for j in range(max(0, L - kv.ring) if kv.ring else 0, L):
+            r = j % kv.ring if kv.ring else j
+            page = int(kv.table[s, r // 64])
+            kv.k[page, :, r % 64] = k[j].cuda(); kv.v[page, :, r % 64] = v[j].cuda()
+        slots.append(s); ks.append(k.double()); vs.append(v.double())
+    return cache, slots, ks, vs
+
+
+def _attn_ref(q, k, v, scale, window, pos):
+    """q [n_q, hd] at position pos against k, v [len, n_kv, hd]."""
+    n_q, n_kv = q.shape[0], k.shape[1]
+    lo = max(0, pos - window + 1) if window else 0
+    out = torch.zeros_like(q)
+    for h in range(n_q):
+        s = (k[lo:pos + 1, h // (n_q // n_kv)] @ q[h]) * scale
+        out[h] = torch.softmax(s, 0) @ v[lo:pos + 1, h // (n_q // n_kv)]
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_q,n_kv,hd,window", [(8, 2, 64, None), (6, 6, 128, None), (12, 4, 32, 100),
+                                                (16, 2, 128, None), (3, 1, 256, None), (4, 2, 16, 70)])
+def test_attention_decode_against_plain_and_general_kernel(kernels, dtype, n_q, n_kv, hd, window):
+    K = kernels(dtype)
+    if not K.lib.idm_attention_decode_supports(hd):
+        pytest.skip("no decode kernel for this head size in this dtype; the general kernel serves it")
+    lens = [1, 64, 65, 255, 256, 257, 700, 1030]
+    cache, slots, ks, vs = _cache_with(K, dtype, n_kv, hd, window, lens, seed=5)
+    kv = cache.view(0)
+    scale = 1.0 / math.sqrt(hd)
+    q = _randn(len(lens), n_q, hd, seed=9)
+    far = {6: 3, 7: 300}                                  # sequence -> a far key that must dominate
+    for i, j in far.items():
+        if not window:
+            ks_i = ks[i]
+            q[i, 1] = ks_i[j, 1 // (n_q // n_kv)] * 4.0
+    qd = q.to(DT[dtype]).cuda()
+    packed, n, q_lens = pack_step_host(slots, [L - 1 for L in lens], [[0]] * len(lens))
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, [L - 1 for L in lens], max_kv_len=1100)
+    out = K.attention_decode(qd, kv, ctx.slots, ctx.kv_len, 1100, scale, window or 0).view(len(lens), n_q, hd)
+    gen = K.attention_generic(qd, kv, ctx, None, None, scale, window).view(len(lens), n_q, hd)
+    assert torch.isfinite(out).all() and torch.isfinite(gen).all(), "a key outside the allowed range was read"
+    for i, L in enumerate(lens):
+        ref = _attn_ref(qd[i].double().cpu(), ks[i], vs[i], scale, window, L - 1)
+        assert helpers.rel_err(out[i], ref) < KTOL[dtype], f"decode kernel, length {L}"
+        assert helpers.rel_err(gen[i], ref) < KTOL[dtype], f"general kernel, length {L}"
+    if not window:
+        got = out[7, 1].double().cpu()
+        assert (got - vs[7][300, 1 // (n_q // n_kv)]).abs().max() < 0.05, "the far key did not dominate"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_q,n_kv,hd,window", [(4, 2, 48, None), (8, 2, 128, None), (6, 3, 80, 33), (2, 1, 16, 64)])
+def test_attention_general_kernel_prompts_with_history_and_new_keys(kernels, dtype, n_q, n_kv, hd, window):
+    K = kernels(dtype)
+    # sequences with `hist` cached tokens bring `new` tokens each
+    hist, new = [0, 10, 130, 64], [70, 5, 1, 140]
+    lens = [h + n for h, n in zip(hist, new)]
+    cache, slots, ks, vs = _cache_with(K, dtype, n_kv, hd, window, lens, seed=21)
+    kv = cache.view(0)
+    scale = 0.7 / math.sqrt(hd)
+    q = [_randn(n, n_q, hd, seed=30 + i) for i, n in enumerate(new)]
+    q[3][-1, 0] = ks[3][2, 0] * 5.0                       # the last query looks far back
+    qd = torch.cat(q).to(DT[dtype]).cuda()
+    packed, n, q_lens = pack_step_host(slots, hist, [[0] * m for m in new])
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, hist)
+    k_new = v_new = None
+    if window:
+        # windowed layers read this step's keys from packed buffers: the ring may not hold them all
+        k_new = torch.cat([k[h:] for k, h in zip(ks, hist)]).to(DT[dtype]).cuda()
+        v_new = torch.cat([v[h:] for v, h in zip(vs, hist)]).to(DT[dtype]).cuda()
+    out = K.attention_generic(qd, kv, ctx, k_new, v_new, scale, window).view(-1, n_q, hd)
+    assert torch.isfinite(out).all()
+    off = 0
+    for i, (h, m) in enumerate(zip(hist, new)):
+        for t in range(m):
+            if window and h + t - window + 1 < h and h + t - window + 1 < lens[i] - kv.ring:
+                continue                                  # that history has left the ring by construction
+            ref = _attn_ref(qd[off + t].double().cpu(), ks[i], vs[i], scale, window, h + t)
+            assert helpers.rel_err(out[off + t], ref) < KTOL[dtype], f"sequence {i} token {t}"
+        off += m
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_qkv_finish_norm_rotation_and_cache_write(kernels, dtype):
+    K = kernels(dtype)
+    n_q, n_kv, hd, eps, theta = 6, 2, 48, 1e-5, 5e4
+    lens, starts = [3, 70], [5, 64]
+    need = CacheNeed("full", n_kv, hd)
+    cache = SequenceCache({0: need}, 64 * 8, DT[dtype], "cuda:0", max_seqs=4)
+    slots = [cache.alloc_slot() for _ in lens]
+    cache.reserve([(s, st + L) for s, st, L in zip(slots, starts, lens)]); cache.flush()
+    packed, n, q_lens = pack_step_host(slots, starts, [[0] * L for L in lens])
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, starts)
+    width = (n_q + 2 * n_kv) * hd
+    parts = _randn(2, n, width, seed=40).float()
+    gq, gk = (1 + _randn(hd, seed=41, scale=0.3)).float(), (1 + _randn(hd, seed=42, scale=0.3)).float()
+    inv = theta ** (-2.0 * torch.arange(0, hd // 2, dtype=torch.float64) / hd)
+    cs = K.rope_table(ctx.positions, inv.cuda())
+    kv = cache.view(0)
+    q, k_new, v_new = K.qkv_finish(parts.cuda(), n_q, n_kv, hd, gq.cuda(), gk.cuda(), eps, cs, ctx, kv, keep_new=True)
+    x = (parts[0] + parts[1]).double().view(n, n_q + 2 * n_kv, hd)
+    pos = ctx.positions.cpu().double()
+    ang = torch.cat([pos[:, None] * inv[None, :]] * 2, -1)
+    cos, sin = torch.cos(ang).float().double()[:, None, :], torch.sin(ang).float().double()[:, None, :]
+
+    def fin(t, g):
+        t = t / torch.sqrt(t.pow(2).mean(-1, keepdim=True) + eps) * g.double()
+        return t * cos + torch.cat([-t[..., hd // 2:], t[..., :hd // 2]], -1) * sin
+    assert helpers.rel_err(q, fin(x[:, :n_q], gq)) < KTOL[dtype]
+    assert helpers.rel_err(k_new, fin(x[:, n_q:n_q + n_kv], gk)) < KTOL[dtype]
+    assert helpers.rel_err(v_new, x[:, n_q + n_kv:]) < KTOL[dtype]
+    t = 0
+    for s, st, L in zip(slots, starts, lens):
+        for j in range(st, st + L):
+            page = int(kv.table[s, j // 64])
+            assert torch.equal(kv.k[page, :, j % 64], k_new[t]) and torch.equal(kv.v[page, :, j % 64], v_new[t])
+            t += 1
+    # without norm weights and without a table the heads pass through
+    q2, _, _ = K.qkv_finish(parts.cuda(), n_q, n_kv, hd, None, None, eps, None, ctx, None, keep_new=False)
+    assert helpers.rel_err(q2, x[:, :n_q]) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_ring_write_keeps_the_last_ring_tokens(kernels, dtype):
+    K = kernels(dtype)
+    n_kv, hd, window = 2, 16, 70                          # ring of 128
+    cache = SequenceCache({0: CacheNeed("window", n_kv, hd, window=window)}, 64 * 8, DT[dtype], "cuda:0", max_seqs=3)
+    slots = [cache.alloc_slot(), cache.alloc_slot()]
+    starts, lens = [0, 100], [300, 40]
+    cache.reserve([(s, st + L) for s, st, L in zip(slots, starts, lens)]); cache.flush()
+    packed, n, q_lens = pack_step_host(slots, starts, [[0] * L for L in lens])
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, starts)
+    k_new = _randn(n, n_kv, hd, seed=50).to(DT[dtype]).cuda()
+    v_new = _randn(n, n_kv, hd, seed=51).to(DT[dtype]).cuda()
+    kv = cache.view(0)
+    kv.k.zero_(); kv.v.zero_()
+    K.kv_write_ring(k_new, v_new, kv, ctx)
+    for (s, st, L), off in zip(zip(slots, starts, lens), (0, 300)):
+        for j in range(max(st, st + L - 128), st + L):
+            page, r = int(kv.table[s, (j % 128) // 64]), (j % 128) % 64
+            assert torch.equal(kv.k[page, :, r], k_new[off + j - st]), f"slot {s} position {j}"
+            assert torch.equal(kv.v[page, :, r], v_new[off + j - st])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(kernels, dtype):
+    K = kernels(dtype)
+    n, inter = 19, 1000
+    gu = _randn(2, n, 2 * inter, seed=60, scale=4.0).float()
+    gu[0, 0, 0], gu[1, 0, 0] = -200.0, 0.0                # a saturated gate stays finite
+    y = K.swiglu(gu.cuda())
+    x = (gu[0] + gu[1]).double()
+    g, u = x[:, :inter], x[:, inter:]
+    assert torch.isfinite(y).all() and helpers.rel_err(y, g * torch.sigmoid(g) * u) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (7, 1000, 160), (130, 257, 224), (64, 64, 16), (3, 5, 7)])
+def test_gemm_32_bit_is_true_32_bit_and_row_independent(kernels, M, N, K_):
+    K = kernels("float32")
+    x, w = _randn(M, K_, seed=70).float(), _randn(N, K_, seed=71).float()
+    out = K.gemm(x.cuda(), w.cuda())
+    assert out.shape == (1, M, N)
+    ref = x.double() @ w.double().T
+    # TF32 would give ~1e-3; true 32-bit FMA chains of K_ terms give ~1e-6
+    assert helpers.rel_err(out[0], ref) < 2e-6
+    one = K.gemm(x[M // 2:M // 2 + 1].contiguous().cuda(), w.cuda())
+    assert torch.equal(one[0, 0], out[0, M // 2]), "a row's result must not depend on the other rows"
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (8, 1000, 160), (200, 512, 1024)])
+def test_gemm_bfloat16(kernels, M, N, K_):
+    K = kernels("bfloat16")
+    x, w = _randn(M, K_, seed=72).bfloat16(), _randn(N, K_, seed=73).bfloat16()
+    out = K.gemm(x.cuda(), w.cuda())
+    assert out.dtype == torch.float32
+    assert helpers.rel_err(out.sum(0), x.double() @ w.double().T) < 1e-2
+
+
+def test_sampler_argmax_ties_and_gumbel(kernels):
+    import plain_qwen3 as plain
+    from idempotent_llm_b200.sampling.sampler import _as_i64, row_key
+    K = kernels("float32")
+    V = 151937
+    lg = _randn(3, V, seed=80).float()
+    lg[0, 777] = lg[0, 99999] = 50.0                      # a tie: the lower id wins
+    lg[1, V - 1] = 60.0
+    lg[2, 5] = float("nan")
+    got = K.sample(lg.cuda(), 0.0, None).tolist()
+    assert got[0] == 777 and got[1] == V - 1 and got[2] == int(torch.nan_to_num(lg[2], nan=-1e30).argmax())
+    small = _randn(4, 300, seed=81).float() * 2
+    keys = torch.tensor([_as_i64(row_key(3, r, 9)) for r in range(4)], dtype=torch.int64)
+    got = K.sample(small.cuda(), 0.7, keys.cuda()).tolist()
+    for r in range(4):
+        sc = plain.gumbel_scores(small[r], 0.7, 3, r, 9)
+        assert float(sc.max() - sc[got[r]]) < 1e-4        # the same draw up to 32-bit rounding of the noise
+    with pytest.raises(Exception, match="keys"):
+        K.sample(small.cuda(), 0.7, None)
+
+
+def test_sizes_the_kernels_cannot_take_are_refused(kernels):
+    from idempotent_llm_b200.kernels import KernelError
+    K = kernels("bfloat16")
+    with pytest.raises(KernelError, match="head_dim"):
+        K.qkv_finish(torch.zeros(1, 1, 3 * 272, device="cuda"), 1, 1, 272, None, None, 1e-6, None,
+                     type("C", (), {"token_seq": torch.zeros(1, dtype=torch.int32, device="cuda"),
+                                    "positions": torch.zeros(1, dtype=torch.int32, device="cuda"),
+                                    "slots": torch.zeros(1, dtype=torch.int32, device="cuda")})(), None, False)
+    with pytest.raises(KernelError, match="contiguous|expected"):
+        K.swiglu(torch.zeros(1, 4, 8, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(KernelError, match="rows"):
+        K.gemm(torch.zeros(2, 8, device="cuda", dtype=torch.bfloat16), torch.zeros(4, 16, device="cuda", dtype=torch.bfloat16))

@@ -1,0 +1,270 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16 (GPU)."""
+
+import pytest
+import torch
+
+import helpers
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+CASES = [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"),
+         ("C", "float32"), ("C", "bfloat16"), ("D", "float32"), ("D", "bfloat16")]
+
+
+@pytest.fixture(scope="module")
+def loaded(model_dirs):
+    """(config name, dtype, sharp) -> (LM, plain cfg, plain weights); engines are reused across tests."""
+    import idempotent_llm_b200 as idm
+    cache = {}
+
+    def get(name, dtype, sharp=1.0, max_tokens=64 * 40):
+        key = (name, dtype, sharp)
+        if key not in cache:
+            d = model_dirs(name, sharp=sharp)
+            lm = idm.load(d, dtype=dtype, max_tokens=max_tokens, max_seqs=8)
+            cache[key] = (lm, *plain.read_model(d))
+        return cache[key]
+    return get
+
+
+def _check_clean(lm):
+    assert lm.engine.cache.slots.n_held == 0 and lm.engine.cache.pages_held() == 0
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_each_request_alone_and_whole(loaded, name, dtype):
+    lm, cfg, w = loaded(name, dtype)
+    eng = lm.engine
+    for i, n in enumerate((1, 2, 5, 33, 64, 65, 150, 257)):
+        ids = helpers.rand_ids(n, cfg["vocab_size"], 10 + i)
+        slot = eng.open()
+        got = eng.step([(slot, ids)], [list(range(n))])
+        eng.close(slot)
+        assert got.shape == (n, cfg["vocab_size"]) and got.dtype == torch.float32
+        assert helpers.rel_err(got, plain.forward(cfg, w, ids)) < helpers.TOL[dtype], f"length {n}"
+    _check_clean(lm)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_last_32_tokens_one_by_one(loaded, name, dtype):
+    lm, cfg, w = loaded(name, dtype)
+    eng = lm.engine
+    for n in (33, 100, 290):
+        ids = helpers.rand_ids(n, cfg["vocab_size"], 20 + n)
+        ref = plain.forward(cfg, w, ids)
+        slot = eng.open()
+        outs = [eng.step([(slot, ids[:-32])], [list(range(n - 32))])]
+        for t in ids[-32:]:
+            outs.append(eng.step([(slot, [t])]).clone())
+        eng.close(slot)
+        got = torch.cat(outs)
+        err = (got.double().cpu() - ref).abs().amax(dim=1) / ref.abs().max()
+        bad = (err >= helpers.TOL[dtype]).nonzero()
+        assert bad.numel() == 0, f"length {n}: first wrong position {int(bad[0])} (prefix is {n - 32} long)"
+    _check_clean(lm)
+
+
+def _run_batches(eng, requests, batch_sizes, decode_tail):
+    """Requests in batches that start together: prompts (all but the last ``decode_tail[i]`` tokens)
+    in one step with logits everywhere, then one teacher-forced token each; shorter requests end
+    earlier and give their slot back; one batch after another.  Returns per-request logits."""
+    got = [None] * len(requests)
+    it = iter(range(len(requests)))
+    for bs in batch_sizes:
+        batch = [next(it) for _ in range(bs)]
+        slots = {r: eng.open() for r in batch}
+        cut = {r: len(requests[r]) - decode_tail[r] for r in batch}
+        lg = eng.step([(slots[r], requests[r][:cut[r]]) for r in batch], [list(range(cut[r])) for r in batch])
+        off, parts = 0, {r: [] for r in batch}
+        for r in batch:
+            parts[r].append(lg[off:off + cut[r]].clone())
+            off += cut[r]
+        k = 0
+        live = [r for r in batch if decode_tail[r] > 0]
+        for r in batch:
+            if r not in live:
+                eng.close(slots[r])
+        while live:
+            lg = eng.step([(slots[r], [requests[r][cut[r] + k]]) for r in live])
+            for i, r in enumerate(live):
+                parts[r].append(lg[i:i + 1].clone())
+            k += 1
+            for r in [r for r in live if decode_tail[r] <= k]:
+                eng.close(slots[r])
+            live = [r for r in live if decode_tail[r] > k]
+        for r in batch:
+            got[r] = torch.cat(parts[r])
+    return got
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_unequal_batches_one_after_another_reusing_slots(loaded, name, dtype):
+    lm, cfg, w = loaded(name, dtype)
+    eng = lm.engine
+    lens = [5, 9, 2, 70, 1, 7, 12, 3, 130, 40]
+    tails = [3, 8, 1, 6, 0, 5, 11, 2, 9, 1]
+    reqs = [helpers.rand_ids(n, cfg["vocab_size"], 40 + i) for i, n in enumerate(lens)]
+    used_before = set()
+    got = _run_batches(eng, reqs, [3, 4, 3], tails)
+    for i, ids in enumerate(reqs):
+        ref = plain.forward(cfg, w, ids)
+        err = (got[i].double().cpu() - ref).abs().amax(dim=1) / ref.abs().max()
+        bad = (err >= helpers.TOL[dtype]).nonzero()
+        assert bad.numel() == 0, (f"request {i} (length {lens[i]}, prompt part {lens[i] - tails[i]}): "
+                                  f"first wrong position {int(bad[0])}")
+    _check_clean(lm)
+
+
+@pytest.mark.parametrize("dtype", ["float32"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_32_bit_logits_are_the_same_bits_however_the_tokens_are_cut(loaded, name, dtype):
+    lm, cfg, w = loaded(name, dtype)
+    eng = lm.engine
+    lens = [70, 9, 131, 33]
+    reqs = [helpers.rand_ids(n, cfg["vocab_size"], 60 + i) for i, n in enumerate(lens)]
+    whole = []
+    for ids in reqs:
+        slot = eng.open()
+        whole.append(eng.step([(slot, ids)], [list(range(len(ids)))]).clone())
+        eng.close(slot)
+    batched = _run_batches(eng, reqs, [4], [32, 5, 32, 32])
+    for a, b in zip(whole, batched):
+        assert torch.equal(a, b)
+    rev = _run_batches(eng, reqs[::-1], [2, 2], [1, 40, 3, 0])[::-1]
+    for a, b in zip(whole, rev):
+        assert torch.equal(a, b)
+    _check_clean(lm)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("C", "float32"), ("C", "bfloat16"),
+                                        ("B", "bfloat16")])
+def test_long_decoding_with_sharp_attention(loaded, name, dtype):
+    # q_norm scaled by 6: single far keys carry weight, so a key lost at a page (64) or chunk (256)
+    # border, or a wrong position, shows as an error of order one
+    lm, cfg, w = loaded(name, dtype, sharp=6.0)
+    eng = lm.engine
+    n, prefix = 600, 60
+    ids = helpers.rand_ids(n, cfg["vocab_size"], 77)
+    ref = plain.forward(cfg, w, ids)
+    slot = eng.open()
+    outs = [eng.step([(slot, ids[:prefix])], [list(range(prefix))])]
+    for t in ids[prefix:]:
+        outs.append(eng.step([(slot, [t])]).clone())
+    eng.close(slot)
+    got = torch.cat(outs)
+    err = (got.double().cpu() - ref).abs().amax(dim=1) / ref.abs().max()
+    tol = helpers.TOL[dtype] * (2.0 if dtype == "bfloat16" else 1.0)   # sharper softmax doubles bf16's rounding
+    bad = (err >= tol).nonzero()
+    assert bad.numel() == 0, f"first wrong position {int(bad[0])}, error {float(err[int(bad[0])]):.3g}"
+    _check_clean(lm)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "bfloat16")])
+def test_first_tokens_and_junk_in_freed_pages(loaded, name, dtype):
+    lm, cfg, w = loaded(name, dtype)
+    eng = lm.engine
+    # leave NaN in every page and state: a freed page's contents must never be read
+    for g in eng.cache.groups:
+        g.k.fill_(float("nan")); g.v.fill_(float("nan"))
+    reqs = [helpers.rand_ids(n, cfg["vocab_size"], 90 + n) for n in (1, 2, 3)]
+    slots = [eng.open() for _ in reqs]
+    lg = eng.step(list(zip(slots, reqs)), [[0], [0, 1], [0, 1, 2]])
+    for s in slots:
+        eng.close(s)
+    assert torch.isfinite(lg).all()
+    ref = torch.cat([plain.forward(cfg, w, r) for r in reqs])
+    assert helpers.rel_err(lg, ref) < helpers.TOL[dtype]
+    _check_clean(lm)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_greedy_generation_through_the_entry_point(loaded, name, dtype):
+    lm, cfg, w = loaded(name, dtype)
+    prompts = [helpers.rand_ids(n, cfg["vocab_size"], 100 + n) for n in (5, 9, 2)]
+    toks, step_logits = lm.generate(prompts, 8)
+    assert toks.shape == (3, 8) and len(step_logits) == 8
+    for i, p in enumerate(prompts):
+        seq = list(p)
+        for s in range(8):
+            ref = plain.forward(cfg, w, seq)[-1]
+            assert helpers.rel_err(step_logits[s][i], ref) < helpers.TOL[dtype], f"request {i} step {s}"
+            tok = int(toks[i, s])
+            # the engine's choice is the plain argmax, or ties with it within the dtype's rounding
+            assert float(ref.max() - ref[tok]) <= helpers.TOL[dtype] * float(ref.abs().max())
+            if dtype == "float32":
+                assert tok == plain.pick(ref)
+            seq.append(tok)
+    _check_clean(lm)
+
+
+def test_reference_style_arguments_padding_and_stop(loaded):
+    lm, cfg, w = loaded("A", "float32")
+    prompts = [helpers.rand_ids(n, 256, 120 + n) for n in (4, 7)]
+    ids = torch.zeros(2, 7, dtype=torch.int64)
+    valid = torch.zeros(2, 7, dtype=torch.bool)
+    for i, p in enumerate(prompts):
+        ids[i, :len(p)] = torch.tensor(p); valid[i, :len(p)] = True
+    ids[0, 4:] = 199                                        # padding values must not matter
+    a, _ = lm.generate(ids, 5, chunk_valid=valid)
+    b, _ = lm.generate(prompts, 5, use_graph=False)
+    assert torch.equal(a, b)
+    stop = int(a[1, 1])
+    c, lg = lm.generate(prompts, 5, stop_token_ids=[stop])
+    assert c[1].tolist() == [int(a[1, 0]), stop, -1, -1, -1]
+    assert int((c[0] == stop).sum()) == 0 or c[0].tolist().index(stop) >= 0
+    assert torch.equal(lm.greedy_pick(lg[0]), c[:, 0].to(lm.device))
+    _check_clean(lm)
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("B", "bfloat16")])
+def test_temperature_sampling_follows_the_documented_generator(loaded, name, dtype):
+    lm, cfg, w = loaded(name, dtype)
+    prompts = [helpers.rand_ids(n, cfg["vocab_size"], 140 + n) for n in (1, 7, 12, 3)]
+    res = lm.generate_requests(prompts, 6, temperature=0.8, seed=11, return_logits=True)
+    again = lm.generate_requests(prompts[::-1], 6, temperature=0.8, seed=11)
+    for r in res:
+        seq = list(prompts[r.request])
+        for s, tok in enumerate(r.tokens):
+            ref = plain.forward(cfg, w, seq)[-1]
+            sc = plain.gumbel_scores(ref, 0.8, 11, r.request, s)
+            assert float(sc.max() - sc[tok]) <= 2 * helpers.TOL[dtype] * float(ref.abs().max()) / 0.8 + 1e-5
+            # the same logits through the plain generator give the same token
+            assert plain.pick(r.logits[s].cpu(), 0.8, 11, r.request, s) == tok
+            seq.append(tok)
+    # a request's draw is keyed by its index in the call, not by its row in the batch
+    assert len({tuple(r.tokens) for r in res}) > 1 and len(again) == 4
+    _check_clean(lm)
+
+
+def test_errors_leave_the_cache_usable(loaded):
+    from idempotent_llm_b200.cache import CacheError
+    lm, cfg, w = loaded("A", "float32")
+    eng = lm.engine
+    slot = eng.open()
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.step([(slot, [1, 256])])
+    with pytest.raises(ValueError, match="no token"):
+        eng.step([(slot, [])])
+    with pytest.raises(CacheError, match="exceeds|full"):
+        eng.step([(slot, [1] * (64 * 41))])
+    with pytest.raises(ValueError, match="outside"):
+        eng.step([(slot, [1, 2])], [[2]])
+    ids = helpers.rand_ids(20, 256, 5)
+    got = eng.step([(slot, ids)], [list(range(20))])
+    eng.close(slot)
+    with pytest.raises(CacheError):
+        eng.close(slot)
+    assert helpers.rel_err(got, plain.forward(cfg, w, ids)) < helpers.TOL["float32"]
+    _check_clean(lm)
+
+
+def test_graph_and_eager_decode_give_the_same_bits(loaded):
+    for dtype in ("float32", "bfloat16"):
+        lm, cfg, w = loaded("C", dtype)
+        prompts = [helpers.rand_ids(n, cfg["vocab_size"], 160 + n) for n in (30, 3, 64)]
+        a, la = lm.generate(prompts, 40, use_graph=True)
+        b, lb = lm.generate(prompts, 40, use_graph=False)
+        assert torch.equal(a, b)
+        assert all(torch.equal(x, y) for x, y in zip(la, lb))
+        lm.engine.use_graph = True

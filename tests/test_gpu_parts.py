@@ -1,0 +1,271 @@
+"""Each part alone against the plain implementation's function for it; a schedule that names a
+layer twice and shares a cache; and a toy mixer with state of its own that is registered, built
+and stepped from this file alone (GPU)."""
+
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import helpers
+import plain_qwen3 as plain
+from idempotent_llm_b200.cache import CacheNeed, SequenceCache
+from idempotent_llm_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, NormSpec, Qwen3Config,
+                                        RotarySpec, RunEntry)
+from idempotent_llm_b200.engine import CausalLM, Engine, cache_needs, declare_weights
+from idempotent_llm_b200.engine.batch import context_from_packed, pack_step_host
+from idempotent_llm_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Mixer, Runtime
+from idempotent_llm_b200.weights import TensorDecl, random_weights
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+F64 = torch.float64
+
+
+def _rt(dtype):
+    from idempotent_llm_b200.kernels import Kernels
+    dev = torch.device("cuda:0")
+    return Runtime(device=dev, dtype=DT[dtype], kernels=Kernels(DT[dtype], dev))
+
+
+def _ctx(slots, starts, lens):
+    packed, n, q_lens = pack_step_host(slots, starts, [[0] * L for L in lens])
+    return context_from_packed(packed.cuda(), n, slots, q_lens, starts)
+
+
+def _w64(w):
+    return {k: v.double().cpu() for k, v in w.items()}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_part(dtype):
+    rt = _rt(dtype)
+    spec = NormSpec(size=100, eps=3e-4)
+    cls = NORMS.get(spec.kind)
+    assert [(d.name, d.shape, d.init) for d in cls.declare(spec, "n.")] == [("n.weight", (100,), "one_plus_normal")]
+    w = random_weights(cls.declare(spec, "n."), 1, 0.3, dtype=DT[dtype], device="cuda")
+    part = cls(spec, w, "n.", rt)
+    h = torch.randn(9, 100, device="cuda")
+    x = part.forward(h, None, None)
+    assert x.dtype == DT[dtype]
+    assert helpers.rel_err(x, plain.rmsnorm(h.double().cpu(), _w64(w)["n.weight"], 3e-4)) < helpers.TOL[dtype]
+
+
+def test_rotary_part_is_shared_per_step():
+    rt = _rt("float32")
+    spec = RotarySpec(theta=7e4, dim=24, max_positions=4096)
+    part = POSITIONS.get(spec.kind)(spec, {}, "", rt)
+    ctx = _ctx([0, 1], [100, 3000], [3, 2])
+    t = part.tables(ctx)
+    assert part.tables(ctx) is t and t.shape == (5, 12, 2)
+    x = torch.randn(5, 1, 24, dtype=F64)
+    want = plain.rope(x, ctx.positions.cpu(), 7e4)
+    c, s = t[..., 0].double().cpu()[:, None, :], t[..., 1].double().cpu()[:, None, :]
+    got = torch.cat([x[..., :12] * c - x[..., 12:] * s, x[..., 12:] * c + x[..., :12] * s], -1)
+    assert (got - want).abs().max() < 1e-12
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [None, 40])
+def test_attention_part_prompt_then_single_tokens(dtype, window):
+    rt = _rt(dtype)
+    cfg = dict(num_attention_heads=6, num_key_value_heads=2, head_dim=32, hidden_size=72, rms_norm_eps=1e-5,
+               rope_theta=3e4)
+    spec = AttentionSpec(hidden=72, n_heads=6, n_kv_heads=2, head_dim=32, softmax_scale=32 ** -0.5, qk_norm=True,
+                         qk_norm_eps=1e-5, position=RotarySpec(3e4, 32, 4096), window=window)
+    cls = MIXERS.get(spec.kind)
+    w = random_weights(cls.declare(spec, "L."), 2, 0.2, dtype=DT[dtype], device="cuda")
+    assert cls.cache_need(spec) == CacheNeed("window" if window else "full", 2, 32, window=window)
+    part = cls(spec, w, "L.", rt)
+    cache = SequenceCache({0: cls.cache_need(spec)}, 64 * 8, DT[dtype], "cuda:0", max_seqs=2)
+    slot = cache.alloc_slot()
+    T, pre = 150, 140
+    x = (torch.randn(T, 72, generator=torch.Generator().manual_seed(3)) * 1.5).to(DT[dtype])
+    ref, _ = plain.attention_block(x.double(), _w64(w), "L.", cfg, torch.arange(T), window)
+    outs = []
+    for lo, hi in [(0, pre)] + [(i, i + 1) for i in range(pre, T)]:
+        cache.reserve([(slot, hi)]); cache.flush()
+        ctx = _ctx([slot], [lo], [hi - lo])
+        outs.append(part.forward(x[lo:hi].contiguous().cuda(), ctx, cache.view(0), None, True).sum(0))
+        cache.set_length(slot, hi)
+    assert helpers.rel_err(torch.cat(outs), ref) < helpers.TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_feed_forward_part(dtype):
+    rt = _rt(dtype)
+    spec = GatedMLPSpec(hidden=72, intermediate=200)
+    cls = FEED_FORWARDS.get(spec.kind)
+    w = random_weights(cls.declare(spec, "L."), 4, 0.2, dtype=DT[dtype], device="cuda")
+    part = cls(spec, w, "L.", rt)
+    x = torch.randn(11, 72).to(DT[dtype])
+    got = part.forward(x.cuda(), None).sum(0)
+    assert got.dtype == torch.float32
+    assert helpers.rel_err(got, plain.mlp_block(x.double(), _w64(w), "L.")) < helpers.TOL[dtype]
+
+
+def test_unknown_kinds_and_bad_parts_are_refused():
+    with pytest.raises(KeyError, match="no mixer registered"):
+        MIXERS.get("nope")
+    with pytest.raises(ValueError, match="activation"):
+        FEED_FORWARDS.get("gated_mlp")(GatedMLPSpec(8, 8, activation="gelu"), {}, "", None)
+
+
+def _custom_schedule_spec(schedule):
+    base = Qwen3Config.from_dict(helpers.TINY["A"]).to_model_spec()
+    layers = list(base.layers)
+    if any(not e.writes_cache for e in schedule):
+        # a third layer without k/v of its own that reads layer 1's cache
+        m = layers[1].mixer
+        reader = AttentionSpec(**{**m.__dict__, "kv_from_other": True})
+        layers.append(LayerSpec(prefix="model.layers.2.", mixer=reader, feed_forward=layers[1].feed_forward,
+                                mixer_norm=layers[1].mixer_norm, feed_forward_norm=layers[1].feed_forward_norm))
+    kw = {f: getattr(base, f) for f in ("architecture", "vocab_size", "hidden", "final_norm", "tie_embeddings",
+                                        "max_positions")}
+    return ModelSpec(layers=tuple(layers), schedule=tuple(schedule), **kw)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_layer_named_twice_and_a_layer_reading_anothers_cache(dtype):
+    rt = _rt(dtype)
+    schedule = [RunEntry(0, 0), RunEntry(1, 1), RunEntry(1, 2), RunEntry(2, 1, writes_cache=False)]
+    spec = _custom_schedule_spec(schedule)
+    decls = declare_weights(spec)
+    assert "model.layers.2.self_attn.k_proj.weight" not in {d.name for d in decls}
+    w = random_weights(decls, 5, 0.05, dtype=DT[dtype], device="cuda")
+    model = CausalLM(spec, w, rt)
+    assert sorted(cache_needs(spec)) == [0, 1, 2]
+    eng = Engine(model, 64 * 8, max_seqs=2)
+    ids = helpers.rand_ids(80, 256, 6)
+    w64 = _w64(w)
+    # the reader layer has no k/v of its own: the plain forward borrows layer 1's tensors for names it never uses
+    cfg = dict(helpers.TINY["A"], num_hidden_layers=3)
+    ref = plain.forward(cfg, w64, ids, schedule=[(0, 0, True), (1, 1, True), (1, 2, True), (2, 1, False)])
+    slot = eng.open()
+    got = [eng.step([(slot, ids[:70])], [list(range(70))])] + [eng.step([(slot, [t])]).clone() for t in ids[70:]]
+    eng.close(slot)
+    assert helpers.rel_err(torch.cat(got), ref) < helpers.TOL[dtype]
+
+
+# ------------------------------------------------------------------ a toy mixer with state
+@dataclass(frozen=True)
+class ToyDecaySpec:
+    hidden: int
+    decay: float
+    kind: str = "toy_decay"
+
+
+class ToyDecayMixer(Mixer):
+    """s_t = decay * s_{t-1} + x_t per sequence (state of fixed size, kept in the cache's state
+    region); output = s_t . W^T.  Plain torch on the device: a toy, not a kernel."""
+
+    graph_safe = False          # reads cu_q and slots on the host
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        return [TensorDecl(prefix + "toy.weight", (spec.hidden, spec.hidden))]
+
+    @classmethod
+    def cache_need(cls, spec):
+        return CacheNeed(kind="none", state_shape=(spec.hidden,), state_dtype=torch.float32)
+
+    def __init__(self, spec, weights, prefix, rt):
+        self.spec, self.rt = spec, rt
+        self.w = weights[prefix + "toy.weight"].float()
+
+    def forward(self, x, ctx, kv, state, writes_cache):
+        assert kv is None and state is not None
+        out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        cu = ctx.cu_q.tolist()
+        for i, slot in enumerate(ctx.slots.tolist()):
+            s = state[slot]
+            for t in range(cu[i], cu[i + 1]):
+                s = self.spec.decay * s + x[t].float()
+                out[t] = s @ self.w.T
+            state[slot] = s
+        return out.unsqueeze(0)
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int = 97
+    hidden_size: int = 48
+    decay: float = 0.75
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: d[k] for k in ("vocab_size", "hidden_size", "decay") if k in d})
+
+    def to_model_spec(self):
+        norm = NormSpec(self.hidden_size, 1e-5)
+        ff = GatedMLPSpec(self.hidden_size, 64)
+        attn = AttentionSpec(hidden=self.hidden_size, n_heads=3, n_kv_heads=1, head_dim=16, softmax_scale=0.25,
+                             qk_norm=True, qk_norm_eps=1e-5, position=RotarySpec(1e4, 16, 512))
+        layers = (LayerSpec("model.layers.0.", ToyDecaySpec(self.hidden_size, self.decay), ff, norm, norm),
+                  LayerSpec("model.layers.1.", attn, ff, norm, norm),
+                  LayerSpec("model.layers.2.", ToyDecaySpec(self.hidden_size, self.decay), ff, norm, norm))
+        return ModelSpec(architecture="ToyForCausalLM", vocab_size=self.vocab_size, hidden=self.hidden_size,
+                         layers=layers, schedule=tuple(RunEntry(i, i) for i in range(3)),
+                         final_norm=norm, tie_embeddings=True, max_positions=512)
+
+
+def _toy_plain(w, ids, cfg: ToyConfig):
+    ids = torch.as_tensor(ids)
+    T = ids.numel()
+    h = w["model.embed_tokens.weight"][ids]
+    acfg = dict(num_attention_heads=3, num_key_value_heads=1, head_dim=16, hidden_size=cfg.hidden_size,
+                rms_norm_eps=1e-5, rope_theta=1e4)
+    for i in range(3):
+        p = f"model.layers.{i}."
+        x = plain.rmsnorm(h, w[p + "input_layernorm.weight"], 1e-5)
+        if i == 1:
+            a, _ = plain.attention_block(x, w, p, acfg, torch.arange(T), None)
+        else:
+            s, rows = torch.zeros(cfg.hidden_size, dtype=F64), []
+            for t in range(T):
+                s = cfg.decay * s + x[t]
+                rows.append(s @ w[p + "toy.weight"].T)
+            a = torch.stack(rows)
+        h = h + a
+        h = h + plain.mlp_block(plain.rmsnorm(h, w[p + "post_attention_layernorm.weight"], 1e-5), w, p)
+    return plain.rmsnorm(h, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_its_own_state_is_registered_built_and_stepped(tmp_path, dtype):
+    import json
+    import idempotent_llm_b200 as idm
+    from idempotent_llm_b200.weights import write_safetensors
+    MIXERS.register("toy_decay", ToyDecayMixer)
+    idm.register_architecture("ToyForCausalLM", ToyConfig)
+    cfg = ToyConfig()
+    spec = cfg.to_model_spec()
+    w = random_weights(declare_weights(spec), 7, 0.2, dtype=torch.bfloat16)
+    (tmp_path / "config.json").write_text(json.dumps({"architectures": ["ToyForCausalLM"], "vocab_size": 97,
+                                                      "hidden_size": 48, "decay": 0.75}))
+    write_safetensors(str(tmp_path / "model.safetensors"), list(w.items()))
+    lm = idm.load(str(tmp_path), dtype=dtype, max_tokens=64 * 6, max_seqs=3)       # through the registry
+    eng = lm.engine
+    assert set(eng.cache.state) == {0, 2} and len(eng.cache.groups) == 1
+    w64 = _w64(w)
+    reqs = [helpers.rand_ids(n, 97, 8 + n) for n in (9, 30, 4)]
+    refs = [_toy_plain(w64, r, cfg) for r in reqs]
+    tol = helpers.TOL[dtype]
+    # whole
+    for r, ref in zip(reqs, refs):
+        s = eng.open()
+        assert helpers.rel_err(eng.step([(s, r)], [list(range(len(r)))]), ref) < tol
+        eng.close(s)
+    # a batch of unequal lengths, then one token each; slots (and their state) are used again
+    for _ in range(2):
+        slots = [eng.open() for _ in reqs]
+        cut = [len(r) - 3 for r in reqs]
+        lg = eng.step([(s, r[:c]) for s, r, c in zip(slots, reqs, cut)], [list(range(c)) for c in cut])
+        assert helpers.rel_err(lg, torch.cat([ref[:c] for ref, c in zip(refs, cut)])) < tol
+        for k in range(3):
+            lg = eng.step([(s, [r[c + k]]) for s, r, c in zip(slots, reqs, cut)])
+            assert helpers.rel_err(lg, torch.stack([ref[c + k] for ref, c in zip(refs, cut)])) < tol
+        for s in slots:
+            eng.close(s)
+    toks, _ = lm.generate(reqs, 4)
+    assert toks.shape == (3, 4) and int(toks.min()) >= 0
