@@ -94,11 +94,9 @@ class DecodeSession:
         self.counter.zero_()
         g = torch.cuda.CUDAGraph()
         before = K.launches
-        with torch.cuda.graph(g, pool=engine._graph_pool):
+        with torch.cuda.graph(g):                 # a pool of its own: it dies with the session
             self._one_step()
         self.launches_per_step = K.launches - before
-        if engine._graph_pool is None:
-            engine._graph_pool = g.pool()
         self.graph = g
 
     def _one_step(self):
@@ -196,9 +194,12 @@ class Engine:
                 g = self._graphs[len(slots)] = _DecodeGraph(self, len(slots))
             full = torch.cat([packed, torch.arange(len(slots), dtype=torch.int32)])
             logits = g.run(self, full, slots, q_lens, starts)
-            if rows != list(range(len(slots))):
+            # the graph writes its logits into the same buffer at every replay: hand out a copy
+            if rows == list(range(len(slots))):
+                logits = logits.clone()
+            else:
                 logits = logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows \
-                    else logits[:0]
+                    else logits[:0].clone()
         else:
             full = torch.cat([packed, torch.tensor(rows, dtype=torch.int32)])
             dev = self._upload(full)

@@ -56,7 +56,7 @@ def test_last_32_tokens_one_by_one(loaded, name, dtype):
         slot = eng.open()
         outs = [eng.step([(slot, ids[:-32])], [list(range(n - 32))])]
         for t in ids[-32:]:
-            outs.append(eng.step([(slot, [t])]).clone())
+            outs.append(eng.step([(slot, [t])]))
         eng.close(slot)
         got = torch.cat(outs)
         err = (got.double().cpu() - ref).abs().amax(dim=1) / ref.abs().max()
@@ -137,12 +137,13 @@ def test_32_bit_logits_are_the_same_bits_however_the_tokens_are_cut(loaded, name
     _check_clean(lm)
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("C", "float32"), ("C", "bfloat16"),
-                                        ("B", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"),
+                                        ("C", "float32"), ("C", "bfloat16")])
 def test_long_decoding_with_sharp_attention(loaded, name, dtype):
-    # q_norm scaled by 6: single far keys carry weight, so a key lost at a page (64) or chunk (256)
-    # border, or a wrong position, shows as an error of order one
-    lm, cfg, w = loaded(name, dtype, sharp=6.0)
+    # q_norm scaled up: single far keys carry weight, so a key lost at a page (64) or chunk (256)
+    # border, or a wrong position, shows as an error of order one.  Scores scale with the factor and
+    # so does their rounding error; 32-bit takes 6, bfloat16 3 (scores of std 3, rounding ~0.01).
+    lm, cfg, w = loaded(name, dtype, sharp=6.0 if dtype == "float32" else 3.0)
     eng = lm.engine
     n, prefix = 600, 60
     ids = helpers.rand_ids(n, cfg["vocab_size"], 77)
@@ -154,8 +155,7 @@ def test_long_decoding_with_sharp_attention(loaded, name, dtype):
     eng.close(slot)
     got = torch.cat(outs)
     err = (got.double().cpu() - ref).abs().amax(dim=1) / ref.abs().max()
-    tol = helpers.TOL[dtype] * (2.0 if dtype == "bfloat16" else 1.0)   # sharper softmax doubles bf16's rounding
-    bad = (err >= tol).nonzero()
+    bad = (err >= helpers.TOL[dtype]).nonzero()
     assert bad.numel() == 0, f"first wrong position {int(bad[0])}, error {float(err[int(bad[0])]):.3g}"
     _check_clean(lm)
 
@@ -199,8 +199,8 @@ def test_greedy_generation_through_the_entry_point(loaded, name, dtype):
 
 
 def test_reference_style_arguments_padding_and_stop(loaded):
-    lm, cfg, w = loaded("A", "float32")
-    prompts = [helpers.rand_ids(n, 256, 120 + n) for n in (4, 7)]
+    lm, cfg, w = loaded("B", "float32")
+    prompts = [helpers.rand_ids(n, 320, 120 + n) for n in (4, 7)]
     ids = torch.zeros(2, 7, dtype=torch.int64)
     valid = torch.zeros(2, 7, dtype=torch.bool)
     for i, p in enumerate(prompts):
@@ -210,9 +210,11 @@ def test_reference_style_arguments_padding_and_stop(loaded):
     b, _ = lm.generate(prompts, 5, use_graph=False)
     assert torch.equal(a, b)
     stop = int(a[1, 1])
+    assert stop != int(a[1, 0])
     c, lg = lm.generate(prompts, 5, stop_token_ids=[stop])
     assert c[1].tolist() == [int(a[1, 0]), stop, -1, -1, -1]
-    assert int((c[0] == stop).sum()) == 0 or c[0].tolist().index(stop) >= 0
+    k = a[0].tolist().index(stop) if stop in a[0].tolist() else 4
+    assert c[0].tolist() == a[0].tolist()[:k + 1] + [-1] * (4 - k)      # the other request is untouched
     assert torch.equal(lm.greedy_pick(lg[0]), c[:, 0].to(lm.device))
     _check_clean(lm)
 
