@@ -1,0 +1,319 @@
+// out[p, t, f] = sum over the p-th slice of k of x[t, k] * w[f, k]   (bfloat16 in, 32-bit out)
+//
+// The dense projections of the model (q/k/v, o, gate/up, down, lm_head) on the 5th-generation
+// tensor cores: tcgen05.mma issued by one thread, operands staged in shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast), the accumulator in tensor memory, read
+// back with tcgen05.ld.  The reference sends these products to a library (torch._int_mm,
+// src/detllm/backends.py:88-135).
+//
+// Roles in a block of 192 threads: warps 0-3 read the accumulator and store it (the epilogue),
+// warp 4 issues TMA loads, warp 5 allocates tensor memory and issues the MMAs.
+//
+// Tiling.  The MMA's M axis carries 128 output features (rows of w), its N axis BN tokens
+// (rows of x), so an accumulator lane is a feature and a column is a token: for one token the 32
+// lanes of a warp store 32 consecutive features, 128 contiguous bytes, with no staging.  K is
+// walked in blocks of 64 (one 128-byte swizzle row); the inner axis may be split over
+// gridDim.z blocks, each writing its own partial sum to out[p] (the consumer adds them in
+// ascending p).  How K is split depends on the layer's shape only, and an output element's value
+// depends on its own row of x and row of w only.
+//
+// Every wait on an mbarrier is bounded by a cycle count; a wait that runs out sets the error flag
+// (idm_gemm_status), all roles leave their loops, tensor memory is freed and the block returns.
+#include "common.cuh"
+
+#if defined(IDM_BF16)
+
+#include <cuda.h>
+
+#define GT_BM 128            // features per tile (MMA M)
+#define GT_BK 64             // k per stage: 64 bf16 = 128 bytes = one swizzle row
+#define GT_UMMA_K 16
+#define GT_THREADS 192
+#define GT_WAIT_CYCLES 4000000000ll   // ~2 s: far beyond any real wait
+
+__device__ int g_gemm_error = 0;
+
+// ------------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// false if the wait ran out (or another role already gave up)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > GT_WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicExch(&g_gemm_error, 1);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive 32-bit columns of this warp's 32 lanes
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of 8 rows
+// 1024 bytes apart; descriptor version 1 (sm_100); start address in units of 16 bytes.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // bits 0-13
+    d |= (uint64_t)0 << 16;                               // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset
+    d |= (uint64_t)1 << 46;                               // version
+    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor, kind::f16: D = F32, A = B = BF16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------- kernel
+template <int BN, int STAGES>
+struct GemmSmem {
+    static constexpr int A_BYTES = GT_BM * GT_BK * 2;
+    static constexpr int B_BYTES = BN * GT_BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BARRIER_BYTES = 1024;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;   // + slack to align to 1024
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                  const __grid_constant__ CUtensorMap map_x,
+                                                                  float* __restrict__ out, int n_tokens,
+                                                                  int n_features, int kb_total, int kb_per_split) {
+    using S = GemmSmem<BN, STAGES>;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;          // allocation: a power of two >= 32
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + STAGES * S::STAGE_BYTES;
+    // barriers: full[STAGES], empty[STAGES], accumulator ready; then the tensor-memory address and the abort flag
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + STAGES * S::STAGE_BYTES + 8 * (2 * STAGES + 1));
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f0 = blockIdx.x * GT_BM, t0 = blockIdx.y * BN;
+    const int kb0 = blockIdx.z * kb_per_split;
+    const int kb_n = min(kb_per_split, kb_total - kb0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *tmem_slot;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int i = 0; i < kb_n; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(empty_bar(s), ((i / STAGES) & 1) ^ 1, abort_flag)) break;
+                mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+                const uint32_t a_dst = base + s * S::STAGE_BYTES;
+                tma_load_2d(a_dst, &map_w, (kb0 + i) * GT_BK, f0, full_bar(s));
+                tma_load_2d(a_dst + S::A_BYTES, &map_x, (kb0 + i) * GT_BK, t0, full_bar(s));
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(GT_BM, BN);
+            bool ok = true;
+            for (int i = 0; i < kb_n && ok; ++i) {
+                const int s = i % STAGES;
+                ok = mbar_wait(full_bar(s), (i / STAGES) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = base + s * S::STAGE_BYTES;
+                const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + S::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < GT_BK / GT_UMMA_K; ++k) {
+                    // 16 k = 32 bytes further along the swizzled row: +2 in units of 16 bytes
+                    tc_mma_bf16(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                tc_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+            }
+            if (ok) tc_commit(accum_bar);         // the accumulator is complete once all MMAs are done
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 0-3)
+        if (mbar_wait(accum_bar, 0, abort_flag)) {
+            tc_fence_after();
+            const int f = f0 + warp * 32 + lane;                  // this thread's feature (accumulator lane)
+            float* dst = out + (size_t)blockIdx.z * n_tokens * n_features;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (t0 + c0 >= n_tokens) break;                   // warp-uniform
+                float v[16];
+                tc_ld16(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+                if (f < n_features) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c0 + j;
+                        if (t < n_tokens) dst[(size_t)t * n_features + f] = v[j];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// a [rows, k] bfloat16 row-major matrix, tiles of [box_rows, 64], 128-byte swizzle, zero fill outside
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    IDM_REQUIRE(fn != nullptr, "gemm: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    cuuint32_t box[2] = {GT_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    IDM_REQUIRE(r == CUDA_SUCCESS, "gemm: cuTensorMapEncodeTiled failed with %d (rows=%d k=%d box=%d)", (int)r, rows,
+                k, box_rows);
+    return 0;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, float* out, int M, int N, int kb_total,
+                       int kb_per_split, int splits, cudaStream_t stream) {
+    using S = GemmSmem<BN, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        IDM_REQUIRE(e == cudaSuccess, "gemm: cannot get %d bytes of shared memory: %s", S::TOTAL, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((N + GT_BM - 1) / GT_BM, (M + BN - 1) / BN, splits);
+    IDM_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm: too many tiles (%u x %u)", grid.y, grid.z);
+    gemm_tcgen05_kernel<BN, STAGES><<<grid, GT_THREADS, S::TOTAL, stream>>>(mw, mx, out, M, N, kb_total, kb_per_split);
+    IDM_LAUNCH_CHECK("gemm_tcgen05");
+    return 0;
+}
+
+// How many partial sums a product of this shape is split into.  Up to 256 tokens the split depends
+// on the layer (N, K) only, so a token's result is the same in any batch; beyond that K is not split.
+extern "C" int idm_gemm_bf16_splits(int M, int N, int K) {
+    const int kb_total = (K + GT_BK - 1) / GT_BK;
+    if (M > 256) return 1;
+    const int tiles = (N + GT_BM - 1) / GT_BM;
+    int want = 296 / tiles;                       // about two blocks per SM
+    if (want < 1) want = 1;
+    if (want > kb_total) want = kb_total;
+    if (want > 16) want = 16;
+    const int per = (kb_total + want - 1) / want;
+    return (kb_total + per - 1) / per;
+}
+
+extern "C" int idm_gemm_bf16(const void* x, const void* w, float* out, int M, int N, int K, int splits,
+                             cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    IDM_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
+    IDM_REQUIRE(K % 8 == 0, "gemm: the inner size %d must be a multiple of 8 (rows start on 16-byte borders)", K);
+    IDM_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm: operands must be 16-byte aligned");
+    const int kb_total = (K + GT_BK - 1) / GT_BK;
+    IDM_REQUIRE(splits >= 1 && splits <= kb_total, "gemm: %d splits for %d k-blocks", splits, kb_total);
+    const int per = (kb_total + splits - 1) / splits;
+    IDM_REQUIRE((kb_total + per - 1) / per == splits, "gemm: %d splits leave one empty", splits);
+    CUtensorMap mw, mx;
+    const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    if (make_map(&mw, w, N, K, GT_BM)) return 1;
+    if (make_map(&mx, x, M, K, bn)) return 1;
+    switch (bn) {
+        case 16: return launch_gemm<16, 8>(mw, mx, out, M, N, kb_total, per, splits, stream);
+        case 32: return launch_gemm<32, 8>(mw, mx, out, M, N, kb_total, per, splits, stream);
+        case 64: return launch_gemm<64, 6>(mw, mx, out, M, N, kb_total, per, splits, stream);
+        default: return launch_gemm<128, 3>(mw, mx, out, M, N, kb_total, per, splits, stream);
+    }
+}
+
+// 0, or 1 if any block's bounded wait ran out since the last call (reads the flag: synchronises)
+extern "C" int idm_gemm_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+    return v;
+}
+
+#endif  // IDM_BF16

@@ -15,6 +15,7 @@ torch wraps (cuBLASLt), as the reference sends every matrix product to
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -57,6 +58,12 @@ class Kernels:
         L.idm_attention_decode_scratch_floats.restype = c_longlong
         if dtype == torch.float32:
             L.idm_gemm_f32.restype = c_int
+        else:
+            for name in ("idm_gemm_bf16", "idm_gemm_bf16_splits", "idm_gemm_status"):
+                getattr(L, name).restype = c_int
+        # "tcgen05": the hand-written tensor-core kernel; "library": the GEMM torch wraps (kept to
+        # compare against)
+        self.gemm_impl = os.environ.get("IDM_GEMM", "tcgen05")
         self.page = L.idm_page_tokens()
 
     # ------------------------------------------------------------------ helpers
@@ -236,7 +243,17 @@ class Kernels:
             self._check(self.lib.idm_gemm_f32(c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(out)), c_int(M),
                                               c_int(N), c_int(Kd), self._stream()))
             return out
-        return self._gemm_library(x, w)
+        if self.gemm_impl == "library" or Kd % 8 or M == 0:
+            return self._gemm_library(x, w)
+        P = self.lib.idm_gemm_bf16_splits(c_int(M), c_int(N), c_int(Kd))
+        out = torch.empty((P, M, N), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_gemm_bf16(c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(out)), c_int(M), c_int(N),
+                                           c_int(Kd), c_int(P), self._stream()))
+        return out
+
+    def gemm_status(self) -> int:
+        """0, or 1 if a bounded wait inside the tensor-core GEMM ran out since the last call (synchronises)."""
+        return 0 if self.dtype == torch.float32 else self.lib.idm_gemm_status()
 
     def _gemm_library(self, x, w):
         if M_is_zero(x):

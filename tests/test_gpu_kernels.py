@@ -264,13 +264,28 @@ def test_gemm_32_bit_is_true_32_bit_and_row_independent(kernels, M, N, K_):
     assert torch.equal(one[0, 0], out[0, M // 2]), "a row's result must not depend on the other rows"
 
 
-@pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (8, 1000, 160), (200, 512, 1024)])
-def test_gemm_bfloat16(kernels, M, N, K_):
+@pytest.mark.parametrize("impl", ["tcgen05", "library"])
+@pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (8, 1000, 160), (200, 512, 1024), (17, 130, 72), (64, 1024, 3072),
+                                    (33, 257, 2048), (300, 384, 136), (1, 151936, 64), (2048, 1024, 1024)])
+def test_gemm_bfloat16(kernels, impl, M, N, K_):
     K = kernels("bfloat16")
     x, w = _randn(M, K_, seed=72).bfloat16(), _randn(N, K_, seed=73).bfloat16()
-    out = K.gemm(x.cuda(), w.cuda())
-    assert out.dtype == torch.float32
-    assert helpers.rel_err(out.sum(0), x.double() @ w.double().T) < 1e-2
+    old, K.gemm_impl = K.gemm_impl, impl
+    try:
+        out = K.gemm(x.cuda(), w.cuda())
+        torch.cuda.synchronize()
+        assert K.gemm_status() == 0, "a bounded wait inside the kernel ran out"
+        assert out.dtype == torch.float32 and out.shape[1:] == (M, N)
+        ref = x.double() @ w.double().T
+        # products of bfloat16 values are exact in 32-bit; only the accumulation rounds
+        assert helpers.rel_err(out.sum(0), ref) < 2e-5
+        if impl == "tcgen05" and M > 1:
+            # a token's partial sums do not depend on what else is in the batch (same split of K)
+            one = K.gemm(x[M // 2:M // 2 + 1].contiguous().cuda(), w.cuda())
+            if one.shape[0] == out.shape[0]:
+                assert torch.equal(one[:, 0], out[:, M // 2])
+    finally:
+        K.gemm_impl = old
 
 
 def test_sampler_argmax_ties_and_gumbel(kernels):

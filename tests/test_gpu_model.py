@@ -141,8 +141,11 @@ def test_32_bit_logits_are_the_same_bits_however_the_tokens_are_cut(loaded, name
                                         ("C", "float32"), ("C", "bfloat16")])
 def test_long_decoding_with_sharp_attention(loaded, name, dtype):
     # q_norm scaled up: single far keys carry weight, so a key lost at a page (64) or chunk (256)
-    # border, or a wrong position, shows as an error of order one.  Scores scale with the factor and
-    # so does their rounding error; 32-bit takes 6, bfloat16 3 (scores of std 3, rounding ~0.01).
+    # border, or a wrong position, shows as an error of order one (at factor 3 the best key of a few
+    # hundred holds about a fifth of the weight).  32-bit takes factor 6 at its usual tolerance.  In
+    # bfloat16 q and k are rounded to 8 bits, so a score s is off by about |s| / 300; at factor 3 the
+    # leading scores are near 10 and their weights move by a few percent in each of the layers, on top
+    # of the rounding the unsharpened model has: the bound is twice the usual one, fixed on that ground.
     lm, cfg, w = loaded(name, dtype, sharp=6.0 if dtype == "float32" else 3.0)
     eng = lm.engine
     n, prefix = 600, 60
@@ -155,7 +158,8 @@ def test_long_decoding_with_sharp_attention(loaded, name, dtype):
     eng.close(slot)
     got = torch.cat(outs)
     err = (got.double().cpu() - ref).abs().amax(dim=1) / ref.abs().max()
-    bad = (err >= helpers.TOL[dtype]).nonzero()
+    tol = helpers.TOL[dtype] * (2.0 if dtype == "bfloat16" else 1.0)
+    bad = (err >= tol).nonzero()
     assert bad.numel() == 0, f"first wrong position {int(bad[0])}, error {float(err[int(bad[0])]):.3g}"
     _check_clean(lm)
 
