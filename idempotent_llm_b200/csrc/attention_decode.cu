@@ -249,3 +249,43 @@ extern "C" int idm_attention_decode(const void* q, void* out, void* k_pool, void
     IDM_LAUNCH_CHECK("attention_decode_merge");
     return 0;
 }
+
+// ------------------------------------------------------------------ entry point without allocation
+// Declared and documented in idm_no_alloc.h.  The partial results of the chunks go to a fixed array
+// that is part of the loaded library instead of caller-provided scratch.
+#include "idm_no_alloc.h"
+
+static __device__ __align__(256) float g_decode_scratch[IDM_NO_ALLOC_MAX_SCRATCH_FLOATS];
+
+#define IDM_NO_ALLOC_MAX_DEVICES 64
+static float* g_decode_scratch_ptr[IDM_NO_ALLOC_MAX_DEVICES];   // device address of the array, per device
+
+extern "C" int idm_attention_decode_static(const void* q, void* out, void* k_pool, void* v_pool,
+                                           const int* table, int table_stride, int ring, const int* slots,
+                                           const int* kv_len, int n_seqs, int n_q, int n_kv, int hd,
+                                           int max_kv_len, float scale, int window, cudaStream_t stream) {
+    if (n_seqs == 0) return 0;
+    IDM_REQUIRE(n_seqs > 0 && n_q > 0 && hd > 0 && max_kv_len > 0, "attention_decode_static: bad sizes");
+    const long long n_chunks = (max_kv_len + AD_CHUNK - 1) / AD_CHUNK;
+    const long long need = (long long)n_seqs * n_q * n_chunks * (hd + 2);
+    IDM_REQUIRE(need <= (long long)IDM_NO_ALLOC_MAX_SCRATCH_FLOATS,
+                "attention_decode_static: %d sequences x %d heads x %lld chunks x (%d + 2) = %lld floats of scratch; "
+                "the built-in array holds %lld",
+                n_seqs, n_q, n_chunks, hd, need, (long long)IDM_NO_ALLOC_MAX_SCRATCH_FLOATS);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    IDM_REQUIRE(e == cudaSuccess, "attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    IDM_REQUIRE(dev >= 0 && dev < IDM_NO_ALLOC_MAX_DEVICES, "attention_decode_static: device %d out of range", dev);
+    if (g_decode_scratch_ptr[dev] == nullptr) {
+        // set-up, once per device, with that device current: the array's name is a host-side stand-in
+        // here, not a device address; the address a kernel can use comes from the runtime
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_decode_scratch);
+        IDM_REQUIRE(e == cudaSuccess && p != nullptr, "attention_decode_static: cudaGetSymbolAddress: %s",
+                    cudaGetErrorString(e));
+        g_decode_scratch_ptr[dev] = p;
+    }
+    // nothing in the array has to start at zero: every chunk that the merge reads was written by this call
+    return idm_attention_decode(q, out, k_pool, v_pool, table, table_stride, ring, slots, kv_len,
+                                g_decode_scratch_ptr[dev], n_seqs, n_q, n_kv, hd, max_kv_len, scale, window, stream);
+}
