@@ -173,20 +173,43 @@ __global__ void attention_decode_merge_kernel(DecodeArgs a, int hd) {
     const int lo = a.window > 0 ? max(0, len - a.window) : 0;
     const int c0 = lo / AD_CHUNK, c1 = (len - 1) / AD_CHUNK;
     const size_t row0 = (size_t)warp * a.n_chunks;
+    // lane c holds chunk c0 + c (+32, +64, ...): maxima and sums of up to 32 chunks at a time
     float M = -INFINITY;
-    for (int c = c0; c <= c1; ++c) M = fmaxf(M, a.part_ml[(row0 + c) * 2]);
+    for (int c = c0 + lane; c <= c1; c += 32) M = fmaxf(M, a.part_ml[(row0 + c) * 2]);
+    M = warp_max(M);
     float L = 0.f;
     float acc[IDM_MAX_HEAD_DIM / 32];
 #pragma unroll
     for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) acc[i] = 0.f;
-    for (int c = c0; c <= c1; ++c) {
-        const float mc = a.part_ml[(row0 + c) * 2];
-        const float f = mc == -INFINITY ? 0.f : exp2f(mc - M);
-        L += f * a.part_ml[(row0 + c) * 2 + 1];
+    for (int cb = c0; cb <= c1; cb += 32) {
+        const int mine = cb + lane;
+        float f_mine = 0.f, l_mine = 0.f;
+        if (mine <= c1) {
+            const float mc = a.part_ml[(row0 + mine) * 2];
+            f_mine = mc == -INFINITY ? 0.f : exp2f(mc - M);
+            l_mine = a.part_ml[(row0 + mine) * 2 + 1];
+        }
+        const int n_here = min(32, c1 - cb + 1);
+        for (int j0 = 0; j0 < n_here; j0 += 4) {                   // four chunks' loads in flight together
+            float f[4], o[4][IDM_MAX_HEAD_DIM / 32];
 #pragma unroll
-        for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
-            const int d = lane + 32 * i;
-            if (d < hd) acc[i] += f * a.part_o[(row0 + c) * hd + d];
+            for (int u = 0; u < 4; ++u) {
+                const int j = j0 + u;
+                f[u] = __shfl_sync(0xffffffffu, f_mine, j & 31);
+                const float lj = __shfl_sync(0xffffffffu, l_mine, j & 31);
+                if (j < n_here) L += f[u] * lj;                    // ascending chunks
+#pragma unroll
+                for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
+                    const int d = lane + 32 * i;
+                    o[u][i] = (j < n_here && d < hd) ? a.part_o[(row0 + cb + j) * hd + d] : 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (j0 + u < n_here) {
+#pragma unroll
+                    for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) acc[i] += f[u] * o[u][i];
+                }
         }
     }
     const float inv = 1.0f / L;

@@ -85,6 +85,23 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return t;
 }
 
+// Sum of the partial results base[p * stride + idx], p = 0 .. n-1, added in ascending p onto `start`.
+// The loads of a group of 8 are issued together (they do not wait on one another); only the adds
+// are a chain.
+__device__ __forceinline__ float add_partials(float start, const float* __restrict__ base, int n, size_t stride,
+                                              size_t idx) {
+    float v = start;
+    for (int p0 = 0; p0 < n; p0 += 8) {
+        float part[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) part[i] = (p0 + i < n) ? __ldg(base + (size_t)(p0 + i) * stride + idx) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (p0 + i < n) v += part[i];
+    }
+    return v;
+}
+
 // ------------------------------------------------------- cache addressing
 // One cache entry: pools [pages, kv_heads, IDM_PAGE, head_dim]; a sequence's
 // pages through table[slot * table_stride + i]; key j sits at ring position

@@ -37,8 +37,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restric
     float* hr = h + (size_t)r * hidden;
     float ss = 0.f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        float v = hr[c];
-        for (int p = 0; p < n_partials; ++p) v += delta[p * partial_stride + (size_t)r * hidden + c];
+        const float v = add_partials(hr[c], delta, n_partials, partial_stride, (size_t)r * hidden + c);
         if (!rows && n_partials) hr[c] = v;
         vals[c] = v;
         ss += v * v;
@@ -49,12 +48,55 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restric
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) from_f32(xr[c], vals[c] * inv * gamma[c]);
 }
 
+// The same for rows of at most 4 * 256 elements with hidden % 4 == 0: a thread owns four consecutive
+// elements, and all of its loads (the stream and up to 16 partials) are in flight at once.
+__global__ void __launch_bounds__(256) add_rmsnorm_vec4_kernel(float* __restrict__ h, const float* __restrict__ delta,
+                                                               int n_partials, size_t partial_stride,
+                                                               const float* __restrict__ gamma, float eps,
+                                                               T* __restrict__ x, const int* __restrict__ rows,
+                                                               int hidden) {
+    __shared__ float scratch[32];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    const int c = threadIdx.x * 4;
+    const bool live = c < hidden;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+        const size_t idx = (size_t)r * hidden + c;
+        v = *reinterpret_cast<const float4*>(h + idx);
+        float4 part[16];
+#pragma unroll
+        for (int p = 0; p < 16; ++p)
+            if (p < n_partials) part[p] = *reinterpret_cast<const float4*>(delta + p * partial_stride + idx);
+#pragma unroll
+        for (int p = 0; p < 16; ++p)
+            if (p < n_partials) { v.x += part[p].x; v.y += part[p].y; v.z += part[p].z; v.w += part[p].w; }
+        if (!rows && n_partials) *reinterpret_cast<float4*>(h + idx) = v;
+    }
+    const float total = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    if (live) {
+        const float4 gm = *reinterpret_cast<const float4*>(gamma + c);
+        T* xr = x + (size_t)i * hidden + c;
+        from_f32(xr[0], v.x * inv * gm.x); from_f32(xr[1], v.y * inv * gm.y);
+        from_f32(xr[2], v.z * inv * gm.z); from_f32(xr[3], v.w * inv * gm.w);
+    }
+}
+
 extern "C" int idm_add_rmsnorm(float* h, const float* delta, int n_partials, long long partial_stride,
                                const float* gamma, float eps, void* x, const int* rows, int n_rows,
                                int hidden, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     IDM_REQUIRE(hidden > 0 && n_rows > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
     IDM_REQUIRE((size_t)hidden * 4 <= 160 * 1024, "add_rmsnorm: hidden=%d does not fit shared memory", hidden);
+    if (hidden % 4 == 0 && hidden <= 1024 && n_partials <= 16 && (partial_stride % 4) == 0) {
+        // NOTE: the sum of squares is taken over the same values in a different thread layout than
+        // the general kernel; which kernel runs depends on `hidden` and the number of partials only
+        add_rmsnorm_vec4_kernel<<<n_rows, 256, 0, stream>>>(h, delta, delta ? n_partials : 0, (size_t)partial_stride,
+                                                            gamma, eps, (T*)x, rows, hidden);
+        IDM_LAUNCH_CHECK("add_rmsnorm");
+        return 0;
+    }
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -119,10 +161,8 @@ __global__ void qkv_finish_kernel(QkvArgs a) {
         const int j = lane + 32 * i;
         x1[i] = x2[i] = 0.f;
         if (j < half) {
-            for (int p = 0; p < a.n_partials; ++p) {
-                x1[i] += a.qkv[p * a.partial_stride + row + j];
-                x2[i] += a.qkv[p * a.partial_stride + row + j + half];
-            }
+            x1[i] = add_partials(0.f, a.qkv, a.n_partials, a.partial_stride, row + j);
+            x2[i] = add_partials(0.f, a.qkv, a.n_partials, a.partial_stride, row + j + half);
             ss += x1[i] * x1[i] + x2[i] * x2[i];
         }
     }
@@ -228,11 +268,8 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, int n_partials, size
     if (i >= total) return;
     const size_t t = i / inter, c = i % inter;
     const size_t base = t * 2 * (size_t)inter + c;
-    float g = 0.f, u = 0.f;
-    for (int p = 0; p < n_partials; ++p) {
-        g += gu[p * partial_stride + base];
-        u += gu[p * partial_stride + base + inter];
-    }
+    const float g = add_partials(0.f, gu, n_partials, partial_stride, base);
+    const float u = add_partials(0.f, gu, n_partials, partial_stride, base + inter);
     from_f32(y[i], g / (1.0f + expf(-g)) * u);
 }
 

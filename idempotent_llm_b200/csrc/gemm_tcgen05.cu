@@ -23,92 +23,14 @@
 
 #if defined(IDM_BF16)
 
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 #define GT_BM 128            // features per tile (MMA M)
 #define GT_BK 64             // k per stage: 64 bf16 = 128 bytes = one swizzle row
 #define GT_UMMA_K 16
 #define GT_THREADS 192
-#define GT_WAIT_CYCLES 4000000000ll   // ~2 s: far beyond any real wait
 
 __device__ int g_gemm_error = 0;
-
-// ------------------------------------------------------------------------------- PTX
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// false if the wait ran out (or another role already gave up)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-        if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > GT_WAIT_CYCLES) {
-            *abort_flag = 1;
-            atomicExch(&g_gemm_error, 1);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-                 " [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 16 consecutive 32-bit columns of this warp's 32 lanes
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v) {
-    uint32_t r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of 8 rows
-// 1024 bytes apart; descriptor version 1 (sm_100); start address in units of 16 bytes.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // bits 0-13
-    d |= (uint64_t)0 << 16;                               // leading byte offset: unused for swizzled K-major
-    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset
-    d |= (uint64_t)1 << 46;                               // version
-    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor, kind::f16: D = F32, A = B = BF16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
 
 // ---------------------------------------------------------------------------- kernel
 template <int BN, int STAGES>
@@ -147,12 +69,10 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         mbar_init(accum_bar, 1);
         *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_init_fence();
     }
     if (warp == 5) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
     }
     tc_fence_before();
     __syncthreads();
@@ -164,7 +84,7 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
         if (lane == 0) {
             for (int i = 0; i < kb_n; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(empty_bar(s), ((i / STAGES) & 1) ^ 1, abort_flag)) break;
+                if (i >= STAGES && !mbar_wait(empty_bar(s), ((i / STAGES) & 1) ^ 1, abort_flag, &g_gemm_error)) break;
                 mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
                 const uint32_t a_dst = base + s * S::STAGE_BYTES;
                 tma_load_2d(a_dst, &map_w, (kb0 + i) * GT_BK, f0, full_bar(s));
@@ -178,11 +98,11 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
             bool ok = true;
             for (int i = 0; i < kb_n && ok; ++i) {
                 const int s = i % STAGES;
-                ok = mbar_wait(full_bar(s), (i / STAGES) & 1, abort_flag);
+                ok = mbar_wait(full_bar(s), (i / STAGES) & 1, abort_flag, &g_gemm_error);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a_addr = base + s * S::STAGE_BYTES;
-                const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + S::A_BYTES);
+                const uint64_t a_desc = umma_desc_kmajor(a_addr), b_desc = umma_desc_kmajor(a_addr + S::A_BYTES);
 #pragma unroll
                 for (int k = 0; k < GT_BK / GT_UMMA_K; ++k) {
                     // 16 k = 32 bytes further along the swizzled row: +2 in units of 16 bytes
@@ -194,7 +114,7 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 0-3)
-        if (mbar_wait(accum_bar, 0, abort_flag)) {
+        if (mbar_wait(accum_bar, 0, abort_flag, &g_gemm_error)) {
             tc_fence_after();
             const int f = f0 + warp * 32 + lane;                  // this thread's feature (accumulator lane)
             float* dst = out + (size_t)blockIdx.z * n_tokens * n_features;
@@ -216,41 +136,18 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
     tc_fence_before();
     __syncthreads();
     if (warp == 5) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)TMEM_COLS)
-                     : "memory");
+        tmem_dealloc(tmem_d, TMEM_COLS);
     }
 }
 
 // ------------------------------------------------------------------------------ host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
 // a [rows, k] bfloat16 row-major matrix, tiles of [box_rows, 64], 128-byte swizzle, zero fill outside
 static int make_map(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    IDM_REQUIRE(fn != nullptr, "gemm: the driver does not offer cuTensorMapEncodeTiled");
     cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)k * 2};
     cuuint32_t box[2] = {GT_BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    IDM_REQUIRE(r == CUDA_SUCCESS, "gemm: cuTensorMapEncodeTiled failed with %d (rows=%d k=%d box=%d)", (int)r, rows,
-                k, box_rows);
+    const int r = tc_make_map_bf16(map, ptr, 2, dims, strides, box);
+    IDM_REQUIRE(r == 0, "gemm: cuTensorMapEncodeTiled failed with %d (rows=%d k=%d box=%d)", r, rows, k, box_rows);
     return 0;
 }
 

@@ -30,6 +30,7 @@ class StepContext:
     single_token: bool         # every sequence brings exactly one token
     host_q_lens: List[int]
     host_slots: List[int]
+    host_starts: List[int]
     memo: Dict = field(default_factory=dict)   # per-step shared tables (position encodings)
 
 
@@ -77,4 +78,4 @@ def context_from_packed(dev_buf: torch.Tensor, n: int, slots: List[int], q_lens:
         max_q_len=max(q_lens) if q_lens else 0,
         max_kv_len=max_kv_len if max_kv_len is not None else max(s + q for s, q in zip(starts, q_lens)),
         single_token=all(q == 1 for q in q_lens),
-        host_q_lens=list(q_lens), host_slots=list(slots))
+        host_q_lens=list(q_lens), host_slots=list(slots), host_starts=list(starts))

@@ -59,11 +59,14 @@ class Kernels:
         if dtype == torch.float32:
             L.idm_gemm_f32.restype = c_int
         else:
-            for name in ("idm_gemm_bf16", "idm_gemm_bf16_splits", "idm_gemm_status"):
+            for name in ("idm_gemm_bf16", "idm_gemm_bf16_splits", "idm_gemm_status", "idm_attention_prefill",
+                         "idm_attention_prefill_supports", "idm_attention_prefill_status"):
                 getattr(L, name).restype = c_int
         # "tcgen05": the hand-written tensor-core kernel; "library": the GEMM torch wraps (kept to
         # compare against)
         self.gemm_impl = os.environ.get("IDM_GEMM", "tcgen05")
+        # "tcgen05": prompts' attention on the tensor cores; "general": the one-warp-per-query kernel
+        self.prefill_impl = os.environ.get("IDM_PREFILL", "tcgen05")
         self.page = L.idm_page_tokens()
 
     # ------------------------------------------------------------------ helpers
@@ -184,6 +187,9 @@ class Kernels:
         if (self.dtype != torch.float32 and ctx.single_token and k_new is None
                 and self.lib.idm_attention_decode_supports(c_int(hd))):
             return self.attention_decode(q, kv, ctx.slots, ctx.kv_len, ctx.max_kv_len, scale, w, out)
+        if (self.dtype == torch.bfloat16 and self.prefill_impl == "tcgen05" and not ctx.single_token
+                and k_new is None and not w and kv.ring == 0 and self.lib.idm_attention_prefill_supports(c_int(hd))):
+            return self.attention_prefill(q, kv, ctx, scale, out)
         self._check(self.lib.idm_attention_generic(
             c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_void_p(_p(kv.table)),
             c_int(kv.table.shape[1]), c_int(kv.ring), c_void_p(_p(k_new)), c_void_p(_p(v_new)),
@@ -191,6 +197,34 @@ class Kernels:
             c_void_p(_p(ctx.q_start)), c_void_p(_p(ctx.cu_q)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads),
             c_int(hd), c_float(scale), c_int(w), self._stream()))
         return out
+
+    def attention_prefill(self, q, kv, ctx, scale: float, out=None) -> torch.Tensor:
+        """Causal attention of prompts on the tensor cores (tiles of 128 query tokens x q-heads)."""
+        n, n_q, hd = q.shape
+        if out is None:
+            out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
+        tiles = ctx.memo.get("prefill_tiles")
+        if tiles is None:
+            # (sequence, first token of the tile); tiles with the most keys first, so that the longest
+            # blocks start first
+            items = []
+            for i, L in enumerate(ctx.host_q_lens):
+                for st in range(0, L, 128):
+                    items.append((ctx.host_starts[i] + min(st + 127, L - 1), i, st))
+            items.sort(key=lambda t: -t[0])
+            host = torch.tensor([[i for _, i, _ in items], [st for _, _, st in items]], dtype=torch.int32)
+            tiles = ctx.memo["prefill_tiles"] = (host.to(self.device), len(items))
+        dev, n_tiles = tiles
+        self._check(self.lib.idm_attention_prefill(
+            c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_int(kv.k.shape[0]),
+            c_void_p(_p(kv.table)), c_int(kv.table.shape[1]), c_void_p(dev[0].data_ptr()),
+            c_void_p(dev[1].data_ptr()), c_int(n_tiles), c_void_p(_p(ctx.cu_q)), c_void_p(_p(ctx.q_start)),
+            c_void_p(_p(ctx.kv_len)), c_void_p(_p(ctx.slots)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads),
+            c_int(hd), c_float(scale), self._stream()))
+        return out
+
+    def attention_prefill_status(self) -> int:
+        return 0 if self.dtype == torch.float32 else self.lib.idm_attention_prefill_status()
 
     def attention_generic(self, q, kv, ctx, k_new, v_new, scale: float, window) -> torch.Tensor:
         """The general kernel, whatever the step's shape (tests compare the special kernels with it)."""

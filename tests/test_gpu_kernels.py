@@ -177,6 +177,40 @@ def test_attention_general_kernel_prompts_with_history_and_new_keys(kernels, dty
         off += m
 
 
+@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (4, 4, 64), (6, 1, 128)])
+def test_attention_prefill_tensor_core_kernel(kernels, n_q, n_kv, hd):
+    """Tiles of 128 queries against pages of 64 keys: lengths straddle both borders, one sequence
+    continues from cached history, unused page tails and free pages hold NaN, one query looks at a
+    single far key."""
+    K = kernels("bfloat16")
+    hist, new = [0, 0, 70, 0, 300], [1, 128, 200, 129, 333]
+    lens = [h + n for h, n in zip(hist, new)]
+    cache, slots, ks, vs = _cache_with(K, "bfloat16", n_kv, hd, None, lens, seed=90)
+    kv = cache.view(0)
+    scale = 1.0 / math.sqrt(hd)
+    q = [_randn(n, n_q, hd, seed=95 + i) for i, n in enumerate(new)]
+    q[4][-1, 0] = ks[4][5, 0] * 4.0                        # the last query of the longest sequence looks at key 5
+    q[2][100, n_q - 1] = ks[2][69, n_kv - 1] * 4.0         # a query looking at the last key of the history
+    qd = torch.cat(q).to(torch.bfloat16).cuda()
+    packed, n, q_lens = pack_step_host(slots, hist, [[0] * m for m in new])
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, hist)
+    out = K.attention_prefill(qd, kv, ctx, scale).view(-1, n_q, hd)
+    torch.cuda.synchronize()
+    assert K.attention_prefill_status() == 0, "a bounded wait inside the kernel ran out"
+    gen = K.attention_generic(qd, kv, ctx, None, None, scale, None).view(-1, n_q, hd)
+    assert torch.isfinite(out).all(), "stale page contents leaked into the result"
+    off = 0
+    for i, (h, m) in enumerate(zip(hist, new)):
+        for t in list(range(min(m, 3))) + list(range(max(0, m - 3), m)) + [m // 2, min(m - 1, 127), min(m - 1, 128)]:
+            ref = _attn_ref(qd[off + t].double().cpu(), ks[i], vs[i], scale, None, h + t)
+            assert helpers.rel_err(out[off + t], ref) < KTOL["bfloat16"], f"sequence {i} token {t} of {m}"
+        off += m
+    # everywhere: against the general kernel (both round p or the output to bfloat16 once)
+    assert helpers.rel_err(out, gen) < 2 * KTOL["bfloat16"]
+    got = out[sum(new) - 1, 0].double().cpu()
+    assert (got - vs[4][5, 0]).abs().max() < 0.05, "the far key did not dominate"
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_qkv_finish_norm_rotation_and_cache_write(kernels, dtype):
     K = kernels(dtype)
