@@ -32,6 +32,8 @@ struct DecodeArgs {
 
 template <int HD, int GT>
 __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     constexpr int LPR = HD / VEC;            // lanes per row
     constexpr int RPI = 32 / LPR;            // rows (keys) per warp-wide load
@@ -166,6 +168,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
 
 // out[s, head, :] = sum_c 2^(m_c - M) o_c / sum_c 2^(m_c - M) l_c over the sequence's chunks, ascending.
 __global__ void attention_decode_merge_kernel(DecodeArgs a, int hd) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= a.n_seqs * a.n_q) return;
     const int s = warp / a.n_q;
@@ -224,9 +228,9 @@ __global__ void attention_decode_merge_kernel(DecodeArgs a, int hd) {
 template <int HD>
 static int launch_decode(const DecodeArgs& a, int group_heads, cudaStream_t stream) {
     dim3 grid(a.n_chunks, a.n_kv, a.n_seqs);
-    if (group_heads % 4 == 0) attention_decode_kernel<HD, 4><<<grid, AD_WARPS * 32, 0, stream>>>(a);
-    else if (group_heads % 2 == 0) attention_decode_kernel<HD, 2><<<grid, AD_WARPS * 32, 0, stream>>>(a);
-    else attention_decode_kernel<HD, 1><<<grid, AD_WARPS * 32, 0, stream>>>(a);
+    if (group_heads % 4 == 0) idm_launch(attention_decode_kernel<HD, 4>, dim3(grid), dim3(AD_WARPS * 32), 0, stream, a);
+    else if (group_heads % 2 == 0) idm_launch(attention_decode_kernel<HD, 2>, dim3(grid), dim3(AD_WARPS * 32), 0, stream, a);
+    else idm_launch(attention_decode_kernel<HD, 1>, dim3(grid), dim3(AD_WARPS * 32), 0, stream, a);
     return 0;
 }
 
@@ -268,7 +272,7 @@ extern "C" int idm_attention_decode(const void* q, void* out, void* k_pool, void
     else launch_decode<(VEC * 32 <= 256 ? VEC * 32 : 256)>(a, gh, stream);
     IDM_LAUNCH_CHECK("attention_decode");
     const int warps = n_seqs * n_q;
-    attention_decode_merge_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(a, hd);
+    idm_launch(attention_decode_merge_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, a, hd);
     IDM_LAUNCH_CHECK("attention_decode_merge");
     return 0;
 }

@@ -27,6 +27,8 @@ struct AttnArgs {
 #define AG_WARPS 4
 
 __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(AttnArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long w = (long long)blockIdx.x * AG_WARPS + wib;
@@ -112,8 +114,7 @@ extern "C" int idm_attention_generic(const void* q, void* out, void* k_pool, voi
     a.token_seq = token_seq; a.positions = positions; a.slots = slots; a.q_start = q_start; a.cu_q = cu_q;
     a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd; a.scale = scale; a.window = window;
     const long long warps = (long long)n_tokens * n_q;
-    attention_generic_kernel<<<(unsigned)((warps + AG_WARPS - 1) / AG_WARPS), AG_WARPS * 32,
-                               AG_WARPS * hd * sizeof(float), stream>>>(a);
+    idm_launch(attention_generic_kernel, dim3((unsigned)((warps + AG_WARPS - 1) / AG_WARPS)), dim3(AG_WARPS * 32), AG_WARPS * hd * sizeof(float), stream, a);
     IDM_LAUNCH_CHECK("attention_generic");
     return 0;
 }

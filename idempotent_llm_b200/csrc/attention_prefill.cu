@@ -76,17 +76,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x, head = blockIdx.y;
-    const int seq = a.tile_seq[tile], tstart = a.tile_start[tile];
-    const int g = head / (a.n_q / a.n_kv);
-    const int tok0 = a.cu_q[seq] + tstart;                       // first token (packed row) of the tile
-    const int q_len = a.cu_q[seq + 1] - a.cu_q[seq];
-    const int rows_valid = min(AP_BM, q_len - tstart);
-    const int p_first = a.q_start[seq] + tstart;                 // position of row 0
-    const int p_last = p_first + rows_valid - 1;
-    const int kv_len = a.kv_len[seq];
-    const int nb = p_last / AP_BN + 1;                           // key blocks 0 .. nb-1
-
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(p_full, 4); mbar_init(o_done, 1);
         for (int i = 0; i < 2; ++i) {
@@ -101,6 +91,18 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_o = tmem + 128;                          // S buffers at columns 0 and 64, O from 128
+    pdl_wait();                                                  // set-up done; now the previous kernel's results
+
+    const int tile = blockIdx.x, head = blockIdx.y;
+    const int seq = a.tile_seq[tile], tstart = a.tile_start[tile];
+    const int g = head / (a.n_q / a.n_kv);
+    const int tok0 = a.cu_q[seq] + tstart;                       // first token (packed row) of the tile
+    const int q_len = a.cu_q[seq + 1] - a.cu_q[seq];
+    const int rows_valid = min(AP_BM, q_len - tstart);
+    const int p_first = a.q_start[seq] + tstart;                 // position of row 0
+    const int p_last = p_first + rows_valid - 1;
+    const int kv_len = a.kv_len[seq];
+    const int nb = p_last / AP_BN + 1;                           // key blocks 0 .. nb-1
 
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
@@ -290,7 +292,7 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
         configured = true;
     }
     dim3 grid(n_tiles, a.n_q);
-    attention_prefill_kernel<HD><<<grid, AP_THREADS, S::TOTAL, stream>>>(mq, mk, mv, a);
+    idm_launch(attention_prefill_kernel<HD>, dim3(grid), dim3(AP_THREADS), S::TOTAL, stream, mq, mk, mv, a);
     IDM_LAUNCH_CHECK("attention_prefill");
     return 0;
 }

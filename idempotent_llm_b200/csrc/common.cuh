@@ -36,6 +36,30 @@ int idm_fail(const char* fmt, ...);   // records the message, returns 1
          if (e_ != cudaSuccess) return idm_fail("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
     } while (0)
 
+// ------------------------------------------- programmatic dependent launch
+// Every kernel of this library starts with pdl_launch_dependents() and executes pdl_wait() before
+// its first access to global memory that an earlier kernel may have written (or may still read).
+// Launched with the programmatic-serialization attribute, the next kernel's blocks are scheduled
+// while this one still runs and do their set-up (and, in the matrix product, fetch weights, which
+// no kernel writes) before the wait returns.  Without the attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+int idm_pdl_enabled();   // runtime.cu: IDM_PDL=0 in the environment switches the attribute off
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t idm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = idm_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ----------------------------------------------------------- conversions
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

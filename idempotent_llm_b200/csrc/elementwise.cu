@@ -7,6 +7,8 @@
 // h[t, :] = table[tokens[t], :]  (a pure lookup, no scaling: src/detllm/model.py:246-249)
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                              float* __restrict__ h, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const T* row = table + (size_t)tokens[t] * hidden;
     float* out = h + (size_t)t * hidden;
@@ -17,7 +19,7 @@ extern "C" int idm_embed(const int* tokens, const void* table, float* h, int n_t
                          cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     IDM_REQUIRE(n_tokens > 0 && hidden > 0, "embed: bad sizes n_tokens=%d hidden=%d", n_tokens, hidden);
-    embed_kernel<<<n_tokens, 256, 0, stream>>>(tokens, (const T*)table, h, hidden);
+    idm_launch(embed_kernel, dim3(n_tokens), dim3(256), 0, stream, tokens, (const T*)table, h, hidden);
     IDM_LAUNCH_CHECK("embed");
     return 0;
 }
@@ -30,6 +32,8 @@ extern "C" int idm_embed(const int* tokens, const void* table, float* h, int n_t
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
                                    size_t partial_stride, const float* __restrict__ gamma, float eps,
                                    T* __restrict__ x, const int* __restrict__ rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     extern __shared__ float vals[];            // the row, kept between the two passes
     const int i = blockIdx.x;
@@ -55,6 +59,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec4_kernel(float* __restrict
                                                                const float* __restrict__ gamma, float eps,
                                                                T* __restrict__ x, const int* __restrict__ rows,
                                                                int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -92,7 +98,7 @@ extern "C" int idm_add_rmsnorm(float* h, const float* delta, int n_partials, lon
     if (hidden % 4 == 0 && hidden <= 1024 && n_partials <= 16 && (partial_stride % 4) == 0) {
         // NOTE: the sum of squares is taken over the same values in a different thread layout than
         // the general kernel; which kernel runs depends on `hidden` and the number of partials only
-        add_rmsnorm_vec4_kernel<<<n_rows, 256, 0, stream>>>(h, delta, delta ? n_partials : 0, (size_t)partial_stride,
+        idm_launch(add_rmsnorm_vec4_kernel, dim3(n_rows), dim3(256), 0, stream, h, delta, delta ? n_partials : 0, (size_t)partial_stride,
                                                             gamma, eps, (T*)x, rows, hidden);
         IDM_LAUNCH_CHECK("add_rmsnorm");
         return 0;
@@ -100,7 +106,7 @@ extern "C" int idm_add_rmsnorm(float* h, const float* delta, int n_partials, lon
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<<<n_rows, 256, smem, stream>>>(h, delta, delta ? n_partials : 0,
+    idm_launch(add_rmsnorm_kernel, dim3(n_rows), dim3(256), smem, stream, h, delta, delta ? n_partials : 0,
                                                       (size_t)partial_stride, gamma, eps, (T*)x, rows, hidden);
     IDM_LAUNCH_CHECK("add_rmsnorm");
     return 0;
@@ -111,6 +117,8 @@ extern "C" int idm_add_rmsnorm(float* h, const float* delta, int n_partials, lon
 // rounded to 32-bit (src/detllm/ops/rope.py:25-35 builds its table the same way).
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                   float2* __restrict__ cs, int n_tokens, int half) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_tokens * half) return;
     const int t = i / half, j = i % half;
@@ -124,7 +132,7 @@ extern "C" int idm_rope_table(const int* positions, const double* inv_freq, floa
     if (n_tokens == 0) return 0;
     IDM_REQUIRE(half > 0, "rope_table: bad half=%d", half);
     const int n = n_tokens * half;
-    rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, inv_freq, (float2*)cs, n_tokens, half);
+    idm_launch(rope_table_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, positions, inv_freq, (float2*)cs, n_tokens, half);
     IDM_LAUNCH_CHECK("rope_table");
     return 0;
 }
@@ -147,6 +155,8 @@ struct QkvArgs {
 };
 
 __global__ void qkv_finish_kernel(QkvArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int heads = a.n_q + 2 * a.n_kv;
     if (warp >= a.n_tokens * heads) return;
@@ -223,7 +233,7 @@ extern "C" int idm_qkv_finish(const float* qkv, int n_partials, long long partia
     a.write_cache = k_pool != nullptr;
     a.token_seq = token_seq; a.positions = positions; a.slots = slots;
     const long long warps = (long long)n_tokens * (n_q + 2 * n_kv);
-    qkv_finish_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(a);
+    idm_launch(qkv_finish_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, a);
     IDM_LAUNCH_CHECK("qkv_finish");
     return 0;
 }
@@ -236,6 +246,8 @@ __global__ void kv_write_ring_kernel(const T* __restrict__ k_new, const T* __res
                                      const int* __restrict__ token_seq, const int* __restrict__ positions,
                                      const int* __restrict__ slots, const int* __restrict__ kv_len,
                                      int n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n_tokens * c.n_kv) return;
     const int t = warp / c.n_kv, g = warp % c.n_kv;
@@ -253,7 +265,7 @@ extern "C" int idm_kv_write_ring(const void* k_new, const void* v_new, void* k_p
     if (n_tokens == 0) return 0;
     KVAddr c{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
     const long long warps = (long long)n_tokens * n_kv;
-    kv_write_ring_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(
+    idm_launch(kv_write_ring_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, 
         (const T*)k_new, (const T*)v_new, c, token_seq, positions, slots, kv_len, n_tokens);
     IDM_LAUNCH_CHECK("kv_write_ring");
     return 0;
@@ -264,6 +276,8 @@ extern "C" int idm_kv_write_ring(const void* k_new, const void* v_new, void* k_p
 // (src/detllm/ops/di_swiglu.py:43-45; float form tests/test_ops.py:240-242).
 __global__ void swiglu_kernel(const float* __restrict__ gu, int n_partials, size_t partial_stride,
                               T* __restrict__ y, int inter, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / inter, c = i % inter;
@@ -278,7 +292,7 @@ extern "C" int idm_swiglu(const float* gu, int n_partials, long long partial_str
     if (n_tokens == 0) return 0;
     IDM_REQUIRE(inter > 0 && n_partials >= 1, "swiglu: bad sizes");
     const size_t total = (size_t)n_tokens * inter;
-    swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(gu, n_partials, (size_t)partial_stride,
+    idm_launch(swiglu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, gu, n_partials, (size_t)partial_stride,
                                                                       (T*)y, inter, total);
     IDM_LAUNCH_CHECK("swiglu");
     return 0;

@@ -10,6 +10,8 @@
 
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                        float* __restrict__ out, int M, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float xs[GK][GB + 4];
     __shared__ float ws[GK][GB + 4];
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
@@ -62,7 +64,7 @@ extern "C" int idm_gemm_f32(const float* x, const float* w, float* out, int M, i
     IDM_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_f32: bad sizes M=%d N=%d K=%d", M, N, K);
     dim3 grid((N + GB - 1) / GB, (M + GB - 1) / GB);
     IDM_REQUIRE(grid.y <= 65535, "gemm_f32: M=%d is too large for one launch", M);
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, out, M, N, K);
+    idm_launch(gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, x, w, out, M, N, K);
     IDM_LAUNCH_CHECK("gemm_f32");
     return 0;
 }

@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
                                                                   int n_features, int kb_total, int kb_per_split) {
     using S = GemmSmem<BN, STAGES>;
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;          // allocation: a power of two >= 32
+    pdl_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -82,9 +83,19 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            for (int i = 0; i < kb_n; ++i) {
+            // Weights are written by no kernel: the first stages' weight tiles are fetched before
+            // the wait on the previous kernel; the activations follow after it.
+            const int early = min(kb_n, STAGES);
+            for (int i = 0; i < early; ++i) {
+                mbar_expect_tx(full_bar(i), S::STAGE_BYTES);
+                tma_load_2d(base + i * S::STAGE_BYTES, &map_w, (kb0 + i) * GT_BK, f0, full_bar(i));
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(base + i * S::STAGE_BYTES + S::A_BYTES, &map_x, (kb0 + i) * GT_BK, t0, full_bar(i));
+            for (int i = early; i < kb_n; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(empty_bar(s), ((i / STAGES) & 1) ^ 1, abort_flag, &g_gemm_error)) break;
+                if (!mbar_wait(empty_bar(s), ((i / STAGES) & 1) ^ 1, abort_flag, &g_gemm_error)) break;
                 mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
                 const uint32_t a_dst = base + s * S::STAGE_BYTES;
                 tma_load_2d(a_dst, &map_w, (kb0 + i) * GT_BK, f0, full_bar(s));
@@ -116,6 +127,7 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
         // ------------------------------------------------------------ epilogue (warps 0-3)
         if (mbar_wait(accum_bar, 0, abort_flag, &g_gemm_error)) {
             tc_fence_after();
+            pdl_wait();                                           // (already satisfied: the activations came after it)
             const int f = f0 + warp * 32 + lane;                  // this thread's feature (accumulator lane)
             float* dst = out + (size_t)blockIdx.z * n_tokens * n_features;
 #pragma unroll 1
@@ -164,7 +176,7 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, float* out,
     }
     dim3 grid((N + GT_BM - 1) / GT_BM, (M + BN - 1) / BN, splits);
     IDM_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm: too many tiles (%u x %u)", grid.y, grid.z);
-    gemm_tcgen05_kernel<BN, STAGES><<<grid, GT_THREADS, S::TOTAL, stream>>>(mw, mx, out, M, N, kb_total, kb_per_split);
+    idm_launch(gemm_tcgen05_kernel<BN, STAGES>, dim3(grid), dim3(GT_THREADS), S::TOTAL, stream, mw, mx, out, M, N, kb_total, kb_per_split);
     IDM_LAUNCH_CHECK("gemm_tcgen05");
     return 0;
 }

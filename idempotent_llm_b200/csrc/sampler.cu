@@ -18,6 +18,8 @@ __device__ __forceinline__ void better(float& bs, int& bi, float s, int i) {
 
 __global__ void sample_kernel(const float* __restrict__ logits, int V, float temperature,
                               const long long* __restrict__ keys, int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float ss[32];
     __shared__ int si[32];
     const int row = blockIdx.x;
@@ -55,7 +57,7 @@ extern "C" int idm_sample(const float* logits, int n_rows, int V, float temperat
     if (n_rows == 0) return 0;
     IDM_REQUIRE(V > 0, "sample: empty vocabulary");
     IDM_REQUIRE(!(temperature > 0.f) || keys != nullptr, "sample: temperature > 0 needs row keys");
-    sample_kernel<<<n_rows, 1024, 0, stream>>>(logits, V, temperature, keys, out);
+    idm_launch(sample_kernel, dim3(n_rows), dim3(1024), 0, stream, logits, V, temperature, keys, out);
     IDM_LAUNCH_CHECK("sample");
     return 0;
 }
@@ -67,6 +69,8 @@ extern "C" int idm_sample(const float* logits, int n_rows, int V, float temperat
 __global__ void decode_advance_kernel(int* tokens, int* positions, int* q_start, int* kv_len,
                                       const int* sampled, int* history, int* step_counter, int n_seqs,
                                       int max_history) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int step = *step_counter;
     if (i < n_seqs) {
@@ -85,7 +89,7 @@ extern "C" int idm_decode_advance(int* tokens, int* positions, int* q_start, int
                                   int* history, int* step_counter, int n_seqs, int max_history,
                                   cudaStream_t stream) {
     IDM_REQUIRE(n_seqs > 0 && n_seqs <= 1024, "decode_advance: %d sequences (at most 1024)", n_seqs);
-    decode_advance_kernel<<<1, 1024, 0, stream>>>(tokens, positions, q_start, kv_len, sampled, history,
+    idm_launch(decode_advance_kernel, dim3(1), dim3(1024), 0, stream, tokens, positions, q_start, kv_len, sampled, history,
                                                   step_counter, n_seqs, max_history);
     IDM_LAUNCH_CHECK("decode_advance");
     return 0;
