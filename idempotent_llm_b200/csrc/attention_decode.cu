@@ -6,9 +6,11 @@
 // Each row of head_dim elements is split over LPR lanes in 16-byte pieces; a warp-wide
 // load covers 32 / LPR keys.  Scores, the running maximum, the exponentials and the
 // context are 32-bit.  Every chunk writes an unnormalised partial (max, sum, context)
-// to scratch; a second kernel merges a sequence's chunks in ascending order.  Which
-// keys form a chunk and in which order everything is added depend on the sequence's
-// length only: a sequence's result is the same alone or in any batch.
+// to scratch; the block that finishes last for a (sequence, kv-head) -- found with a
+// counter in scratch that it sets back to zero -- merges that sequence's chunks in
+// ascending order, whichever block it is.  Which keys form a chunk and in which order
+// everything is added depend on the sequence's length only: a sequence's result is the
+// same alone or in any batch.
 //
 // Masked keys (beyond the length, or before the window) give p = 0 exactly and are left
 // out of the maximum (src/detllm/ops/di_softmax.py:45-58 does this with an integer
@@ -19,6 +21,8 @@
 #define AD_CHUNK 256
 #define AD_WARPS 4
 #define AD_ITERS 8            // warp-wide loads in flight per group
+#define AD_COUNTER_SLOTS 65536  // arrival counters at the start of scratch: a fixed place, so that they are
+                                // zero at every launch whatever the sizes of earlier launches were
 
 struct DecodeArgs {
     const T* q; T* out;
@@ -26,9 +30,66 @@ struct DecodeArgs {
     const int* slots; const int* kv_len;
     float* part_o;            // [n_seqs, n_q, n_chunks, hd]
     float* part_ml;           // [n_seqs, n_q, n_chunks, 2]
+    int* counters;            // [n_seqs, n_kv], zero between launches
     int n_seqs, n_q, n_kv, n_chunks;
     float scale_log2; int window;
 };
+
+// out[s, head, :] = sum_c 2^(m_c - M) o_c / sum_c 2^(m_c - M) l_c over the sequence's chunks, ascending.
+// One warp per (sequence, q-head).  Partials were written by other blocks: read around L1.
+__device__ __forceinline__ void decode_merge_head(const DecodeArgs& a, int s, int head, int hd, int lane) {
+    const int warp = s * a.n_q + head;
+    const int len = a.kv_len[s];
+    const int lo = a.window > 0 ? max(0, len - a.window) : 0;
+    const int c0 = lo / AD_CHUNK, c1 = (len - 1) / AD_CHUNK;
+    const size_t row0 = (size_t)warp * a.n_chunks;
+    // lane c holds chunk c0 + c (+32, +64, ...): maxima and sums of up to 32 chunks at a time
+    float M = -INFINITY;
+    for (int c = c0 + lane; c <= c1; c += 32) M = fmaxf(M, __ldcg(a.part_ml + (row0 + c) * 2));
+    M = warp_max(M);
+    float L = 0.f;
+    float acc[IDM_MAX_HEAD_DIM / 32];
+#pragma unroll
+    for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) acc[i] = 0.f;
+    for (int cb = c0; cb <= c1; cb += 32) {
+        const int mine = cb + lane;
+        float f_mine = 0.f, l_mine = 0.f;
+        if (mine <= c1) {
+            const float mc = __ldcg(a.part_ml + (row0 + mine) * 2);
+            f_mine = mc == -INFINITY ? 0.f : exp2f(mc - M);
+            l_mine = __ldcg(a.part_ml + (row0 + mine) * 2 + 1);
+        }
+        const int n_here = min(32, c1 - cb + 1);
+        for (int j0 = 0; j0 < n_here; j0 += 4) {                   // four chunks' loads in flight together
+            float f[4], o[4][IDM_MAX_HEAD_DIM / 32];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = j0 + u;
+                f[u] = __shfl_sync(0xffffffffu, f_mine, j & 31);
+                const float lj = __shfl_sync(0xffffffffu, l_mine, j & 31);
+                if (j < n_here) L += f[u] * lj;                    // ascending chunks
+#pragma unroll
+                for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
+                    const int d = lane + 32 * i;
+                    o[u][i] = (j < n_here && d < hd) ? __ldcg(a.part_o + (row0 + cb + j) * hd + d) : 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (j0 + u < n_here) {
+#pragma unroll
+                    for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) acc[i] += f[u] * o[u][i];
+                }
+        }
+    }
+    const float inv = 1.0f / L;
+    T* orow = a.out + (size_t)warp * hd;
+#pragma unroll
+    for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < hd) from_f32(orow[d], acc[i] * inv);
+    }
+}
 
 template <int HD, int GT>
 __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeArgs a) {
@@ -70,11 +131,14 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
             constexpr int KEYS = IDM_PAGE;
             for (int k0 = 0; k0 < KEYS; k0 += GROUP) {
                 if (kb + k0 >= len || kb + k0 + GROUP <= lo) continue;       // warp-uniform
-                Vec16<T> kv[AD_ITERS];
+                Vec16<T> kv[AD_ITERS], vv[AD_ITERS];             // keys and values: all loads in flight together
 #pragma unroll
                 for (int it = 0; it < AD_ITERS; ++it) {
                     const int r = k0 + it * RPI + sub;
-                    if (r < KEYS) kv[it].load(kpage + (size_t)r * HD + li * VEC);
+                    if (r < KEYS) {
+                        kv[it].load(kpage + (size_t)r * HD + li * VEC);
+                        vv[it].load(vpage + (size_t)r * HD + li * VEC);
+                    }
                 }
                 float sc[AD_ITERS][GT];
 #pragma unroll
@@ -93,12 +157,6 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
                         for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
                         sc[it][h] = ok ? d : -INFINITY;
                     }
-                }
-                // values of the same keys
-#pragma unroll
-                for (int it = 0; it < AD_ITERS; ++it) {
-                    const int r = k0 + it * RPI + sub;
-                    if (r < KEYS) kv[it].load(vpage + (size_t)r * HD + li * VEC);
                 }
 #pragma unroll
                 for (int h = 0; h < GT; ++h) {
@@ -119,7 +177,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
                         ps += p;
                         if (p != 0.f) {
 #pragma unroll
-                            for (int e = 0; e < VEC; ++e) acc[h][e] = fmaf(p, kv[it].get(e), acc[h][e]);
+                            for (int e = 0; e < VEC; ++e) acc[h][e] = fmaf(p, vv[it].get(e), acc[h][e]);
                         }
                     }
                     l[h] = l[h] * alpha + ps;
@@ -164,64 +222,20 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
             if (d == 0) { a.part_ml[row * 2] = M; a.part_ml[row * 2 + 1] = L; }
         }
     }
-}
-
-// out[s, head, :] = sum_c 2^(m_c - M) o_c / sum_c 2^(m_c - M) l_c over the sequence's chunks, ascending.
-__global__ void attention_decode_merge_kernel(DecodeArgs a, int hd) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= a.n_seqs * a.n_q) return;
-    const int s = warp / a.n_q;
-    const int len = a.kv_len[s];
-    const int lo = a.window > 0 ? max(0, len - a.window) : 0;
-    const int c0 = lo / AD_CHUNK, c1 = (len - 1) / AD_CHUNK;
-    const size_t row0 = (size_t)warp * a.n_chunks;
-    // lane c holds chunk c0 + c (+32, +64, ...): maxima and sums of up to 32 chunks at a time
-    float M = -INFINITY;
-    for (int c = c0 + lane; c <= c1; c += 32) M = fmaxf(M, a.part_ml[(row0 + c) * 2]);
-    M = warp_max(M);
-    float L = 0.f;
-    float acc[IDM_MAX_HEAD_DIM / 32];
-#pragma unroll
-    for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) acc[i] = 0.f;
-    for (int cb = c0; cb <= c1; cb += 32) {
-        const int mine = cb + lane;
-        float f_mine = 0.f, l_mine = 0.f;
-        if (mine <= c1) {
-            const float mc = a.part_ml[(row0 + mine) * 2];
-            f_mine = mc == -INFINITY ? 0.f : exp2f(mc - M);
-            l_mine = a.part_ml[(row0 + mine) * 2 + 1];
-        }
-        const int n_here = min(32, c1 - cb + 1);
-        for (int j0 = 0; j0 < n_here; j0 += 4) {                   // four chunks' loads in flight together
-            float f[4], o[4][IDM_MAX_HEAD_DIM / 32];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int j = j0 + u;
-                f[u] = __shfl_sync(0xffffffffu, f_mine, j & 31);
-                const float lj = __shfl_sync(0xffffffffu, l_mine, j & 31);
-                if (j < n_here) L += f[u] * lj;                    // ascending chunks
-#pragma unroll
-                for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
-                    const int d = lane + 32 * i;
-                    o[u][i] = (j < n_here && d < hd) ? a.part_o[(row0 + cb + j) * hd + d] : 0.f;
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (j0 + u < n_here) {
-#pragma unroll
-                    for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) acc[i] += f[u] * o[u][i];
-                }
-        }
+    // The block that arrives last for this (sequence, kv-head) merges the chunks.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int live = (len - 1) / AD_CHUNK - lo / AD_CHUNK + 1;
+        const int prev = atomicAdd(&a.counters[s * a.n_kv + g], 1);
+        is_last = prev == live - 1;
+        if (is_last) a.counters[s * a.n_kv + g] = 0;             // ready for the next launch
     }
-    const float inv = 1.0f / L;
-    T* orow = a.out + (size_t)warp * hd;
-#pragma unroll
-    for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
-        const int d = lane + 32 * i;
-        if (d < hd) from_f32(orow[d], acc[i] * inv);
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        for (int h = wib; h < group_heads; h += AD_WARPS) decode_merge_head(a, s, g * group_heads + h, HD, lane);
     }
 }
 
@@ -242,7 +256,7 @@ extern "C" int idm_attention_decode_supports(int hd) {
 
 // floats of scratch for the partials: part_o then part_ml
 extern "C" long long idm_attention_decode_scratch_floats(int n_seqs, int n_q, int n_chunks, int hd) {
-    return (long long)n_seqs * n_q * n_chunks * (hd + 2);
+    return (long long)AD_COUNTER_SLOTS + (long long)n_seqs * n_q * n_chunks * (hd + 2);   // counters + partials
 }
 
 extern "C" int idm_attention_decode(const void* q, void* out, void* k_pool, void* v_pool, const int* table,
@@ -259,8 +273,11 @@ extern "C" int idm_attention_decode(const void* q, void* out, void* k_pool, void
     a.slots = slots; a.kv_len = kv_len;
     a.n_seqs = n_seqs; a.n_q = n_q; a.n_kv = n_kv;
     a.n_chunks = (max_kv_len + AD_CHUNK - 1) / AD_CHUNK;
-    a.part_o = scratch;
-    a.part_ml = scratch + (size_t)n_seqs * n_q * a.n_chunks * hd;
+    IDM_REQUIRE((long long)n_seqs * n_kv <= AD_COUNTER_SLOTS, "attention_decode: %d sequences x %d kv-heads exceed %d",
+                n_seqs, n_kv, AD_COUNTER_SLOTS);
+    a.counters = (int*)scratch;
+    a.part_o = scratch + AD_COUNTER_SLOTS;
+    a.part_ml = a.part_o + (size_t)n_seqs * n_q * a.n_chunks * hd;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.window = window;
     const int gh = n_q / n_kv;
@@ -271,9 +288,6 @@ extern "C" int idm_attention_decode(const void* q, void* out, void* k_pool, void
     else if (hd == VEC * 16) launch_decode<VEC * 16>(a, gh, stream);
     else launch_decode<(VEC * 32 <= 256 ? VEC * 32 : 256)>(a, gh, stream);
     IDM_LAUNCH_CHECK("attention_decode");
-    const int warps = n_seqs * n_q;
-    idm_launch(attention_decode_merge_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, a, hd);
-    IDM_LAUNCH_CHECK("attention_decode_merge");
     return 0;
 }
 
@@ -294,7 +308,7 @@ extern "C" int idm_attention_decode_static(const void* q, void* out, void* k_poo
     if (n_seqs == 0) return 0;
     IDM_REQUIRE(n_seqs > 0 && n_q > 0 && hd > 0 && max_kv_len > 0, "attention_decode_static: bad sizes");
     const long long n_chunks = (max_kv_len + AD_CHUNK - 1) / AD_CHUNK;
-    const long long need = (long long)n_seqs * n_q * n_chunks * (hd + 2);
+    const long long need = idm_attention_decode_scratch_floats(n_seqs, n_q, (int)n_chunks, hd);
     IDM_REQUIRE(need <= (long long)IDM_NO_ALLOC_MAX_SCRATCH_FLOATS,
                 "attention_decode_static: %d sequences x %d heads x %lld chunks x (%d + 2) = %lld floats of scratch; "
                 "the built-in array holds %lld",
@@ -312,7 +326,9 @@ extern "C" int idm_attention_decode_static(const void* q, void* out, void* k_poo
                     cudaGetErrorString(e));
         g_decode_scratch_ptr[dev] = p;
     }
-    // nothing in the array has to start at zero: every chunk that the merge reads was written by this call
+    // the partial results need no clearing (every chunk the merge reads was written by this call); the
+    // arrival counters behind them must be zero at launch: the array starts as zeros and each launch
+    // sets its counters back to zero before it ends
     return idm_attention_decode(q, out, k_pool, v_pool, table, table_stride, ring, slots, kv_len,
                                 g_decode_scratch_ptr[dev], n_seqs, n_q, n_kv, hd, max_kv_len, scale, window, stream);
 }

@@ -210,9 +210,9 @@ extern "C" int idm_gemm_bf16(const void* x, const void* w, float* out, int M, in
     if (make_map(&mw, w, N, K, GT_BM)) return 1;
     if (make_map(&mx, x, M, K, bn)) return 1;
     switch (bn) {
-        case 16: return launch_gemm<16, 8>(mw, mx, out, M, N, kb_total, per, splits, stream);
-        case 32: return launch_gemm<32, 8>(mw, mx, out, M, N, kb_total, per, splits, stream);
-        case 64: return launch_gemm<64, 6>(mw, mx, out, M, N, kb_total, per, splits, stream);
+        case 16: return launch_gemm<16, 6>(mw, mx, out, M, N, kb_total, per, splits, stream);
+        case 32: return launch_gemm<32, 6>(mw, mx, out, M, N, kb_total, per, splits, stream);
+        case 64: return launch_gemm<64, 4>(mw, mx, out, M, N, kb_total, per, splits, stream);
         default: return launch_gemm<128, 3>(mw, mx, out, M, N, kb_total, per, splits, stream);
     }
 }

@@ -15,16 +15,17 @@
 // is loaded holds that array until the process exits.
 //
 // Limits and rules.
-//  * n_seqs * n_q * ceil(max_kv_len / 256) * (head_dim + 2) must not exceed
+//  * 65536 + n_seqs * n_q * ceil(max_kv_len / 256) * (head_dim + 2) must not exceed
 //    IDM_NO_ALLOC_MAX_SCRATCH_FLOATS; a larger request is refused with a message
 //    (idm_last_error) and nothing is launched.
 //  * The function calls no cudaMalloc, cudaFree or other allocating routine.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
 //    that device current).  Make that first call outside any stream capture.
-//  * All calls share the one array, which keeps what the last call left in it.  Nothing in it has to
-//    be cleared between calls (each call writes every partial result it later reads), but two calls
-//    that overlap on the GPU, on different streams, race on it: keep them on one stream or order
-//    them with events.
+//  * All calls share the one array, which keeps what the last call left in it.  The partial results
+//    need no clearing (each call writes every one it later reads); the small arrival counters
+//    behind them must be zero when a call starts, which holds because the array starts as zeros
+//    and every call sets its counters back before it ends.  Two calls that overlap on the GPU, on
+//    different streams, race on the array: keep them on one stream or order them with events.
 //
 // Arguments are those of idm_attention_decode without `scratch`:
 //   q [n_seqs, n_q, hd] and out [n_seqs, n_q * hd] in the library's storage type; the cache entry's

@@ -16,19 +16,27 @@ __device__ __forceinline__ void better(float& bs, int& bi, float s, int i) {
     if (s > bs || (s == bs && i < bi)) { bs = s; bi = i; }
 }
 
-__global__ void sample_kernel(const float* __restrict__ logits, int V, float temperature,
-                              const long long* __restrict__ keys, int* __restrict__ out) {
+#define SP_SLICE 4096       // vocabulary entries per block
+#define SP_THREADS 256
+
+// grid (slices, rows).  Each block finds the best entry of its slice; the block that arrives last for
+// a row (a counter in scratch, set back to zero) picks the best of the slices.
+__global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restrict__ logits, int V, float temperature,
+                                                            const long long* __restrict__ keys, int* __restrict__ out,
+                                                            float* part_s, int* part_i, int* counters) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float ss[32];
-    __shared__ int si[32];
-    const int row = blockIdx.x;
+    __shared__ float ss[SP_THREADS / 32];
+    __shared__ int si[SP_THREADS / 32];
+    __shared__ int is_last;
+    const int row = blockIdx.y, slice = blockIdx.x, n_slices = gridDim.x;
     const float* lg = logits + (size_t)row * V;
     const unsigned long long key = keys ? (unsigned long long)keys[row] : 0ull;
     const float inv_t = temperature > 0.f ? 1.0f / temperature : 1.0f;
     float bs = -INFINITY;
     int bi = 0x7fffffff;
-    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+    const int end = min(V, (slice + 1) * SP_SLICE);
+    for (int v = slice * SP_SLICE + threadIdx.x; v < end; v += SP_THREADS) {
         float s = lg[v];
         if (s != s) s = -INFINITY;                      // a NaN never wins
         if (temperature > 0.f) {
@@ -47,17 +55,48 @@ __global__ void sample_kernel(const float* __restrict__ logits, int V, float tem
     if ((threadIdx.x & 31) == 0) { ss[threadIdx.x >> 5] = bs; si[threadIdx.x >> 5] = bi; }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) better(bs, bi, ss[w], si[w]);
-        out[row] = bi == 0x7fffffff ? 0 : bi;
+        for (int w = 1; w < SP_THREADS / 32; ++w) better(bs, bi, ss[w], si[w]);
+        part_s[(size_t)row * n_slices + slice] = bs;
+        part_i[(size_t)row * n_slices + slice] = bi;
+        __threadfence();
+        const int prev = atomicAdd(&counters[row], 1);
+        is_last = prev == n_slices - 1;
+        if (is_last) counters[row] = 0;
+    }
+    __syncthreads();
+    if (is_last && threadIdx.x < 32) {
+        __threadfence();
+        bs = -INFINITY; bi = 0x7fffffff;
+        for (int c = threadIdx.x; c < n_slices; c += 32)
+            better(bs, bi, __ldcg(part_s + (size_t)row * n_slices + c), __ldcg(part_i + (size_t)row * n_slices + c));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            better(bs, bi, os, oi);
+        }
+        if (threadIdx.x == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
     }
 }
 
+// 32-bit words of scratch: best score and index per (row, slice), one counter per row (zero between launches)
+extern "C" long long idm_sample_scratch_floats(int n_rows, int V) {
+    const long long n_slices = (V + SP_SLICE - 1) / SP_SLICE;
+    return 65536 + 2 * n_rows * n_slices;      // counters first, at a fixed place
+}
+
 extern "C" int idm_sample(const float* logits, int n_rows, int V, float temperature, const long long* keys,
-                          int* out, cudaStream_t stream) {
+                          int* out, float* scratch, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     IDM_REQUIRE(V > 0, "sample: empty vocabulary");
+    IDM_REQUIRE(n_rows <= 65535, "sample: %d rows in one launch", n_rows);
     IDM_REQUIRE(!(temperature > 0.f) || keys != nullptr, "sample: temperature > 0 needs row keys");
-    idm_launch(sample_kernel, dim3(n_rows), dim3(1024), 0, stream, logits, V, temperature, keys, out);
+    const int n_slices = (V + SP_SLICE - 1) / SP_SLICE;
+    int* counters = (int*)scratch;
+    float* part_s = scratch + 65536;
+    int* part_i = (int*)(part_s + (size_t)n_rows * n_slices);
+    idm_launch(sample_kernel, dim3(n_slices, n_rows), dim3(SP_THREADS), 0, stream, logits, V, temperature, keys, out,
+               part_s, part_i, counters);
     IDM_LAUNCH_CHECK("sample");
     return 0;
 }

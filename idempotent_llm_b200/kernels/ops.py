@@ -56,6 +56,7 @@ class Kernels:
                      "idm_attention_decode_supports", "idm_decode_advance"):
             getattr(L, name).restype = c_int
         L.idm_attention_decode_scratch_floats.restype = c_longlong
+        L.idm_sample_scratch_floats.restype = c_longlong
         if dtype == torch.float32:
             L.idm_gemm_f32.restype = c_int
         else:
@@ -89,7 +90,8 @@ class Kernels:
         if buf is None or buf.numel() < n_floats:
             # a captured graph may still point at the old buffer: it is kept, never freed
             self._retired.append(buf)
-            buf = self._scratch[key] = torch.empty(max(n_floats, 1), dtype=torch.float32, device=self.device)
+            # zeros: kernels keep arrival counters in their scratch and leave them at zero
+            buf = self._scratch[key] = torch.zeros(max(n_floats, 1), dtype=torch.float32, device=self.device)
         return buf
 
     # ------------------------------------------------------------------ kernels
@@ -251,7 +253,7 @@ class Kernels:
             c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_void_p(_p(kv.table)),
             c_int(kv.table.shape[1]), c_int(kv.ring), c_void_p(_p(slots)), c_void_p(_p(kv_len)),
             c_void_p(_p(scratch)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads), c_int(hd), c_int(max_kv_len),
-            c_float(scale), c_int(window), self._stream()), 2)
+            c_float(scale), c_int(window), self._stream()))
         return out
 
     def swiglu(self, gu: torch.Tensor) -> torch.Tensor:
@@ -306,8 +308,9 @@ class Kernels:
             if keys.numel() != B:
                 raise KernelError("one key per row")
         out = torch.empty((B,), dtype=torch.int32, device=self.device)
+        scratch = self.scratch("sample", self.lib.idm_sample_scratch_floats(c_int(B), c_int(V)))
         self._check(self.lib.idm_sample(c_void_p(_p(logits)), c_int(B), c_int(V), c_float(temperature),
-                                        c_void_p(_p(keys)), c_void_p(_p(out)), self._stream()))
+                                        c_void_p(_p(keys)), c_void_p(_p(out)), c_void_p(_p(scratch)), self._stream()))
         return out
 
 
