@@ -18,9 +18,16 @@
 // per (batch, q-head), three passes over a capacity-wide cache).
 #include "common.cuh"
 
+#ifndef AD_CHUNK
 #define AD_CHUNK 256
-#define AD_WARPS 4
-#define AD_ITERS 8            // warp-wide loads in flight per group
+#endif
+#define AD_WARPS (AD_CHUNK / 64)   // one page per warp
+#ifndef AD_ITERS
+#define AD_ITERS 8            // warp-wide loads per group
+#endif
+#ifndef AD_PREFETCH
+#define AD_PREFETCH 0         // 1: the next group's loads are issued before this group's arithmetic
+#endif
 #define AD_COUNTER_SLOTS 65536  // arrival counters at the start of scratch: a fixed place, so that they are
                                 // zero at every launch whatever the sizes of earlier launches were
 
@@ -129,16 +136,32 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
         }
         if (warp_live) {
             constexpr int KEYS = IDM_PAGE;
-            for (int k0 = 0; k0 < KEYS; k0 += GROUP) {
-                if (kb + k0 >= len || kb + k0 + GROUP <= lo) continue;       // warp-uniform
-                Vec16<T> kv[AD_ITERS], vv[AD_ITERS];             // keys and values: all loads in flight together
+            constexpr int NG = (KEYS + GROUP - 1) / GROUP;          // groups per page
+            // Two register buffers: the next group's keys and values are on their way while this
+            // group is worked on.  Every row of a live page is readable memory (rows past the
+            // length hold stale data and are masked below).
+            Vec16<T> kbuf[AD_PREFETCH + 1][AD_ITERS], vbuf[AD_PREFETCH + 1][AD_ITERS];
+            auto fetch = [&](int grp, int buf) {
 #pragma unroll
                 for (int it = 0; it < AD_ITERS; ++it) {
-                    const int r = k0 + it * RPI + sub;
+                    const int r = grp * GROUP + it * RPI + sub;
                     if (r < KEYS) {
-                        kv[it].load(kpage + (size_t)r * HD + li * VEC);
-                        vv[it].load(vpage + (size_t)r * HD + li * VEC);
+                        kbuf[buf][it].load(kpage + (size_t)r * HD + li * VEC);
+                        vbuf[buf][it].load(vpage + (size_t)r * HD + li * VEC);
                     }
+                }
+            };
+            if (AD_PREFETCH) fetch(0, 0);
+#pragma unroll
+            for (int grp = 0; grp < NG; ++grp) {
+                const int cur = AD_PREFETCH ? (grp & 1) : 0;
+                const int k0 = grp * GROUP;
+                if (AD_PREFETCH) {
+                    if (grp + 1 < NG) fetch(grp + 1, cur ^ 1);
+                    if (kb + k0 >= len || kb + k0 + GROUP <= lo) continue;   // warp-uniform: no live key here
+                } else {
+                    if (kb + k0 >= len || kb + k0 + GROUP <= lo) continue;
+                    fetch(grp, 0);
                 }
                 float sc[AD_ITERS][GT];
 #pragma unroll
@@ -151,7 +174,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
                         float d = 0.f;
                         if (r < KEYS) {
 #pragma unroll
-                            for (int e = 0; e < VEC; ++e) d = fmaf(q[h][e], kv[it].get(e), d);
+                            for (int e = 0; e < VEC; ++e) d = fmaf(q[h][e], kbuf[cur][it].get(e), d);
                         }
 #pragma unroll
                         for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
@@ -177,7 +200,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
                         ps += p;
                         if (p != 0.f) {
 #pragma unroll
-                            for (int e = 0; e < VEC; ++e) acc[h][e] = fmaf(p, vv[it].get(e), acc[h][e]);
+                            for (int e = 0; e < VEC; ++e) acc[h][e] = fmaf(p, vbuf[cur][it].get(e), acc[h][e]);
                         }
                     }
                     l[h] = l[h] * alpha + ps;
@@ -253,6 +276,8 @@ extern "C" int idm_attention_decode_supports(int hd) {
     constexpr int VEC = Vec16<T>::N;
     return hd == VEC * 2 || hd == VEC * 4 || hd == VEC * 8 || hd == VEC * 16 || (hd == VEC * 32 && hd <= 256);
 }
+
+extern "C" int idm_attention_decode_chunk() { return AD_CHUNK; }
 
 // floats of scratch for the partials: part_o then part_ml
 extern "C" long long idm_attention_decode_scratch_floats(int n_seqs, int n_q, int n_chunks, int hd) {

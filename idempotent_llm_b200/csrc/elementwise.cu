@@ -2,6 +2,7 @@
 // write, ring write, SwiGLU.  Memory-bound kernels; everything that follows a
 // matrix product reads its 32-bit partial sums and adds them in ascending order.
 #include "common.cuh"
+#include "qkv_finish.cuh"
 
 // ------------------------------------------------------------------ embedding
 // h[t, :] = table[tokens[t], :]  (a pure lookup, no scaling: src/detllm/model.py:246-249)
@@ -144,16 +145,6 @@ extern "C" int idm_rope_table(const int* positions, const double* inv_freq, floa
 // by the token's position (src/detllm/ops/rope.py:47-55); v heads are copied.
 // q goes to q_out [N, n_q, hd]; k and v go to the cache at the token's position
 // and/or to packed buffers k_new, v_new [N, n_kv, hd].
-struct QkvArgs {
-    const float* qkv; int n_partials; size_t partial_stride;
-    int n_tokens, n_q, n_kv, hd;
-    const float* gq; const float* gk; float eps;
-    const float2* cs;
-    T* q_out; T* k_new; T* v_new;
-    KVAddr cache; int write_cache;
-    const int* token_seq; const int* positions; const int* slots;
-};
-
 __global__ void qkv_finish_kernel(QkvArgs a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -161,57 +152,10 @@ __global__ void qkv_finish_kernel(QkvArgs a) {
     const int heads = a.n_q + 2 * a.n_kv;
     if (warp >= a.n_tokens * heads) return;
     const int t = warp / heads, head = warp % heads;
-    const int half = a.hd >> 1;
     const size_t row = (size_t)t * heads * a.hd + (size_t)head * a.hd;
-    constexpr int MAXP = IDM_MAX_HEAD_DIM / 64;   // pairs per lane
-    float x1[MAXP], x2[MAXP];
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < MAXP; ++i) {
-        const int j = lane + 32 * i;
-        x1[i] = x2[i] = 0.f;
-        if (j < half) {
-            x1[i] = add_partials(0.f, a.qkv, a.n_partials, a.partial_stride, row + j);
-            x2[i] = add_partials(0.f, a.qkv, a.n_partials, a.partial_stride, row + j + half);
-            ss += x1[i] * x1[i] + x2[i] * x2[i];
-        }
-    }
-    const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
-    T* dst_a = nullptr; T* dst_b = nullptr;
-    if (is_q) {
-        dst_a = a.q_out + ((size_t)t * a.n_q + head) * a.hd;
-    } else {
-        const int g = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
-        if (a.write_cache) {
-            const size_t off = kv_offset(a.cache, a.slots[a.token_seq[t]], a.positions[t], g);
-            dst_a = (is_k ? a.cache.k : a.cache.v) + off;
-        }
-        T* packed = is_k ? a.k_new : a.v_new;
-        if (packed) dst_b = packed + ((size_t)t * a.n_kv + g) * a.hd;
-    }
-    const float* gamma = is_q ? a.gq : (is_k ? a.gk : nullptr);
-    float inv = 1.f;
-    if (gamma) {
-        ss = warp_sum(ss);
-        inv = 1.0f / sqrtf(ss / (float)a.hd + a.eps);
-    }
-    const bool rotate = (is_q || is_k) && a.cs != nullptr;
-#pragma unroll
-    for (int i = 0; i < MAXP; ++i) {
-        const int j = lane + 32 * i;
-        if (j < half) {
-            float u = x1[i], w = x2[i];
-            if (gamma) { u = u * inv * gamma[j]; w = w * inv * gamma[j + half]; }
-            if (rotate) {
-                const float2 c = a.cs[(size_t)t * half + j];
-                const float ru = u * c.x - w * c.y;
-                const float rw = w * c.x + u * c.y;
-                u = ru; w = rw;
-            }
-            if (dst_a) { from_f32(dst_a[j], u); from_f32(dst_a[j + half], w); }
-            if (dst_b) { from_f32(dst_b[j], u); from_f32(dst_b[j + half], w); }
-        }
-    }
+    qkv_finish_row(a, t, head, lane,
+                   [&](int j) { return add_partials(0.f, a.qkv, a.n_partials, a.partial_stride, row + j); },
+                   QkvLocateFromTables{a, t});
 }
 
 extern "C" int idm_qkv_finish(const float* qkv, int n_partials, long long partial_stride, int n_tokens,
@@ -272,28 +216,37 @@ extern "C" int idm_kv_write_ring(const void* k_new, const void* v_new, void* k_p
 }
 
 // ---------------------------------------------------------------------- SwiGLU
-// y[t, i] = g * sigmoid(g) * u with g = gu[t, i], u = gu[t, inter + i]
-// (src/detllm/ops/di_swiglu.py:43-45; float form tests/test_ops.py:240-242).
-__global__ void swiglu_kernel(const float* __restrict__ gu, int n_partials, size_t partial_stride,
-                              T* __restrict__ y, int inter, size_t total) {
+// y[t, i] = g * sigmoid(g) * u  (src/detllm/ops/di_swiglu.py:43-45; float form tests/test_ops.py:240-242).
+// Plain layout: g = gu[t, i], u = gu[t, inter + i].  Tiled layout (the gate/up weight's rows in tiles
+// of 64 gate + 64 up rows): g = gu[t, 128 (i / 64) + i % 64], u = 64 further.
+// grid (column blocks, tokens): no division by a runtime size per element.
+__global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ gu, int n_partials, size_t partial_stride,
+                                                     T* __restrict__ y, int inter, int width, int tiled) {
     pdl_launch_dependents();
     pdl_wait();
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= total) return;
-    const size_t t = i / inter, c = i % inter;
-    const size_t base = t * 2 * (size_t)inter + c;
-    const float g = add_partials(0.f, gu, n_partials, partial_stride, base);
-    const float u = add_partials(0.f, gu, n_partials, partial_stride, base + inter);
-    from_f32(y[i], g / (1.0f + expf(-g)) * u);
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= inter) return;
+    const size_t t = blockIdx.y;
+    const int gi = tiled ? ((c >> 6) << 7) + (c & 63) : c;
+    const int ui = tiled ? gi + 64 : c + inter;
+    const size_t base = t * (size_t)width;
+    const float g = add_partials(0.f, gu, n_partials, partial_stride, base + gi);
+    const float u = add_partials(0.f, gu, n_partials, partial_stride, base + ui);
+    from_f32(y[t * (size_t)inter + c], g / (1.0f + expf(-g)) * u);
 }
 
 extern "C" int idm_swiglu(const float* gu, int n_partials, long long partial_stride, void* y, int n_tokens,
-                          int inter, cudaStream_t stream) {
+                          int inter, int tiled, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     IDM_REQUIRE(inter > 0 && n_partials >= 1, "swiglu: bad sizes");
-    const size_t total = (size_t)n_tokens * inter;
-    idm_launch(swiglu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, gu, n_partials, (size_t)partial_stride,
-                                                                      (T*)y, inter, total);
-    IDM_LAUNCH_CHECK("swiglu");
+    IDM_REQUIRE(n_tokens <= 65535 * 64, "swiglu: %d tokens in one launch", n_tokens);
+    const int width = tiled ? ((inter + 63) / 64) * 128 : 2 * inter;
+    for (int t0 = 0; t0 < n_tokens; t0 += 65535) {
+        const int nt = n_tokens - t0 < 65535 ? n_tokens - t0 : 65535;
+        idm_launch(swiglu_kernel, dim3((inter + 255) / 256, nt), dim3(256), 0, stream,
+                   gu + (size_t)t0 * width, n_partials, (size_t)partial_stride, (T*)y + (size_t)t0 * inter, inter, width,
+                   tiled);
+        IDM_LAUNCH_CHECK("swiglu");
+    }
     return 0;
 }

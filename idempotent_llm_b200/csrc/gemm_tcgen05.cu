@@ -17,6 +17,15 @@
 // ascending p).  How K is split depends on the layer's shape only, and an output element's value
 // depends on its own row of x and row of w only.
 //
+// Epilogues.  PARTIAL stores each K-slice's 32-bit tile to out[p].  The fused epilogues produce the
+// finished result inside the kernel: STORE (32-bit [M, N]), RESIDUAL (h[t, f] += result, the
+// 32-bit residual sum), SWIGLU (bfloat16 y = silu(gate) * up; the weight's rows are tiled so that
+// a 128-row tile holds 64 gate rows followed by the 64 up rows of the same features) and QKV (per-head
+// q/k norm, rotation, q out and cache write; a tile of 128 features must hold whole heads).  With K
+// split, every slice writes its tile to a workspace and the block that arrives last for the tile
+// (a counter it sets back to zero) adds the slices in ascending order and runs the epilogue, so the
+// value does not depend on which block that is.
+//
 // Every wait on an mbarrier is bounded by a cycle count; a wait that runs out sets the error flag
 // (idm_gemm_status), all roles leave their loops, tensor memory is freed and the block returns.
 #include "common.cuh"
@@ -24,13 +33,27 @@
 #if defined(IDM_BF16)
 
 #include "tcgen05.cuh"
+#include "qkv_finish.cuh"
 
 #define GT_BM 128            // features per tile (MMA M)
 #define GT_BK 64             // k per stage: 64 bf16 = 128 bytes = one swizzle row
 #define GT_UMMA_K 16
 #define GT_THREADS 192
+#define GT_COUNTER_SLOTS 65536
 
 __device__ int g_gemm_error = 0;
+
+enum { EPI_PARTIAL = 0, EPI_STORE = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
+
+struct GemmEpi {
+    float* out;          // PARTIAL: [splits, M, N]; STORE: [M, N]; RESIDUAL: the residual stream [M, N]
+    float* ws;           // workspace [splits, M, N] of the fused epilogues when K is split
+    int* counters;       // one per output tile, zero between launches
+    T* y; int inter;     // SWIGLU: y [M, inter]
+    QkvArgs q;           // QKV
+};
+
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // warps 0-3
 
 // ---------------------------------------------------------------------------- kernel
 template <int BN, int STAGES>
@@ -38,14 +61,14 @@ struct GemmSmem {
     static constexpr int A_BYTES = GT_BM * GT_BK * 2;
     static constexpr int B_BYTES = BN * GT_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int BARRIER_BYTES = 1024;
+    static constexpr int BARRIER_BYTES = 2048;          // barriers and flags, then per-token cache rows (QKV)
     static constexpr int TOTAL = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;   // + slack to align to 1024
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                   const __grid_constant__ CUtensorMap map_x,
-                                                                  float* __restrict__ out, int n_tokens,
+                                                                  const GemmEpi e, int n_tokens,
                                                                   int n_features, int kb_total, int kb_per_split) {
     using S = GemmSmem<BN, STAGES>;
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;          // allocation: a power of two >= 32
@@ -125,21 +148,182 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 0-3)
+        if (EPI == EPI_QKV) {
+            // while the main loop runs: where each token's key/value row lies in the cache
+            pdl_wait();
+            int* meta = (int*)(gen_base + STAGES * S::STAGE_BYTES + 1024);
+            const int tl = warp * 32 + lane;
+            if (tl < BN && t0 + tl < n_tokens && e.q.write_cache) {
+                const int t = t0 + tl;
+                const int pos = e.q.positions[t];
+                const int r = e.q.cache.ring ? pos % e.q.cache.ring : pos;
+                meta[2 * tl] = e.q.cache.table[(size_t)e.q.slots[e.q.token_seq[t]] * e.q.cache.table_stride + r / IDM_PAGE];
+                meta[2 * tl + 1] = r % IDM_PAGE;
+            }
+        }
         if (mbar_wait(accum_bar, 0, abort_flag, &g_gemm_error)) {
             tc_fence_after();
             pdl_wait();                                           // (already satisfied: the activations came after it)
-            const int f = f0 + warp * 32 + lane;                  // this thread's feature (accumulator lane)
-            float* dst = out + (size_t)blockIdx.z * n_tokens * n_features;
+            const int fl = warp * 32 + lane;                      // feature within the tile = accumulator lane
+            const int f = f0 + fl;
+            const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+            const size_t mn = (size_t)n_tokens * n_features;
+            const int splits = gridDim.z;
+            if (EPI == EPI_PARTIAL) {
+                float* dst = e.out + blockIdx.z * mn;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (t0 + c0 >= n_tokens) break;                   // warp-uniform
-                float v[16];
-                tc_ld16(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
-                if (f < n_features) {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (t0 + c0 >= n_tokens) break;               // warp-uniform
+                    float v[16];
+                    tc_ld16(tmem_d + lane_base + (uint32_t)c0, v);
+                    if (f < n_features) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = t0 + c0 + j;
-                        if (t < n_tokens) dst[(size_t)t * n_features + f] = v[j];
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + c0 + j;
+                            if (t < n_tokens) dst[(size_t)t * n_features + f] = v[j];
+                        }
+                    }
+                }
+            } else {
+                float* xs = (float*)gen_base;                     // [BN][128] tile; the pipeline's stages are free now
+                const int cols = min(BN, n_tokens - t0);
+                bool last = true;
+                if (splits > 1) {
+                    float* dst = e.ws + blockIdx.z * mn;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        if (t0 + c0 >= n_tokens) break;
+                        float v[16];
+                        tc_ld16(tmem_d + lane_base + (uint32_t)c0, v);
+                        if (f < n_features) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int t = t0 + c0 + j;
+                                if (t < n_tokens) dst[(size_t)t * n_features + f] = v[j];
+                            }
+                        }
+                    }
+                    __threadfence();
+                    epi_sync();
+                    volatile int* flag = (volatile int*)(tmem_slot + 2);
+                    if (threadIdx.x == 0) {
+                        int* ctr = e.counters + blockIdx.y * gridDim.x + blockIdx.x;
+                        const int prev = atomicAdd(ctr, 1);
+                        *flag = prev == splits - 1;
+                        if (prev == splits - 1) *ctr = 0;
+                    }
+                    epi_sync();
+                    last = *flag != 0;
+                    if (last) {
+                        // Add the slices' tiles in ascending order into the shared-memory tile.  A warp
+                        // takes whole token rows; eight slices' loads are in flight together.
+                        __threadfence();
+                        if ((n_features & 3) == 0) {
+                            const int f4 = f0 + lane * 4;
+                            for (int t = warp; t < cols; t += 4) {
+                                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (f4 < n_features) {
+                                    const float* src = e.ws + (size_t)(t0 + t) * n_features + f4;
+                                    for (int z0 = 0; z0 < splits; z0 += 8) {
+                                        float4 part[8];
+#pragma unroll
+                                        for (int i = 0; i < 8; ++i)
+                                            if (z0 + i < splits) part[i] = __ldcg(reinterpret_cast<const float4*>(src + (z0 + i) * mn));
+#pragma unroll
+                                        for (int i = 0; i < 8; ++i)
+                                            if (z0 + i < splits) {
+                                                acc.x += part[i].x; acc.y += part[i].y; acc.z += part[i].z; acc.w += part[i].w;
+                                            }
+                                    }
+                                }
+                                *reinterpret_cast<float4*>(xs + t * GT_BM + lane * 4) = acc;
+                            }
+                        } else {
+                            for (int t = warp; t < cols; t += 4)
+                                for (int i = lane; i < GT_BM; i += 32) {
+                                    float acc = 0.f;
+                                    if (f0 + i < n_features)
+                                        acc = add_partials(0.f, e.ws, splits, mn, (size_t)(t0 + t) * n_features + f0 + i);
+                                    xs[t * GT_BM + i] = acc;
+                                }
+                        }
+                        epi_sync();
+                    }
+                } else if (EPI == EPI_SWIGLU || EPI == EPI_QKV) {
+                    // the tile from tensor memory into shared memory: these epilogues work across lanes
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        if (t0 + c0 >= n_tokens) break;
+                        float v[16];
+                        tc_ld16(tmem_d + lane_base + (uint32_t)c0, v);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) xs[(c0 + j) * GT_BM + fl] = v[j];
+                    }
+                    epi_sync();
+                }
+                if (last) {
+                    if (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+                        if (splits > 1) {
+                            if (f < n_features)
+                                for (int c0 = 0; c0 < cols; c0 += 16) {            // 16 tokens' loads go out together
+                                    float old[16];
+#pragma unroll
+                                    for (int j = 0; j < 16; ++j)
+                                        old[j] = (EPI == EPI_RESIDUAL && c0 + j < cols)
+                                                     ? e.out[(size_t)(t0 + c0 + j) * n_features + f] : 0.f;
+#pragma unroll
+                                    for (int j = 0; j < 16; ++j)
+                                        if (c0 + j < cols)
+                                            e.out[(size_t)(t0 + c0 + j) * n_features + f] = old[j] + xs[(c0 + j) * GT_BM + fl];
+                                }
+                        } else {
+#pragma unroll 1
+                            for (int c0 = 0; c0 < BN; c0 += 32) {     // 32 tokens at a time: their loads go out together
+                                if (t0 + c0 >= n_tokens) break;
+                                float v[32], old[32];
+                                tc_ld16(tmem_d + lane_base + (uint32_t)c0, v);
+                                if (BN > 16) tc_ld16(tmem_d + lane_base + (uint32_t)c0 + 16, v + 16);
+                                if (f < n_features) {
+                                    if (EPI == EPI_RESIDUAL) {
+#pragma unroll
+                                        for (int j = 0; j < (BN > 16 ? 32 : 16); ++j) {
+                                            const int t = t0 + c0 + j;
+                                            old[j] = t < n_tokens ? e.out[(size_t)t * n_features + f] : 0.f;
+                                        }
+                                    }
+#pragma unroll
+                                    for (int j = 0; j < (BN > 16 ? 32 : 16); ++j) {
+                                        const int t = t0 + c0 + j;
+                                        if (t < n_tokens)
+                                            e.out[(size_t)t * n_features + f] = EPI == EPI_RESIDUAL ? old[j] + v[j] : v[j];
+                                    }
+                                }
+                            }
+                        }
+                    } else if (EPI == EPI_SWIGLU) {
+                        // lanes 64..127 of the tile hold the up rows of the features whose gate rows lanes 0..63 hold
+                        const int fg = blockIdx.x * 64 + (fl & 63);                // the feature of y
+                        if (fg < e.inter)
+                            for (int t = fl >> 6; t < cols; t += 2) {                  // two token rows at a time
+                                const float g = xs[t * GT_BM + (fl & 63)], u = xs[t * GT_BM + 64 + (fl & 63)];
+                                from_f32(e.y[(size_t)(t0 + t) * e.inter + fg], g / (1.0f + expf(-g)) * u);
+                            }
+                    } else if (EPI == EPI_QKV) {
+                        const int hpt = GT_BM / e.q.hd;           // heads per tile
+                        const int heads = e.q.n_q + 2 * e.q.n_kv;
+                        const int* meta = (const int*)(gen_base + STAGES * S::STAGE_BYTES + 1024);   // [BN][2]: page, row
+                        for (int row = warp; row < cols * hpt; row += 4) {
+                            const int c = row / hpt, hh = row % hpt;
+                            const int head = f0 / e.q.hd + hh;
+                            if (head < heads) {
+                                const float* src = xs + c * GT_BM + hh * e.q.hd;
+                                const int page = meta[2 * c], prow = meta[2 * c + 1];
+                                qkv_finish_row(e.q, t0 + c, head, lane, [&](int j) { return src[j]; },
+                                               [&](int g) {
+                                                   return (((size_t)page * e.q.n_kv + g) * IDM_PAGE + prow) * (size_t)e.q.hd;
+                                               });
+                            }
+                        }
                     }
                 }
             }
@@ -163,20 +347,24 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int k, int box_
     return 0;
 }
 
-template <int BN, int STAGES>
-static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, float* out, int M, int N, int kb_total,
+template <int BN, int STAGES, int EPI>
+static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
                        int kb_per_split, int splits, cudaStream_t stream) {
     using S = GemmSmem<BN, STAGES>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-        IDM_REQUIRE(e == cudaSuccess, "gemm: cannot get %d bytes of shared memory: %s", S::TOTAL, cudaGetErrorString(e));
+        cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        IDM_REQUIRE(err == cudaSuccess, "gemm: cannot get %d bytes of shared memory: %s", S::TOTAL,
+                    cudaGetErrorString(err));
         configured = true;
     }
     dim3 grid((N + GT_BM - 1) / GT_BM, (M + BN - 1) / BN, splits);
     IDM_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm: too many tiles (%u x %u)", grid.y, grid.z);
-    idm_launch(gemm_tcgen05_kernel<BN, STAGES>, dim3(grid), dim3(GT_THREADS), S::TOTAL, stream, mw, mx, out, M, N, kb_total, kb_per_split);
+    IDM_REQUIRE(EPI == EPI_PARTIAL || splits == 1 || (long long)grid.x * grid.y <= GT_COUNTER_SLOTS,
+                "gemm: %u x %u tiles exceed the %d counters", grid.x, grid.y, GT_COUNTER_SLOTS);
+    idm_launch(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(GT_THREADS), S::TOTAL, stream, mw, mx, e, M, N,
+               kb_total, kb_per_split);
     IDM_LAUNCH_CHECK("gemm_tcgen05");
     return 0;
 }
@@ -195,8 +383,15 @@ extern "C" int idm_gemm_bf16_splits(int M, int N, int K) {
     return (kb_total + per - 1) / per;
 }
 
-extern "C" int idm_gemm_bf16(const void* x, const void* w, float* out, int M, int N, int K, int splits,
-                             cudaStream_t stream) {
+// 32-bit words of workspace for a fused epilogue: the counters (a fixed place at the start, so that
+// they are zero at every launch), then the slices' tiles
+extern "C" long long idm_gemm_bf16_workspace_floats(int M, int N, int splits) {
+    return (long long)GT_COUNTER_SLOTS + (splits > 1 ? (long long)splits * M * N : 0);
+}
+
+template <int EPI>
+static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, int M, int N, int K, int splits,
+                    cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     IDM_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
     IDM_REQUIRE(K % 8 == 0, "gemm: the inner size %d must be a multiple of 8 (rows start on 16-byte borders)", K);
@@ -205,16 +400,74 @@ extern "C" int idm_gemm_bf16(const void* x, const void* w, float* out, int M, in
     IDM_REQUIRE(splits >= 1 && splits <= kb_total, "gemm: %d splits for %d k-blocks", splits, kb_total);
     const int per = (kb_total + splits - 1) / splits;
     IDM_REQUIRE((kb_total + per - 1) / per == splits, "gemm: %d splits leave one empty", splits);
+    if (EPI != EPI_PARTIAL) {
+        IDM_REQUIRE(splits == 1 || workspace != nullptr, "gemm: a split product with a fused epilogue needs a workspace");
+        e.counters = (int*)workspace;
+        e.ws = workspace ? workspace + GT_COUNTER_SLOTS : nullptr;
+    }
     CUtensorMap mw, mx;
     const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     if (make_map(&mw, w, N, K, GT_BM)) return 1;
     if (make_map(&mx, x, M, K, bn)) return 1;
     switch (bn) {
-        case 16: return launch_gemm<16, 6>(mw, mx, out, M, N, kb_total, per, splits, stream);
-        case 32: return launch_gemm<32, 6>(mw, mx, out, M, N, kb_total, per, splits, stream);
-        case 64: return launch_gemm<64, 4>(mw, mx, out, M, N, kb_total, per, splits, stream);
-        default: return launch_gemm<128, 3>(mw, mx, out, M, N, kb_total, per, splits, stream);
+        case 16: return launch_gemm<16, 6, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
+        case 32: return launch_gemm<32, 6, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
+        case 64: return launch_gemm<64, 4, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
+        default: return launch_gemm<128, 3, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
     }
+}
+
+// out [splits, M, N]: the slices' partial sums
+extern "C" int idm_gemm_bf16(const void* x, const void* w, float* out, int M, int N, int K, int splits,
+                             cudaStream_t stream) {
+    GemmEpi e = {};
+    e.out = out;
+    return gemm_any<EPI_PARTIAL>(x, w, e, nullptr, M, N, K, splits, stream);
+}
+
+// out [M, N] = x . w^T (finished, 32-bit)
+extern "C" int idm_gemm_bf16_store(const void* x, const void* w, float* out, float* workspace, int M, int N, int K,
+                                   int splits, cudaStream_t stream) {
+    GemmEpi e = {};
+    e.out = out;
+    return gemm_any<EPI_STORE>(x, w, e, workspace, M, N, K, splits, stream);
+}
+
+// h [M, N] += x . w^T (the 32-bit residual sum)
+extern "C" int idm_gemm_bf16_residual(const void* x, const void* w, float* h, float* workspace, int M, int N, int K,
+                                      int splits, cudaStream_t stream) {
+    GemmEpi e = {};
+    e.out = h;
+    return gemm_any<EPI_RESIDUAL>(x, w, e, workspace, M, N, K, splits, stream);
+}
+
+// y [M, inter] = silu(x . gate^T) * (x . up^T); w_tiled [tiles * 128, K]: tile j = gate rows 64j..64j+63,
+// then up rows 64j..64j+63 (rows past `inter` are zero)
+extern "C" int idm_gemm_bf16_swiglu(const void* x, const void* w_tiled, void* y, float* workspace, int M, int inter,
+                                    int K, int splits, cudaStream_t stream) {
+    GemmEpi e = {};
+    e.y = (T*)y; e.inter = inter;
+    const int tiles = (inter + 63) / 64;
+    return gemm_any<EPI_SWIGLU>(x, w_tiled, e, workspace, M, tiles * GT_BM, K, splits, stream);
+}
+
+// The fused q/k/v projection with the per-head finish (see qkv_finish.cuh); 128 % head_dim must be 0
+extern "C" int idm_gemm_bf16_qkv(const void* x, const void* w, float* workspace, int M, int K, int splits, int n_q,
+                                 int n_kv, int hd, const float* gq, const float* gk, float eps, const float* cs,
+                                 void* q_out, void* k_new, void* v_new, void* k_pool, void* v_pool, const int* table,
+                                 int table_stride, int ring, const int* token_seq, const int* positions,
+                                 const int* slots, cudaStream_t stream) {
+    IDM_REQUIRE(hd > 0 && GT_BM % hd == 0 && hd % 2 == 0, "gemm_qkv: head_dim=%d must divide %d", hd, GT_BM);
+    GemmEpi e = {};
+    QkvArgs& a = e.q;
+    a.qkv = nullptr; a.n_partials = 0; a.partial_stride = 0;
+    a.n_tokens = M; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd;
+    a.gq = gq; a.gk = gk; a.eps = eps; a.cs = (const float2*)cs;
+    a.q_out = (T*)q_out; a.k_new = (T*)k_new; a.v_new = (T*)v_new;
+    a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
+    a.write_cache = k_pool != nullptr;
+    a.token_seq = token_seq; a.positions = positions; a.slots = slots;
+    return gemm_any<EPI_QKV>(x, w, e, workspace, M, (n_q + 2 * n_kv) * hd, K, splits, stream);
 }
 
 // 0, or 1 if any block's bounded wait ran out since the last call (reads the flag: synchronises)

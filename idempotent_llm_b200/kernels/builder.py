@@ -111,7 +111,7 @@ def build(dtype: str, verbose: bool = True, extra_flags: List[str] = ()) -> str:
     """Compile the library for ``dtype`` if it is not current; returns its path."""
     if dtype not in SOURCES:
         raise BuildError(f"no kernels for dtype {dtype!r}; known: {sorted(SOURCES)}")
-    extra_flags = list(extra_flags)
+    extra_flags = list(extra_flags) + os.environ.get("IDM_EXTRA_NVCC_FLAGS", "").split()
     out_dir = os.path.join(_build_root(), dtype)
     os.makedirs(out_dir, exist_ok=True)
     lib = os.path.join(out_dir, f"libidm_{dtype}.so")

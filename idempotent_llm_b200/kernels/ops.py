@@ -60,15 +60,29 @@ class Kernels:
         if dtype == torch.float32:
             L.idm_gemm_f32.restype = c_int
         else:
-            for name in ("idm_gemm_bf16", "idm_gemm_bf16_splits", "idm_gemm_status", "idm_attention_prefill",
+            for name in ("idm_gemm_bf16", "idm_gemm_bf16_splits", "idm_gemm_status", "idm_gemm_bf16_store",
+                         "idm_gemm_bf16_residual", "idm_gemm_bf16_swiglu", "idm_gemm_bf16_qkv", "idm_attention_prefill",
                          "idm_attention_prefill_supports", "idm_attention_prefill_status"):
                 getattr(L, name).restype = c_int
         # "tcgen05": the hand-written tensor-core kernel; "library": the GEMM torch wraps (kept to
         # compare against)
         self.gemm_impl = os.environ.get("IDM_GEMM", "tcgen05")
+        if dtype == torch.bfloat16:
+            L.idm_gemm_bf16_workspace_floats.restype = c_longlong
+        # fused epilogues of the tensor-core product (residual add, SwiGLU, q/k/v finish): parts use
+        # them when this is True and fall back to separate kernels otherwise
+        self.fused = (dtype == torch.bfloat16 and self.gemm_impl == "tcgen05"
+                      and os.environ.get("IDM_FUSED", "1") != "0")
+        # Below this many tokens the inner axis is split over blocks and the separate kernels, which
+        # add the slices with the whole GPU, are quicker than one block per tile doing it; from here
+        # on (no split) the fused epilogues win.  IDM_FUSED_MIN_TOKENS=0 fuses always.
+        self.fused_min_tokens = int(os.environ.get("IDM_FUSED_MIN_TOKENS", "257"))
         # "tcgen05": prompts' attention on the tensor cores; "general": the one-warp-per-query kernel
         self.prefill_impl = os.environ.get("IDM_PREFILL", "tcgen05")
         self.page = L.idm_page_tokens()
+
+    def use_fused(self, n_tokens: int) -> bool:
+        return self.fused and n_tokens >= self.fused_min_tokens
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -242,11 +256,11 @@ class Kernels:
 
     def attention_decode(self, q, kv, slots, kv_len, max_kv_len: int, scale: float, window: int,
                          out=None) -> torch.Tensor:
-        """One query per sequence against its cached keys (split over chunks of 256 keys, then merged)."""
+        """One query per sequence against its cached keys (split over chunks of keys, then merged)."""
         n, n_q, hd = q.shape
         if out is None:
             out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
-        n_chunks = -(-max_kv_len // 256)
+        n_chunks = -(-max_kv_len // self.lib.idm_attention_decode_chunk())
         need = self.lib.idm_attention_decode_scratch_floats(c_int(n), c_int(n_q), c_int(n_chunks), c_int(hd))
         scratch = self.scratch("attention_decode", need)
         self._check(self.lib.idm_attention_decode(
@@ -256,14 +270,22 @@ class Kernels:
             c_float(scale), c_int(window), self._stream()))
         return out
 
-    def swiglu(self, gu: torch.Tensor) -> torch.Tensor:
+    def swiglu(self, gu: torch.Tensor, tiled_inter: Optional[int] = None) -> torch.Tensor:
+        """``g * sigmoid(g) * u`` of the gate/up product ``[P, N, 2 * inter]`` (gate columns, then up
+        columns), or of its tiled form ``[P, N, ceil(inter / 64) * 128]`` when ``tiled_inter`` is given."""
         self._need(gu, torch.float32, "gate-up")
-        P, n, two_i = gu.shape
-        if two_i % 2:
-            raise KernelError("gate-up rows must have an even number of elements")
-        y = torch.empty((n, two_i // 2), dtype=self.dtype, device=self.device)
-        self._check(self.lib.idm_swiglu(c_void_p(_p(gu)), c_int(P), c_longlong(n * two_i), c_void_p(_p(y)),
-                                        c_int(n), c_int(two_i // 2), self._stream()))
+        P, n, width = gu.shape
+        if tiled_inter is None:
+            if width % 2:
+                raise KernelError("gate-up rows must have an even number of elements")
+            inter, tiled = width // 2, 0
+        else:
+            inter, tiled = int(tiled_inter), 1
+            if width != -(-inter // 64) * 128:
+                raise KernelError(f"tiled gate-up rows have {width} elements, expected {-(-inter // 64) * 128}")
+        y = torch.empty((n, inter), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_swiglu(c_void_p(_p(gu)), c_int(P), c_longlong(n * width), c_void_p(_p(y)),
+                                        c_int(n), c_int(inter), c_int(tiled), self._stream()))
         return y
 
     def gemm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -286,6 +308,91 @@ class Kernels:
         self._check(self.lib.idm_gemm_bf16(c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(out)), c_int(M), c_int(N),
                                            c_int(Kd), c_int(P), self._stream()))
         return out
+
+    # ---- fused epilogues (bfloat16 only) ------------------------------------------------------------
+    def _gemm_shape(self, x, w):
+        self._need(x, self.dtype, "gemm input")
+        self._need(w, self.dtype, "gemm weight")
+        M, Kd = x.shape
+        N, K2 = w.shape
+        if Kd != K2:
+            raise KernelError(f"gemm: input rows have {Kd} elements, weight rows {K2}")
+        if Kd % 8:
+            raise KernelError(f"gemm: the inner size {Kd} must be a multiple of 8 for the fused kernels")
+        P = self.lib.idm_gemm_bf16_splits(c_int(M), c_int(N), c_int(Kd))
+        ws = self.scratch("gemm_ws", self.lib.idm_gemm_bf16_workspace_floats(c_int(M), c_int(N), c_int(P)))
+        return M, N, Kd, P, ws
+
+    def gemm_store(self, x, w) -> torch.Tensor:
+        """``x . w^T`` finished in 32-bit ``[M, N]``."""
+        M, N, Kd, P, ws = self._gemm_shape(x, w)
+        out = torch.empty((M, N), dtype=torch.float32, device=self.device)
+        if M:
+            self._check(self.lib.idm_gemm_bf16_store(c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(out)),
+                                                     c_void_p(_p(ws)), c_int(M), c_int(N), c_int(Kd), c_int(P),
+                                                     self._stream()))
+        return out
+
+    def gemm_residual(self, x, w, h) -> None:
+        """``h += x . w^T`` in 32-bit, in place."""
+        M, N, Kd, P, ws = self._gemm_shape(x, w)
+        self._need(h, torch.float32, "residual stream")
+        if tuple(h.shape) != (M, N):
+            raise KernelError(f"residual stream {tuple(h.shape)} does not match the product {(M, N)}")
+        if M:
+            self._check(self.lib.idm_gemm_bf16_residual(c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(h)),
+                                                        c_void_p(_p(ws)), c_int(M), c_int(N), c_int(Kd), c_int(P),
+                                                        self._stream()))
+
+    def tile_gate_up(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        """Rows of gate and up interleaved in tiles of 64 + 64 (zero rows past the end), the layout
+        ``gemm_swiglu`` reads."""
+        inter, Kd = gate.shape
+        tiles = -(-inter // 64)
+        out = torch.zeros((tiles, 2, 64, Kd), dtype=gate.dtype, device=gate.device)
+        pad = tiles * 64 - inter
+        g = torch.nn.functional.pad(gate, (0, 0, 0, pad)) if pad else gate
+        u = torch.nn.functional.pad(up, (0, 0, 0, pad)) if pad else up
+        out[:, 0] = g.view(tiles, 64, Kd)
+        out[:, 1] = u.view(tiles, 64, Kd)
+        return out.view(tiles * 128, Kd).contiguous()
+
+    def gemm_swiglu(self, x, w_tiled, inter: int) -> torch.Tensor:
+        """``silu(x . gate^T) * (x . up^T)`` in the storage dtype ``[M, inter]``."""
+        M, N, Kd, P, ws = self._gemm_shape(x, w_tiled)
+        if N != -(-inter // 64) * 128:
+            raise KernelError(f"tiled gate/up weight has {N} rows, expected {-(-inter // 64) * 128}")
+        y = torch.empty((M, inter), dtype=self.dtype, device=self.device)
+        if M:
+            self._check(self.lib.idm_gemm_bf16_swiglu(c_void_p(_p(x)), c_void_p(_p(w_tiled)), c_void_p(_p(y)),
+                                                      c_void_p(_p(ws)), c_int(M), c_int(inter), c_int(Kd), c_int(P),
+                                                      self._stream()))
+        return y
+
+    def gemm_qkv(self, x, w, n_q, n_kv, hd, q_gamma, k_gamma, eps, cs, ctx, kv, keep_new: bool):
+        """The fused q/k/v projection with ``qkv_finish`` as its epilogue (128 % hd == 0)."""
+        M, N, Kd, P, ws = self._gemm_shape(x, w)
+        if N != (n_q + 2 * n_kv) * hd or 128 % hd:
+            raise KernelError(f"gemm_qkv: weight rows {N}, heads {(n_q, n_kv)}, head_dim {hd}")
+        if cs is not None and tuple(cs.shape) != (M, hd // 2, 2):
+            raise KernelError(f"rotary table {tuple(cs.shape)} does not match {(M, hd // 2, 2)}")
+        q = torch.empty((M, n_q, hd), dtype=self.dtype, device=self.device)
+        k_new = v_new = None
+        if keep_new and n_kv:
+            k_new = torch.empty((M, n_kv, hd), dtype=self.dtype, device=self.device)
+            v_new = torch.empty((M, n_kv, hd), dtype=self.dtype, device=self.device)
+        if kv is not None:
+            self._check_kv(kv, n_kv, hd)
+        if M:
+            self._check(self.lib.idm_gemm_bf16_qkv(
+                c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(ws)), c_int(M), c_int(Kd), c_int(P), c_int(n_q),
+                c_int(n_kv), c_int(hd), c_void_p(_p(q_gamma)), c_void_p(_p(k_gamma)), c_float(eps),
+                c_void_p(_p(cs)), c_void_p(_p(q)), c_void_p(_p(k_new)), c_void_p(_p(v_new)),
+                c_void_p(_p(kv.k) if kv is not None else None), c_void_p(_p(kv.v) if kv is not None else None),
+                c_void_p(_p(kv.table) if kv is not None else None),
+                c_int(kv.table.shape[1] if kv is not None else 0), c_int(kv.ring if kv is not None else 0),
+                c_void_p(_p(ctx.token_seq)), c_void_p(_p(ctx.positions)), c_void_p(_p(ctx.slots)), self._stream()))
+        return q, k_new, v_new
 
     def gemm_status(self) -> int:
         """0, or 1 if a bounded wait inside the tensor-core GEMM ran out since the last call (synchronises)."""

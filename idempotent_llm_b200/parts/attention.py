@@ -23,6 +23,8 @@ from .base import MIXERS, POSITIONS, Mixer
 
 @MIXERS.register("attention")
 class GQAAttention(Mixer):
+    accepts_residual = True
+
     @classmethod
     def declare(cls, spec, prefix):
         p = prefix + "self_attn."
@@ -66,22 +68,30 @@ class GQAAttention(Mixer):
         if spec.position is not None:
             self.position = POSITIONS.get(spec.position.kind)(spec.position, weights, prefix, rt)
 
-    def forward(self, x, ctx, kv, state, writes_cache: bool):
+    def forward(self, x, ctx, kv, state, writes_cache: bool, residual=None):
+        """Returns the delta ``[P, N, hidden]``, or None after adding it into ``residual`` in place."""
         s, K = self.spec, self.rt.kernels
         if writes_cache == s.kv_from_other:
             raise ValueError("a mixer with its own k/v must write its cache entry; one without must not")
-        qkv = K.gemm(x, self.w_qkv)                                   # [P, N, (n_q [+ 2 n_kv]) * hd]
         cs = self.position.tables(ctx) if self.position is not None else None
+        fused = (bool(getattr(K, "fused", False)) and K.use_fused(x.shape[0]) and s.hidden % 8 == 0
+                 and (s.n_heads * s.head_dim) % 8 == 0)
         # A windowed layer's ring cannot hold a whole prompt, so a step of several tokens reads its
         # own keys from packed buffers and writes the ring afterwards.  A single token overwrites
         # position p - ring only, which lies outside its window, so it is written first like any key.
         windowed = kv.ring > 0 and not ctx.single_token
-        q, k_new, v_new = K.qkv_finish(
-            qkv, s.n_heads, 0 if s.kv_from_other else s.n_kv_heads, s.head_dim,
-            self.q_gamma, self.k_gamma, s.qk_norm_eps, cs, ctx,
-            kv if (writes_cache and not windowed) else None,
-            keep_new=writes_cache and windowed)
+        finish = (s.n_heads, 0 if s.kv_from_other else s.n_kv_heads, s.head_dim, self.q_gamma, self.k_gamma,
+                  s.qk_norm_eps, cs, ctx, kv if (writes_cache and not windowed) else None)
+        if fused and 128 % s.head_dim == 0:
+            # norm, rotation and the cache write are the epilogue of the projection
+            q, k_new, v_new = K.gemm_qkv(x, self.w_qkv, *finish, keep_new=writes_cache and windowed)
+        else:
+            qkv = K.gemm(x, self.w_qkv)                               # [P, N, (n_q [+ 2 n_kv]) * hd]
+            q, k_new, v_new = K.qkv_finish(qkv, *finish, keep_new=writes_cache and windowed)
         o = K.attention(q, kv, ctx, k_new, v_new, s.softmax_scale, s.window)  # [N, n_q * hd]
         if writes_cache and windowed:
             K.kv_write_ring(k_new, v_new, kv, ctx)
+        if fused and residual is not None:
+            K.gemm_residual(o, self.w_o, residual)
+            return None
         return K.gemm(o, self.w_o)                                    # [P, N, hidden]

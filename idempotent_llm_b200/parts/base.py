@@ -24,6 +24,9 @@ Interfaces (duck-typed; the base classes document them):
 * ``Block.forward(h, pending, ctx, kv, state, writes_cache) -> (h, pending)``:
   ``pending`` is a delta not yet added to ``h``; the next norm adds it.
 
+A mixer or feed-forward whose class sets ``accepts_residual = True`` also takes ``residual=h``
+and may add its output into ``h`` itself (fused into its last kernel) and return None.
+
 ``delta`` is always 32-bit ``[P, N, hidden]``: P partial sums whose total is the
 part's output (P is 1 unless a matrix product was split along its inner axis);
 the consumer adds them in ascending order.

@@ -30,6 +30,11 @@ class PreNormBlock(Block):
 
     def forward(self, h, pending, ctx, kv, state, writes_cache: bool):
         x = self.mixer_norm.forward(h, pending, ctx)
-        a = self.mixer.forward(x, ctx, kv, state, writes_cache)
+        if getattr(self.mixer, "accepts_residual", False):
+            a = self.mixer.forward(x, ctx, kv, state, writes_cache, residual=h)    # None: already added
+        else:
+            a = self.mixer.forward(x, ctx, kv, state, writes_cache)
         x = self.feed_forward_norm.forward(h, a, ctx)
+        if getattr(self.feed_forward, "accepts_residual", False):
+            return h, self.feed_forward.forward(x, ctx, residual=h)
         return h, self.feed_forward.forward(x, ctx)

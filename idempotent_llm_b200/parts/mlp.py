@@ -13,6 +13,8 @@ from .base import FEED_FORWARDS, FeedForward
 
 @FEED_FORWARDS.register("gated_mlp")
 class GatedMLP(FeedForward):
+    accepts_residual = True
+
     @classmethod
     def declare(cls, spec, prefix):
         p = prefix + "mlp."
@@ -26,12 +28,25 @@ class GatedMLP(FeedForward):
         self.spec = spec
         self.rt = rt
         p = prefix + "mlp."
-        self.w_gate_up = torch.cat([weights[p + "gate_proj.weight"].to(rt.dtype),
-                                    weights[p + "up_proj.weight"].to(rt.dtype)], dim=0).contiguous()
+        gate, up = weights[p + "gate_proj.weight"].to(rt.dtype), weights[p + "up_proj.weight"].to(rt.dtype)
+        # with the fused kernels the activation is the epilogue of the gate/up product, which wants
+        # gate and up rows interleaved in tiles; otherwise the rows are simply concatenated
+        self.fused = bool(getattr(rt.kernels, "fused", False)) and spec.hidden % 8 == 0 and spec.intermediate % 8 == 0
+        if self.fused:
+            self.w_gate_up = rt.kernels.tile_gate_up(gate, up)
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = weights[p + "down_proj.weight"].to(rt.dtype).contiguous()
 
-    def forward(self, x, ctx):
+    def forward(self, x, ctx, residual=None):
+        """Returns the delta ``[P, N, hidden]``, or None after adding it into ``residual`` in place."""
         K = self.rt.kernels
-        gu = K.gemm(x, self.w_gate_up)          # [P, N, 2 * intermediate]
-        y = K.swiglu(gu)                        # [N, intermediate]
+        if self.fused and K.use_fused(x.shape[0]):
+            y = K.gemm_swiglu(x, self.w_gate_up, self.spec.intermediate)
+            if residual is not None:
+                K.gemm_residual(y, self.w_down, residual)
+                return None
+            return K.gemm(y, self.w_down)
+        gu = K.gemm(x, self.w_gate_up)          # [P, N, 2 * intermediate] (tiled rows when self.fused)
+        y = K.swiglu(gu, tiled_inter=self.spec.intermediate if self.fused else None)   # [N, intermediate]
         return K.gemm(y, self.w_down)           # [P, N, hidden]

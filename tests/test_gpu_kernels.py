@@ -115,7 +115,8 @@ def _attn_ref(q, k, v, scale, window, pos):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("n_q,n_kv,hd,window", [(8, 2, 64, None), (6, 6, 128, None), (12, 4, 32, 100),
-                                                (16, 2, 128, None), (3, 1, 256, None), (4, 2, 16, 70)])
+                                                (16, 2, 128, None), (3, 1, 256, None), (4, 2, 16, 70),
+                                                (16, 8, 128, None), (8, 2, 128, None), (4, 2, 64, 300)])
 def test_attention_decode_against_plain_and_general_kernel(kernels, dtype, n_q, n_kv, hd, window):
     K = kernels(dtype)
     if not K.lib.idm_attention_decode_supports(hd):
@@ -135,6 +136,7 @@ def test_attention_decode_against_plain_and_general_kernel(kernels, dtype, n_q, 
     ctx = context_from_packed(packed.cuda(), n, slots, q_lens, [L - 1 for L in lens], max_kv_len=1100)
     out = K.attention_decode(qd, kv, ctx.slots, ctx.kv_len, 1100, scale, window or 0).view(len(lens), n_q, hd)
     gen = K.attention_generic(qd, kv, ctx, None, None, scale, window).view(len(lens), n_q, hd)
+    torch.cuda.synchronize()
     assert torch.isfinite(out).all() and torch.isfinite(gen).all(), "a key outside the allowed range was read"
     for i, L in enumerate(lens):
         ref = _attn_ref(qd[i].double().cpu(), ks[i], vs[i], scale, window, L - 1)
@@ -320,6 +322,77 @@ def test_gemm_bfloat16(kernels, impl, M, N, K_):
                 assert torch.equal(one[:, 0], out[:, M // 2])
     finally:
         K.gemm_impl = old
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (8, 1024, 2048), (64, 1024, 3072), (200, 512, 1024), (300, 384, 136),
+                                    (2048, 1024, 1024), (5, 151936, 64)])
+def test_gemm_fused_store_and_residual(kernels, M, N, K_):
+    K = kernels("bfloat16")
+    x, w = _randn(M, K_, seed=74).bfloat16(), _randn(N, K_, seed=75).bfloat16()
+    ref = x.double() @ w.double().T
+    for _ in range(2):                                    # twice: the tile counters must be back at zero
+        out = K.gemm_store(x.cuda(), w.cuda())
+        assert out.shape == (M, N) and helpers.rel_err(out, ref) < 2e-5
+    h0 = _randn(M, N, seed=76, scale=3.0).float()
+    h = h0.clone().cuda()
+    K.gemm_residual(x.cuda(), w.cuda(), h)
+    assert helpers.rel_err(h, h0.double() + ref) < 2e-5
+    # the fused result is the partial sums added in ascending order: the same bits
+    parts = K.gemm(x.cuda(), w.cuda())
+    acc = torch.zeros_like(out)
+    for p_ in parts:
+        acc += p_
+    assert torch.equal(acc, out)
+    torch.cuda.synchronize()
+    assert K.gemm_status() == 0
+
+
+@pytest.mark.parametrize("M,inter,K_", [(1, 128, 64), (8, 3072, 1024), (7, 224, 96), (130, 136, 80), (2048, 288, 160)])
+def test_gemm_fused_swiglu(kernels, M, inter, K_):
+    K = kernels("bfloat16")
+    x = _randn(M, K_, seed=77).bfloat16()
+    gate, up = _randn(inter, K_, seed=78, scale=0.3).bfloat16(), _randn(inter, K_, seed=79, scale=0.3).bfloat16()
+    tiled = K.tile_gate_up(gate.cuda(), up.cuda())
+    assert tiled.shape == (-(-inter // 64) * 128, K_)
+    for _ in range(2):
+        y = K.gemm_swiglu(x.cuda(), tiled, inter)
+        g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+        assert y.shape == (M, inter) and helpers.rel_err(y, g * torch.sigmoid(g) * u) < KTOL["bfloat16"]
+    unfused = K.swiglu(K.gemm(x.cuda(), torch.cat([gate, up]).cuda()))
+    assert torch.equal(unfused, y), "fused and separate kernels add the same partial sums in the same order"
+    assert torch.equal(K.swiglu(K.gemm(x.cuda(), tiled), tiled_inter=inter), y), "the tiled layout read by the separate kernel"
+
+
+@pytest.mark.parametrize("M,n_q,n_kv,hd,hidden", [(3, 6, 2, 32, 96), (70, 4, 2, 16, 64), (9, 16, 8, 128, 1024),
+                                                  (300, 8, 2, 128, 160), (64, 2, 1, 64, 72)])
+def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, hidden):
+    K = kernels("bfloat16")
+    starts, lens = [5, 64], [M // 2, M - M // 2]
+    if lens[0] == 0:
+        starts, lens = [5], [M]
+
+    def run(fused):
+        cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, 64 * 16, torch.bfloat16, "cuda:0", max_seqs=4)
+        slots = [cache.alloc_slot() for _ in lens]
+        cache.reserve([(s_, st + L) for s_, st, L in zip(slots, starts, lens)]); cache.flush()
+        packed, n, q_lens = pack_step_host(slots, starts, [[0] * L for L in lens])
+        ctx = context_from_packed(packed.cuda(), n, slots, q_lens, starts)
+        x = _randn(M, hidden, seed=80).bfloat16().cuda()
+        w = _randn((n_q + 2 * n_kv) * hd, hidden, seed=81, scale=0.2).bfloat16().cuda()
+        gq, gk = (1 + _randn(hd, seed=82, scale=0.3)).float().cuda(), (1 + _randn(hd, seed=83, scale=0.3)).float().cuda()
+        inv = 3e4 ** (-2.0 * torch.arange(0, hd // 2, dtype=torch.float64) / hd)
+        cs = K.rope_table(ctx.positions, inv.cuda())
+        kv = cache.view(0)
+        if fused:
+            q, kn, vn = K.gemm_qkv(x, w, n_q, n_kv, hd, gq, gk, 1e-5, cs, ctx, kv, keep_new=True)
+        else:
+            q, kn, vn = K.qkv_finish(K.gemm(x, w), n_q, n_kv, hd, gq, gk, 1e-5, cs, ctx, kv, keep_new=True)
+        torch.cuda.synchronize()
+        return q, kn, vn, kv.k.clone(), kv.v.clone()
+    a, b = run(True), run(False)
+    for t_a, t_b, name in zip(a, b, ("q", "k_new", "v_new", "cache k", "cache v")):
+        assert torch.equal(t_a, t_b), name
+    assert K.gemm_status() == 0
 
 
 def test_sampler_argmax_ties_and_gumbel(kernels):
