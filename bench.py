@@ -193,8 +193,9 @@ def reference_arm():
     ``detllm.prepare`` makes, and that downloads the checkpoint and a calibration set
     (src/detllm/prepare.py:172, 236-240); there is no network."""
     print(json.dumps({"impl": "reference", "unavailable":
-                      "the reference runs only from an artifact that detllm.prepare builds by downloading "
-                      "Qwen/Qwen3-0.6B and WikiText2 (prepare.py:172,236-240); no network here"}))
+                      "offline install fails (build backend uv_build is not in the wheelhouse), and the reference "
+                      "runs only from an artifact that detllm.prepare builds by downloading Qwen/Qwen3-0.6B and "
+                      "WikiText2 (prepare.py:172,236-240); no network here"}))
     return 0
 
 
