@@ -21,7 +21,10 @@
 #ifndef AD_CHUNK
 #define AD_CHUNK 256
 #endif
-#define AD_WARPS (AD_CHUNK / 64)   // one page per warp
+#ifndef AD_WARPS
+#define AD_WARPS (AD_CHUNK / 64)   // warps of a block; each takes AD_CHUNK / AD_WARPS consecutive keys (at most a page)
+#endif
+#define AD_WKEYS (AD_CHUNK / AD_WARPS)
 #ifndef AD_ITERS
 #define AD_ITERS 8            // warp-wide loads per group
 #endif
@@ -40,6 +43,7 @@ struct DecodeArgs {
     int* counters;            // [n_seqs, n_kv], zero between launches
     int n_seqs, n_q, n_kv, n_chunks;
     float scale_log2; int window;
+    int early_trigger;        // 1: let the next kernel's blocks be scheduled as soon as this one's have started
 };
 
 // out[s, head, :] = sum_c 2^(m_c - M) o_c / sum_c 2^(m_c - M) l_c over the sequence's chunks, ascending.
@@ -100,14 +104,14 @@ __device__ __forceinline__ void decode_merge_head(const DecodeArgs& a, int s, in
 
 template <int HD, int GT>
 __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeArgs a) {
-    pdl_launch_dependents();
+    if (a.early_trigger) pdl_launch_dependents();
     pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     constexpr int LPR = HD / VEC;            // lanes per row
     constexpr int RPI = 32 / LPR;            // rows (keys) per warp-wide load
     constexpr int GROUP = AD_ITERS * RPI;    // keys per group
     static_assert(LPR >= 1 && LPR <= 32 && (LPR & (LPR - 1)) == 0, "head_dim / 16 bytes must be a power of two <= 32");
-    static_assert(IDM_PAGE % GROUP == 0 || GROUP > IDM_PAGE, "page is a whole number of groups");
+    static_assert(AD_WKEYS <= IDM_PAGE && IDM_PAGE % AD_WKEYS == 0, "a warp's keys lie inside one page");
     __shared__ float sm_m[AD_WARPS][GT], sm_l[AD_WARPS][GT];
     __shared__ float sm_o[AD_WARPS][GT][HD];
 
@@ -118,8 +122,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane / LPR, li = lane % LPR;
     const int group_heads = a.n_q / a.n_kv;
-    const int kb = chunk * AD_CHUNK + wib * IDM_PAGE;                        // this warp's page of keys
-    const bool warp_live = kb < len && kb + IDM_PAGE > lo;
+    const int kb = chunk * AD_CHUNK + wib * AD_WKEYS;                        // this warp's keys (inside one page)
+    const bool warp_live = kb < len && kb + AD_WKEYS > lo;
     const T* kpage = nullptr; const T* vpage = nullptr;
     if (warp_live) {
         const size_t off = kv_offset(a.cache, a.slots[s], kb, g);
@@ -135,7 +139,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
             m[h] = -INFINITY; l[h] = 0.f;
         }
         if (warp_live) {
-            constexpr int KEYS = IDM_PAGE;
+            constexpr int KEYS = AD_WKEYS;
             constexpr int NG = (KEYS + GROUP - 1) / GROUP;          // groups per page
             // Two register buffers: the next group's keys and values are on their way while this
             // group is worked on.  Every row of a live page is readable memory (rows past the
@@ -262,12 +266,195 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
     }
 }
 
+#if defined(IDM_BF16)
+// ------------------------------------------------------------- the same on mma.sync fragments
+// For bfloat16 caches with head_dim 64 or 128 and up to 8 q-heads per kv-head.  The scalar kernel above
+// spends its issue slots on FMAs and shuffles (a page of 64 keys costs a warp ~2 000 instructions);
+// here q . k^T and p . v are m16n8k16 tensor-core products on registers (a page costs ~450):
+//   * the 16 rows of the MMA tile are the group's q-heads (rows past the group are zero);
+//   * a thread reads 16-byte pieces of key and value rows straight from the cache, coalesced; because
+//     a dot product does not care in which order its terms come, the piece a thread holds is used as
+//     the fragment of two k-steps (dims are permuted the same way for q and k);
+//   * value fragments need keys along k: each 8 x 8 piece is transposed in registers with movmatrix;
+//     the permutation makes a thread's output columns the same 8 consecutive dims it loads.
+// Chunks, partials, the order of the merge and the masking rules are those of the scalar kernel.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&p);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_mma_kernel(DecodeArgs a) {
+    if (a.early_trigger) pdl_launch_dependents();
+    pdl_wait();
+    constexpr int NC = HD / 32;              // 32-dim pieces of a row: a thread holds 8 dims of each
+    constexpr int GT = 8;                    // q-heads per block (rows 0..7 of the tile)
+    __shared__ float sm_m[AD_WARPS][GT], sm_l[AD_WARPS][GT];
+    __shared__ float sm_o[AD_WARPS][GT][HD];
+    __shared__ int is_last;
+
+    const int chunk = blockIdx.x, g = blockIdx.y, s = blockIdx.z;
+    const int len = a.kv_len[s];
+    const int lo = a.window > 0 ? max(0, len - a.window) : 0;
+    if (chunk * AD_CHUNK >= len || (chunk + 1) * AD_CHUNK <= lo) return;
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;             // fragment row / column pair
+    const int group_heads = a.n_q / a.n_kv;
+    const int kb = chunk * AD_CHUNK + wib * IDM_PAGE;      // this warp's page of keys
+    const bool warp_live = kb < len && kb + IDM_PAGE > lo;
+
+    // q fragments: row gid = q-head gid of the group; piece c of the row feeds k-steps 2c and 2c + 1
+    uint32_t qa[2 * NC][4];
+    {
+        const bool row_live = gid < group_heads;
+        const T* qrow = a.q + ((size_t)s * a.n_q + g * group_heads + (row_live ? gid : 0)) * HD;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row_live) v = *reinterpret_cast<const uint4*>(qrow + 32 * c + tig * 8);
+            qa[2 * c][0] = v.x; qa[2 * c][2] = v.y; qa[2 * c + 1][0] = v.z; qa[2 * c + 1][2] = v.w;
+            qa[2 * c][1] = qa[2 * c][3] = qa[2 * c + 1][1] = qa[2 * c + 1][3] = 0;      // rows 8..15: none
+        }
+    }
+    float o[4 * NC][4];                      // o[4 c + m]: dims 32 c + 8 tig + 2 m (+1) of row gid (and row gid + 8, unused)
+#pragma unroll
+    for (int i = 0; i < 4 * NC; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_run = -INFINITY, l_run = 0.f;    // of row gid; l is this thread's share (keys 2 tig, 2 tig + 1 of each tile)
+
+    if (warp_live) {
+        const size_t off = kv_offset(a.cache, a.slots[s], kb, g);
+        const T* kpage = a.cache.k + off;
+        const T* vpage = a.cache.v + off;
+        // scores of the page: 8 tiles of 8 keys
+        float sc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+            const T* krow = kpage + (size_t)(8 * j + gid) * HD + tig * 8;
+            uint4 kv[NC];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) kv[c] = *reinterpret_cast<const uint4*>(krow + 32 * c);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                mma_bf16_16816(sc[j], qa[2 * c], kv[c].x, kv[c].y);
+                mma_bf16_16816(sc[j], qa[2 * c + 1], kv[c].z, kv[c].w);
+            }
+        }
+        // mask, scale, row maximum (row gid: this thread's 16 scores, then the 4 threads of the row)
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = kb + 8 * j + 2 * tig + e;
+                const float v = (key < len && key >= lo) ? sc[j][e] * a.scale_log2 : -INFINITY;
+                sc[j][e] = v;
+                mx = fmaxf(mx, v);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        m_run = mx;                          // finite: the page holds a live key, and every row sees the same keys
+        uint32_t pa[4][4];                   // p as A fragments: k-step t = key tiles 2t, 2t + 1
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float p0 = exp2f(sc[j][0] - m_run), p1 = exp2f(sc[j][1] - m_run);       // exp2(-inf) = 0
+            l_run += p0 + p1;
+            pa[j >> 1][(j & 1) * 2] = pack_bf16x2(p0, p1);
+            pa[j >> 1][(j & 1) * 2 + 1] = 0;                                             // rows 8..15
+        }
+        // o = p . v
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            uint4 v0[NC], v1[NC];            // value rows of key tiles 2t and 2t + 1
+            const int key0 = kb + 16 * t + gid, key1 = key0 + 8;
+            const T* vrow = vpage + (size_t)(16 * t + gid) * HD + tig * 8;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                v0[c] = *reinterpret_cast<const uint4*>(vrow + 32 * c);
+                v1[c] = *reinterpret_cast<const uint4*>(vrow + 8 * HD + 32 * c);
+                // rows past the length (or before the window) hold stale data: p is 0 there, but 0 * NaN is not
+                if (key0 >= len || key0 < lo) v0[c] = make_uint4(0, 0, 0, 0);
+                if (key1 >= len || key1 < lo) v1[c] = make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const uint32_t r0[4] = {v0[c].x, v0[c].y, v0[c].z, v0[c].w};
+                const uint32_t r1[4] = {v1[c].x, v1[c].y, v1[c].z, v1[c].w};
+#pragma unroll
+                for (int mth = 0; mth < 4; ++mth)
+                    mma_bf16_16816(o[4 * c + mth], pa[t], movmatrix_trans(r0[mth]), movmatrix_trans(r1[mth]));
+            }
+        }
+    }
+    // the row's sum: the 4 threads of the row hold different keys
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (gid < GT) {
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int mth = 0; mth < 4; ++mth) {
+                sm_o[wib][gid][32 * c + 8 * tig + 2 * mth] = o[4 * c + mth][0];
+                sm_o[wib][gid][32 * c + 8 * tig + 2 * mth + 1] = o[4 * c + mth][1];
+            }
+        if (tig == 0) { sm_m[wib][gid] = m_run; sm_l[wib][gid] = l_run; }
+    }
+    __syncthreads();
+    // merge the warps in ascending order and write the chunk's partial
+    for (int idx = threadIdx.x; idx < group_heads * HD; idx += AD_WARPS * 32) {
+        const int h = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, sm_m[w][h]);
+        float ov = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) {
+            const float f = sm_m[w][h] == -INFINITY ? 0.f : exp2f(sm_m[w][h] - M);
+            ov += f * sm_o[w][h][d];
+            L += f * sm_l[w][h];
+        }
+        const size_t row = ((size_t)s * a.n_q + g * group_heads + h) * a.n_chunks + chunk;
+        a.part_o[row * HD + d] = ov;
+        if (d == 0) { a.part_ml[row * 2] = M; a.part_ml[row * 2 + 1] = L; }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int live = (len - 1) / AD_CHUNK - lo / AD_CHUNK + 1;
+        const int prev = atomicAdd(&a.counters[s * a.n_kv + g], 1);
+        is_last = prev == live - 1;
+        if (is_last) a.counters[s * a.n_kv + g] = 0;
+    }
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        for (int h = wib; h < group_heads; h += AD_WARPS) decode_merge_head(a, s, g * group_heads + h, HD, lane);
+    }
+}
+#endif  // IDM_BF16
+
 template <int HD>
 static int launch_decode(const DecodeArgs& a, int group_heads, cudaStream_t stream) {
     dim3 grid(a.n_chunks, a.n_kv, a.n_seqs);
-    if (group_heads % 4 == 0) idm_launch(attention_decode_kernel<HD, 4>, dim3(grid), dim3(AD_WARPS * 32), 0, stream, a);
-    else if (group_heads % 2 == 0) idm_launch(attention_decode_kernel<HD, 2>, dim3(grid), dim3(AD_WARPS * 32), 0, stream, a);
-    else idm_launch(attention_decode_kernel<HD, 1>, dim3(grid), dim3(AD_WARPS * 32), 0, stream, a);
+    // launched early, this kernel's waiting blocks (all registers of an SM) slow the product before it: measured
+    static const bool pdl = idm_pdl_flag("IDM_PDL_ATTN", 0);
+    static const bool early = idm_pdl_flag("IDM_PDL_ATTN_EARLY", 1);
+    DecodeArgs b = a;
+    b.early_trigger = early;
+    if (group_heads % 4 == 0) idm_launch_opt(pdl, attention_decode_kernel<HD, 4>, dim3(grid), dim3(AD_WARPS * 32), 0, stream, b);
+    else if (group_heads % 2 == 0) idm_launch_opt(pdl, attention_decode_kernel<HD, 2>, dim3(grid), dim3(AD_WARPS * 32), 0, stream, b);
+    else idm_launch_opt(pdl, attention_decode_kernel<HD, 1>, dim3(grid), dim3(AD_WARPS * 32), 0, stream, b);
     return 0;
 }
 
@@ -307,6 +494,19 @@ extern "C" int idm_attention_decode(const void* q, void* out, void* k_pool, void
     a.window = window;
     const int gh = n_q / n_kv;
     constexpr int VEC = Vec16<T>::N;
+#if defined(IDM_BF16)
+    static const bool use_mma = idm_pdl_flag("IDM_DECODE_MMA", 1);
+    if (use_mma && (hd == 64 || hd == 128) && gh <= 8 && AD_WARPS * IDM_PAGE == AD_CHUNK) {
+        static const bool pdl = idm_pdl_flag("IDM_PDL_ATTN", 0);
+        static const bool early = idm_pdl_flag("IDM_PDL_ATTN_EARLY", 1);
+        a.early_trigger = early;
+        dim3 grid(a.n_chunks, a.n_kv, a.n_seqs);
+        if (hd == 128) idm_launch_opt(pdl, attention_decode_mma_kernel<128>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+        else idm_launch_opt(pdl, attention_decode_mma_kernel<64>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+        IDM_LAUNCH_CHECK("attention_decode_mma");
+        return 0;
+    }
+#endif
     if (hd == VEC * 2) launch_decode<VEC * 2>(a, gh, stream);
     else if (hd == VEC * 4) launch_decode<VEC * 4>(a, gh, stream);
     else if (hd == VEC * 8) launch_decode<VEC * 8>(a, gh, stream);

@@ -55,6 +55,99 @@ struct GemmEpi {
 
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // warps 0-3
 
+// ---- thread-block clusters: all blocks of a cluster run together and can read each other's shared memory
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
+// The finished row of 128 features of one token, four consecutive features per lane, through the
+// fused epilogues (the cluster path: each block of a cluster finishes some of the tile's rows).
+template <int EPI>
+__device__ __forceinline__ void epilogue_row(const GemmEpi& e, float4 v, int t, int f0, int tile_x, int lane,
+                                             int n_features, const int* meta_row) {
+    const int f = f0 + lane * 4;
+    if (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+        if (f < n_features) {
+            float4* p = reinterpret_cast<float4*>(e.out + (size_t)t * n_features + f);
+            if (EPI == EPI_RESIDUAL) { const float4 o = *p; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+            *p = v;
+        }
+    } else if (EPI == EPI_SWIGLU) {
+        // lanes 0..15 hold gate features 4 lane .. 4 lane + 3 of this tile, lanes 16..31 the up rows of the same
+        const float ux = __shfl_down_sync(0xffffffffu, v.x, 16), uy = __shfl_down_sync(0xffffffffu, v.y, 16);
+        const float uz = __shfl_down_sync(0xffffffffu, v.z, 16), uw = __shfl_down_sync(0xffffffffu, v.w, 16);
+        if (lane < 16) {
+            const int fg = tile_x * 64 + lane * 4;
+            T* y = e.y + (size_t)t * e.inter + fg;
+            if (fg + 0 < e.inter) from_f32(y[0], v.x / (1.0f + expf(-v.x)) * ux);
+            if (fg + 1 < e.inter) from_f32(y[1], v.y / (1.0f + expf(-v.y)) * uy);
+            if (fg + 2 < e.inter) from_f32(y[2], v.z / (1.0f + expf(-v.z)) * uz);
+            if (fg + 3 < e.inter) from_f32(y[3], v.w / (1.0f + expf(-v.w)) * uw);
+        }
+    } else if (EPI == EPI_QKV) {
+        const QkvArgs& a = e.q;
+        const int lph = a.hd >> 2;                        // lanes per head (a power of two)
+        const int head = f0 / a.hd + lane / lph, li = lane % lph;
+        const int heads = a.n_q + 2 * a.n_kv, half = a.hd >> 1;
+        const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv, live = head < heads;
+        const float* gamma = is_q ? a.gq : (is_k ? a.gk : nullptr);
+        float x[4] = {v.x, v.y, v.z, v.w};
+        const int d = li * 4;                             // first of this lane's dims within the head
+        // (every lane runs the shuffles, whatever its head is: they are warp-wide)
+        float ss = __fmaf_rn(x[3], x[3], __fmaf_rn(x[2], x[2], __fmaf_rn(x[1], x[1], __fmul_rn(x[0], x[0]))));
+        for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (live && gamma != nullptr) {
+            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.hd), a.eps)));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[i] = __fmul_rn(__fmul_rn(x[i], inv), gamma[d + i]);
+        }
+        float other[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) other[i] = __shfl_xor_sync(0xffffffffu, x[i], lph >> 1);   // the rotation partner
+        if (live && (is_q || is_k) && a.cs != nullptr) {
+            const bool first = li < (lph >> 1);           // dims below head_dim / 2
+            const int j = first ? d : d - half;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 c = a.cs[(size_t)t * half + j + i];
+                x[i] = first ? __fmaf_rn(x[i], c.x, -__fmul_rn(other[i], c.y))
+                             : __fmaf_rn(x[i], c.x, __fmul_rn(other[i], c.y));
+            }
+        }
+        if (live) {
+            T* dst_a = nullptr; T* dst_b = nullptr;
+            if (is_q) {
+                dst_a = a.q_out + ((size_t)t * a.n_q + head) * a.hd + d;
+            } else {
+                const int g = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
+                if (a.write_cache)
+                    dst_a = (is_k ? a.cache.k : a.cache.v) +
+                            (((size_t)meta_row[0] * a.n_kv + g) * IDM_PAGE + meta_row[1]) * (size_t)a.hd + d;
+                T* packed = is_k ? a.k_new : a.v_new;
+                if (packed) dst_b = packed + ((size_t)t * a.n_kv + g) * a.hd + d;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (dst_a) from_f32(dst_a[i], x[i]);
+                if (dst_b) from_f32(dst_b[i], x[i]);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------- kernel
 template <int BN, int STAGES>
 struct GemmSmem {
@@ -65,7 +158,7 @@ struct GemmSmem {
     static constexpr int TOTAL = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;   // + slack to align to 1024
 };
 
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, bool CL>
 __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                   const __grid_constant__ CUtensorMap map_x,
                                                                   const GemmEpi e, int n_tokens,
@@ -183,6 +276,17 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
                             if (t < n_tokens) dst[(size_t)t * n_features + f] = v[j];
                         }
                     }
+                }
+            } else if (CL) {
+                // cluster path: this block's slice of the tile goes to its own shared memory
+                float* xs = (float*)gen_base;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (t0 + c0 >= n_tokens) break;
+                    float v[16];
+                    tc_ld16(tmem_d + lane_base + (uint32_t)c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) xs[(c0 + j) * GT_BM + fl] = v[j];
                 }
             } else {
                 float* xs = (float*)gen_base;                     // [BN][128] tile; the pipeline's stages are free now
@@ -331,6 +435,31 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
     }
     tc_fence_before();
     __syncthreads();
+    if (CL) {
+        // Every block of the cluster holds its K-slice of the tile in shared memory.  Block `rank`
+        // finishes the token rows rank, rank + S, ...: it adds the S slices in ascending order, read
+        // through distributed shared memory, and runs the epilogue on the row.  Two cluster barriers:
+        // all slices written before anyone reads; nobody leaves while others may still read.
+        cluster_sync_all();
+        if (warp < 4 && !*abort_flag) {
+            const uint32_t S_ = gridDim.z, rank = cluster_rank();
+            const int cols = min(BN, n_tokens - t0);
+            const int* meta = (const int*)(gen_base + STAGES * S::STAGE_BYTES + 1024);
+            for (int t = (int)rank + (int)S_ * warp; t < cols; t += (int)S_ * 4) {
+                const uint32_t addr = base + (uint32_t)(t * GT_BM + lane * 4) * 4u;
+                float4 part[16];
+#pragma unroll
+                for (int r = 0; r < 16; ++r)
+                    if (r < (int)S_) part[r] = ld_cluster_f4(addr, (uint32_t)r);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int r = 0; r < 16; ++r)
+                    if (r < (int)S_) { acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w; }
+                epilogue_row<EPI>(e, acc, t0 + t, f0, blockIdx.x, lane, n_features, meta + 2 * t);
+            }
+        }
+        cluster_sync_all();
+    }
     if (warp == 5) {
         tmem_dealloc(tmem_d, TMEM_COLS);
     }
@@ -348,12 +477,36 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int k, int box_
 }
 
 template <int BN, int STAGES, int EPI>
+static int launch_gemm_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
+                               int kb_per_split, int splits, cudaStream_t stream) {
+    using S = GemmSmem<BN, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI, true>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        IDM_REQUIRE(err == cudaSuccess, "gemm: cannot get %d bytes of shared memory: %s", S::TOTAL,
+                    cudaGetErrorString(err));
+        err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI, true>,
+                                   cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        IDM_REQUIRE(err == cudaSuccess, "gemm: clusters of up to 16 blocks are not allowed here: %s",
+                    cudaGetErrorString(err));
+        configured = true;
+    }
+    dim3 grid((N + GT_BM - 1) / GT_BM, 1, splits);
+    cudaError_t err = idm_launch_cluster(gemm_tcgen05_kernel<BN, STAGES, EPI, true>, grid, dim3(GT_THREADS), S::TOTAL,
+                                         stream, splits, mw, mx, e, M, N, kb_total, kb_per_split);
+    IDM_REQUIRE(err == cudaSuccess, "gemm: cluster launch failed: %s", cudaGetErrorString(err));
+    IDM_LAUNCH_CHECK("gemm_tcgen05 (cluster)");
+    return 0;
+}
+
+template <int BN, int STAGES, int EPI>
 static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
                        int kb_per_split, int splits, cudaStream_t stream) {
     using S = GemmSmem<BN, STAGES>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI>,
+        cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI, false>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
         IDM_REQUIRE(err == cudaSuccess, "gemm: cannot get %d bytes of shared memory: %s", S::TOTAL,
                     cudaGetErrorString(err));
@@ -363,7 +516,7 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmE
     IDM_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm: too many tiles (%u x %u)", grid.y, grid.z);
     IDM_REQUIRE(EPI == EPI_PARTIAL || splits == 1 || (long long)grid.x * grid.y <= GT_COUNTER_SLOTS,
                 "gemm: %u x %u tiles exceed the %d counters", grid.x, grid.y, GT_COUNTER_SLOTS);
-    idm_launch(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(GT_THREADS), S::TOTAL, stream, mw, mx, e, M, N,
+    idm_launch(gemm_tcgen05_kernel<BN, STAGES, EPI, false>, dim3(grid), dim3(GT_THREADS), S::TOTAL, stream, mw, mx, e, M, N,
                kb_total, kb_per_split);
     IDM_LAUNCH_CHECK("gemm_tcgen05");
     return 0;
@@ -389,6 +542,9 @@ extern "C" long long idm_gemm_bf16_workspace_floats(int M, int N, int splits) {
     return (long long)GT_COUNTER_SLOTS + (splits > 1 ? (long long)splits * M * N : 0);
 }
 
+static int g_gemm_cluster = 1;
+extern "C" void idm_gemm_set_cluster(int on) { g_gemm_cluster = on ? 1 : 0; }
+
 template <int EPI>
 static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, int M, int N, int K, int splits,
                     cudaStream_t stream) {
@@ -409,6 +565,14 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, i
     const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     if (make_map(&mw, w, N, K, GT_BM)) return 1;
     if (make_map(&mx, x, M, K, bn)) return 1;
+    // up to 64 tokens with K split: the slices are added inside a thread-block cluster
+    if (EPI != EPI_PARTIAL && splits > 1 && splits <= 16 && M <= 64 && N % 4 == 0 && g_gemm_cluster) {
+        switch (bn) {
+            case 16: return launch_gemm_cluster<16, 6, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
+            case 32: return launch_gemm_cluster<32, 6, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
+            default: return launch_gemm_cluster<64, 4, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
+        }
+    }
     switch (bn) {
         case 16: return launch_gemm<16, 6, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
         case 32: return launch_gemm<32, 6, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);

@@ -29,3 +29,9 @@ int idm_pdl_enabled() {
     return g_pdl;
 }
 extern "C" void idm_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+
+int idm_pdl_flag(const char* name, int dflt) {
+    const char* e = getenv(name);
+    if (!e) return dflt;
+    return strcmp(e, "0") != 0;
+}

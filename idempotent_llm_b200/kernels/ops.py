@@ -73,16 +73,18 @@ class Kernels:
         # them when this is True and fall back to separate kernels otherwise
         self.fused = (dtype == torch.bfloat16 and self.gemm_impl == "tcgen05"
                       and os.environ.get("IDM_FUSED", "1") != "0")
-        # Below this many tokens the inner axis is split over blocks and the separate kernels, which
-        # add the slices with the whole GPU, are quicker than one block per tile doing it; from here
-        # on (no split) the fused epilogues win.  IDM_FUSED_MIN_TOKENS=0 fuses always.
+        # Up to 64 tokens the slices of a split inner axis are added inside a thread-block cluster and
+        # the epilogue is fused; above 256 tokens nothing is split and the epilogue is fused; between
+        # the two the separate kernels, which add the slices with the whole GPU, are quicker than one
+        # block per tile doing it.  IDM_FUSED_MIN_TOKENS / IDM_FUSED_MAX_SMALL move the borders.
         self.fused_min_tokens = int(os.environ.get("IDM_FUSED_MIN_TOKENS", "257"))
+        self.fused_max_small = int(os.environ.get("IDM_FUSED_MAX_SMALL", "64"))
         # "tcgen05": prompts' attention on the tensor cores; "general": the one-warp-per-query kernel
         self.prefill_impl = os.environ.get("IDM_PREFILL", "tcgen05")
         self.page = L.idm_page_tokens()
 
     def use_fused(self, n_tokens: int) -> bool:
-        return self.fused and n_tokens >= self.fused_min_tokens
+        return self.fused and (n_tokens >= self.fused_min_tokens or n_tokens <= self.fused_max_small)
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):

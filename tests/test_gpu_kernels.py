@@ -391,7 +391,12 @@ def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, 
         return q, kn, vn, kv.k.clone(), kv.v.clone()
     a, b = run(True), run(False)
     for t_a, t_b, name in zip(a, b, ("q", "k_new", "v_new", "cache k", "cache v")):
-        assert torch.equal(t_a, t_b), name
+        if M <= 64:
+            # up to 64 tokens the slices are added inside a cluster and a row's sum of squares is taken
+            # four elements per lane: the same numbers added in another order
+            assert helpers.rel_err(t_a, t_b) < KTOL["bfloat16"], name
+        else:
+            assert torch.equal(t_a, t_b), name
     assert K.gemm_status() == 0
 
 
