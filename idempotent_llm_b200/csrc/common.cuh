@@ -106,6 +106,17 @@ template <> struct Vec16<__nv_bfloat16> {
     }
 };
 
+// g * sigmoid(g) * u with the hardware exponential and reciprocal (relative error ~1e-6, far below the
+// bfloat16 rounding of the result).  Every kernel that applies the activation uses this one formula,
+// so fused and separate paths give the same bits.  (src/detllm/ops/di_swiglu.py:43-45)
+__device__ __forceinline__ float silu_mul(float g, float u) {
+#if defined(IDM_F32)
+    return g / (1.0f + expf(-g)) * u;                       // the 32-bit path stays exact
+#else
+    return __fmul_rn(__fmul_rn(g, __frcp_rn(1.0f + __expf(-g))), u);
+#endif
+}
+
 // ------------------------------------------------------------ reductions
 // Fixed-order reductions: xor butterflies inside a warp, then the warps' values
 // added in ascending order.  The order depends on the block size only.
@@ -136,14 +147,26 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // are a chain.
 __device__ __forceinline__ float add_partials(float start, const float* __restrict__ base, int n, size_t stride,
                                               size_t idx) {
+    const float* p = base + idx;
+    if (n == 1) return start + __ldg(p);                    // the common case: nothing was split
     float v = start;
-    for (int p0 = 0; p0 < n; p0 += 8) {
+    int left = n;
+    while (left >= 8) {
         float part[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) part[i] = (p0 + i < n) ? __ldg(base + (size_t)(p0 + i) * stride + idx) : 0.f;
+        for (int i = 0; i < 8; ++i) part[i] = __ldg(p + (size_t)i * stride);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v += part[i];
+        p += 8 * stride;
+        left -= 8;
+    }
+    if (left > 0) {
+        float part[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) part[i] = i < left ? __ldg(p + (size_t)i * stride) : 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-            if (p0 + i < n) v += part[i];
+            if (i < left) v += part[i];
     }
     return v;
 }

@@ -71,13 +71,15 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec4_kernel(float* __restrict
     if (live) {
         const size_t idx = (size_t)r * hidden + c;
         v = *reinterpret_cast<const float4*>(h + idx);
-        float4 part[16];
+        if (n_partials > 0) {
+            float4 part[16];
 #pragma unroll
-        for (int p = 0; p < 16; ++p)
-            if (p < n_partials) part[p] = *reinterpret_cast<const float4*>(delta + p * partial_stride + idx);
+            for (int p = 0; p < 16; ++p)
+                if (p < n_partials) part[p] = *reinterpret_cast<const float4*>(delta + p * partial_stride + idx);
 #pragma unroll
-        for (int p = 0; p < 16; ++p)
-            if (p < n_partials) { v.x += part[p].x; v.y += part[p].y; v.z += part[p].z; v.w += part[p].w; }
+            for (int p = 0; p < 16; ++p)
+                if (p < n_partials) { v.x += part[p].x; v.y += part[p].y; v.z += part[p].z; v.w += part[p].w; }
+        }
         if (!rows && n_partials) *reinterpret_cast<float4*>(h + idx) = v;
     }
     const float total = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, scratch);
@@ -145,17 +147,44 @@ extern "C" int idm_rope_table(const int* positions, const double* inv_freq, floa
 // by the token's position (src/detllm/ops/rope.py:47-55); v heads are copied.
 // q goes to q_out [N, n_q, hd]; k and v go to the cache at the token's position
 // and/or to packed buffers k_new, v_new [N, n_kv, hd].
-__global__ void qkv_finish_kernel(QkvArgs a) {
+__global__ void __launch_bounds__(128) qkv_finish_kernel(QkvArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    // one block per token: the token's place in the cache is looked up once, the warps share the heads
+    __shared__ int place[2];
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = a.n_q + 2 * a.n_kv;
-    if (warp >= a.n_tokens * heads) return;
-    const int t = warp / heads, head = warp % heads;
-    const size_t row = (size_t)t * heads * a.hd + (size_t)head * a.hd;
-    qkv_finish_row(a, t, head, lane,
-                   [&](int j) { return add_partials(0.f, a.qkv, a.n_partials, a.partial_stride, row + j); },
-                   QkvLocateFromTables{a, t});
+    if (threadIdx.x == 0 && a.write_cache) {
+        const int pos = a.positions[t];
+        const int r = a.cache.ring ? pos % a.cache.ring : pos;
+        place[0] = a.cache.table[(size_t)a.slots[a.token_seq[t]] * a.cache.table_stride + r / IDM_PAGE];
+        place[1] = r % IDM_PAGE;
+    }
+    __syncthreads();
+    const int page = place[0], prow = place[1];
+    if (a.tiles4) {
+        // whole heads inside tiles of 128 features, four features per lane (qkv_finish_tile4)
+        const int width = heads * a.hd;
+        for (int f0 = warp * 128; f0 < width; f0 += 4 * 128) {
+            const int f = f0 + lane * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (f < width) {
+                const float* p = a.qkv + (size_t)t * width + f;
+                for (int z = 0; z < a.n_partials; ++z) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(p + (size_t)z * a.partial_stride);
+                    v.x += q4.x; v.y += q4.y; v.z += q4.z; v.w += q4.w;
+                }
+            }
+            qkv_finish_tile4(a, v, t, f0, lane, page, prow);
+        }
+        return;
+    }
+    for (int head = warp; head < heads; head += 4) {
+        const size_t row = (size_t)t * heads * a.hd + (size_t)head * a.hd;
+        qkv_finish_row(a, t, head, lane,
+                       [&](int j) { return add_partials(0.f, a.qkv, a.n_partials, a.partial_stride, row + j); },
+                       [&](int g) { return (((size_t)page * a.n_kv + g) * IDM_PAGE + prow) * (size_t)a.hd; });
+    }
 }
 
 extern "C" int idm_qkv_finish(const float* qkv, int n_partials, long long partial_stride, int n_tokens,
@@ -176,8 +205,8 @@ extern "C" int idm_qkv_finish(const float* qkv, int n_partials, long long partia
     a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
     a.write_cache = k_pool != nullptr;
     a.token_seq = token_seq; a.positions = positions; a.slots = slots;
-    const long long warps = (long long)n_tokens * (n_q + 2 * n_kv);
-    idm_launch(qkv_finish_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, a);
+    a.tiles4 = (128 % hd == 0 && hd >= 8 && (partial_stride % 4) == 0) ? 1 : 0;
+    idm_launch(qkv_finish_kernel, dim3(n_tokens), dim3(128), 0, stream, a);
     IDM_LAUNCH_CHECK("qkv_finish");
     return 0;
 }
@@ -232,7 +261,7 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ g
     const size_t base = t * (size_t)width;
     const float g = add_partials(0.f, gu, n_partials, partial_stride, base + gi);
     const float u = add_partials(0.f, gu, n_partials, partial_stride, base + ui);
-    from_f32(y[t * (size_t)inter + c], g / (1.0f + expf(-g)) * u);
+    from_f32(y[t * (size_t)inter + c], silu_mul(g, u));
 }
 
 extern "C" int idm_swiglu(const float* gu, int n_partials, long long partial_stride, void* y, int n_tokens,

@@ -92,59 +92,13 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, float4 v, int t, 
         if (lane < 16) {
             const int fg = tile_x * 64 + lane * 4;
             T* y = e.y + (size_t)t * e.inter + fg;
-            if (fg + 0 < e.inter) from_f32(y[0], v.x / (1.0f + expf(-v.x)) * ux);
-            if (fg + 1 < e.inter) from_f32(y[1], v.y / (1.0f + expf(-v.y)) * uy);
-            if (fg + 2 < e.inter) from_f32(y[2], v.z / (1.0f + expf(-v.z)) * uz);
-            if (fg + 3 < e.inter) from_f32(y[3], v.w / (1.0f + expf(-v.w)) * uw);
+            if (fg + 0 < e.inter) from_f32(y[0], silu_mul(v.x, ux));
+            if (fg + 1 < e.inter) from_f32(y[1], silu_mul(v.y, uy));
+            if (fg + 2 < e.inter) from_f32(y[2], silu_mul(v.z, uz));
+            if (fg + 3 < e.inter) from_f32(y[3], silu_mul(v.w, uw));
         }
     } else if (EPI == EPI_QKV) {
-        const QkvArgs& a = e.q;
-        const int lph = a.hd >> 2;                        // lanes per head (a power of two)
-        const int head = f0 / a.hd + lane / lph, li = lane % lph;
-        const int heads = a.n_q + 2 * a.n_kv, half = a.hd >> 1;
-        const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv, live = head < heads;
-        const float* gamma = is_q ? a.gq : (is_k ? a.gk : nullptr);
-        float x[4] = {v.x, v.y, v.z, v.w};
-        const int d = li * 4;                             // first of this lane's dims within the head
-        // (every lane runs the shuffles, whatever its head is: they are warp-wide)
-        float ss = __fmaf_rn(x[3], x[3], __fmaf_rn(x[2], x[2], __fmaf_rn(x[1], x[1], __fmul_rn(x[0], x[0]))));
-        for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (live && gamma != nullptr) {
-            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.hd), a.eps)));
-#pragma unroll
-            for (int i = 0; i < 4; ++i) x[i] = __fmul_rn(__fmul_rn(x[i], inv), gamma[d + i]);
-        }
-        float other[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) other[i] = __shfl_xor_sync(0xffffffffu, x[i], lph >> 1);   // the rotation partner
-        if (live && (is_q || is_k) && a.cs != nullptr) {
-            const bool first = li < (lph >> 1);           // dims below head_dim / 2
-            const int j = first ? d : d - half;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 c = a.cs[(size_t)t * half + j + i];
-                x[i] = first ? __fmaf_rn(x[i], c.x, -__fmul_rn(other[i], c.y))
-                             : __fmaf_rn(x[i], c.x, __fmul_rn(other[i], c.y));
-            }
-        }
-        if (live) {
-            T* dst_a = nullptr; T* dst_b = nullptr;
-            if (is_q) {
-                dst_a = a.q_out + ((size_t)t * a.n_q + head) * a.hd + d;
-            } else {
-                const int g = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
-                if (a.write_cache)
-                    dst_a = (is_k ? a.cache.k : a.cache.v) +
-                            (((size_t)meta_row[0] * a.n_kv + g) * IDM_PAGE + meta_row[1]) * (size_t)a.hd + d;
-                T* packed = is_k ? a.k_new : a.v_new;
-                if (packed) dst_b = packed + ((size_t)t * a.n_kv + g) * a.hd + d;
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (dst_a) from_f32(dst_a[i], x[i]);
-                if (dst_b) from_f32(dst_b[i], x[i]);
-            }
-        }
+        qkv_finish_tile4(e.q, v, t, f0, lane, meta_row[0], meta_row[1]);
     }
 }
 
@@ -410,7 +364,7 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
                         if (fg < e.inter)
                             for (int t = fl >> 6; t < cols; t += 2) {                  // two token rows at a time
                                 const float g = xs[t * GT_BM + (fl & 63)], u = xs[t * GT_BM + 64 + (fl & 63)];
-                                from_f32(e.y[(size_t)(t0 + t) * e.inter + fg], g / (1.0f + expf(-g)) * u);
+                                from_f32(e.y[(size_t)(t0 + t) * e.inter + fg], silu_mul(g, u));
                             }
                     } else if (EPI == EPI_QKV) {
                         const int hpt = GT_BM / e.q.hd;           // heads per tile
@@ -463,6 +417,214 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
     if (warp == 5) {
         tmem_dealloc(tmem_d, TMEM_COLS);
     }
+}
+
+// ------------------------------------------------------------------- persistent kernel (many tokens)
+// Above 256 tokens nothing is split and the product is bound by the tensor cores.  One block per SM
+// walks over output tiles of 128 features x BN tokens (BN = 256, or 128 when that fills more SMs):
+//   * warp 4 keeps the TMA ring full across tile borders;
+//   * warp 5 issues the MMAs into one of TWO accumulators in tensor memory (2 x BN columns);
+//   * warps 0-3 run the epilogue of the finished accumulator while the next tile's MMAs run.
+// A 128 x 256 tile reads 12 KB of shared memory per 128 tensor-core cycles (128 x 128 reads 8 KB per
+// 64, the whole shared-memory bandwidth).  The fused epilogues work on chunks of 32 tokens through a
+// 16 KB buffer of their own, as the ring is never idle here.
+template <int BN, int STAGES>
+struct PersistSmem {
+    static constexpr int A_BYTES = GT_BM * GT_BK * 2;
+    static constexpr int B_BYTES = BN * GT_BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int XS_BYTES = 32 * GT_BM * 4;                // [32 tokens][128 features] floats
+    static constexpr int META_BYTES = BN * 8;                      // per token: page, row
+    static constexpr int XS_OFF = STAGES * STAGE_BYTES;
+    static constexpr int META_OFF = XS_OFF + XS_BYTES;
+    static constexpr int BAR_OFF = META_OFF + META_BYTES;
+    static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(GT_THREADS) gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                     const __grid_constant__ CUtensorMap map_x,
+                                                                     const GemmEpi e, int n_tokens, int n_features,
+                                                                     int kb_total, int tiles_x, int n_tiles) {
+    using S = PersistSmem<BN, STAGES>;
+    constexpr int TMEM_COLS = 2 * BN;                              // 256 or 512
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + S::BAR_OFF;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + S::BAR_OFF + 8 * (2 * STAGES + 4));
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 5) tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    pdl_wait();
+
+    if (warp == 4) {
+        if (lane == 0) {
+            uint32_t cnt = 0;                                      // k-blocks issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                const int f0 = (tile % tiles_x) * GT_BM, t0 = (tile / tiles_x) * BN;
+                bool ok = true;
+                for (int i = 0; i < kb_total && ok; ++i, ++cnt) {
+                    const int s = cnt % STAGES;
+                    ok = mbar_wait(empty_bar(s), ((cnt / STAGES) & 1) ^ 1, abort_flag, &g_gemm_error);
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+                    const uint32_t a_dst = base + s * S::STAGE_BYTES;
+                    tma_load_2d(a_dst, &map_w, i * GT_BK, f0, full_bar(s));
+                    tma_load_2d(a_dst + S::A_BYTES, &map_x, i * GT_BK, t0, full_bar(s));
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(GT_BM, BN);
+            uint32_t cnt = 0, it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t acc = it & 1;
+                ok = mbar_wait(tempty_bar(acc), ((it >> 1) & 1) ^ 1, abort_flag, &g_gemm_error);   // epilogue drained it
+                if (!ok) break;
+                tc_fence_after();
+                for (int i = 0; i < kb_total && ok; ++i, ++cnt) {
+                    const int s = cnt % STAGES;
+                    ok = mbar_wait(full_bar(s), (cnt / STAGES) & 1, abort_flag, &g_gemm_error);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * S::STAGE_BYTES;
+                    const uint64_t a_desc = umma_desc_kmajor(a_addr), b_desc = umma_desc_kmajor(a_addr + S::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < GT_BK / GT_UMMA_K; ++k)
+                        tc_mma_bf16(tmem + acc * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty_bar(s));
+                }
+                if (ok) tc_commit(tfull_bar(acc));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        float* xs = (float*)(gen_base + S::XS_OFF);
+        int* meta = (int*)(gen_base + S::META_OFF);
+        const int fl = warp * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+            const int tx = tile % tiles_x, f0 = tx * GT_BM, t0 = (tile / tiles_x) * BN;
+            const int f = f0 + fl;
+            const uint32_t acc = it & 1;
+            if (EPI == EPI_QKV && e.q.write_cache) {
+                epi_sync();                                        // the previous tile's readers of meta are done
+                for (int tl = fl; tl < BN; tl += 128)
+                    if (t0 + tl < n_tokens) {
+                        const int t = t0 + tl;
+                        const int pos = e.q.positions[t];
+                        const int r = e.q.cache.ring ? pos % e.q.cache.ring : pos;
+                        meta[2 * tl] = e.q.cache.table[(size_t)e.q.slots[e.q.token_seq[t]] * e.q.cache.table_stride + r / IDM_PAGE];
+                        meta[2 * tl + 1] = r % IDM_PAGE;
+                    }
+            }
+            ok = mbar_wait(tfull_bar(acc), (it >> 1) & 1, abort_flag, &g_gemm_error);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (t0 + c0 >= n_tokens) break;                    // warp-uniform
+                float v[32];
+                tc_ld16(tmem + acc * BN + lane_base + (uint32_t)c0, v);
+                tc_ld16(tmem + acc * BN + lane_base + (uint32_t)c0 + 16, v + 16);
+                if (EPI == EPI_PARTIAL || EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+                    if (f < n_features) {
+                        float old[32];
+                        if (EPI == EPI_RESIDUAL) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                old[j] = t0 + c0 + j < n_tokens ? e.out[(size_t)(t0 + c0 + j) * n_features + f] : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (t0 + c0 + j < n_tokens)
+                                e.out[(size_t)(t0 + c0 + j) * n_features + f] = EPI == EPI_RESIDUAL ? old[j] + v[j] : v[j];
+                    }
+                } else {
+                    const int cols = min(32, n_tokens - t0 - c0);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) xs[j * GT_BM + fl] = v[j];
+                    epi_sync();
+                    if (EPI == EPI_SWIGLU) {
+                        const int fg = tx * 64 + (fl & 63);
+                        if (fg < e.inter)
+                            for (int j = fl >> 6; j < cols; j += 2) {
+                                const float g = xs[j * GT_BM + (fl & 63)], u = xs[j * GT_BM + 64 + (fl & 63)];
+                                from_f32(e.y[(size_t)(t0 + c0 + j) * e.inter + fg], silu_mul(g, u));
+                            }
+                    } else if (EPI == EPI_QKV) {
+                        const int hpt = GT_BM / e.q.hd, heads = e.q.n_q + 2 * e.q.n_kv;
+                        for (int row = warp; row < cols * hpt; row += 4) {
+                            const int c = row / hpt, hh = row % hpt;
+                            const int head = f0 / e.q.hd + hh;
+                            if (head < heads) {
+                                const float* src = xs + c * GT_BM + hh * e.q.hd;
+                                const int page = meta[2 * (c0 + c)], prow = meta[2 * (c0 + c) + 1];
+                                qkv_finish_row(e.q, t0 + c0 + c, head, lane, [&](int j) { return src[j]; },
+                                               [&](int g) {
+                                                   return (((size_t)page * e.q.n_kv + g) * IDM_PAGE + prow) * (size_t)e.q.hd;
+                                               });
+                            }
+                        }
+                    }
+                    epi_sync();                                    // the buffer is free for the next chunk
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+template <int BN, int STAGES, int EPI>
+static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
+                             cudaStream_t stream) {
+    using S = PersistSmem<BN, STAGES>;
+    static bool configured = false;
+    static int n_sm = 0;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_persistent_kernel<BN, STAGES, EPI>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        IDM_REQUIRE(err == cudaSuccess, "gemm: cannot get %d bytes of shared memory: %s", S::TOTAL,
+                    cudaGetErrorString(err));
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    const int tiles_x = (N + GT_BM - 1) / GT_BM, tiles_y = (M + BN - 1) / BN;
+    const int n_tiles = tiles_x * tiles_y;
+    const int grid = n_tiles < n_sm ? n_tiles : n_sm;
+    idm_launch(gemm_persistent_kernel<BN, STAGES, EPI>, dim3(grid), dim3(GT_THREADS), S::TOTAL, stream, mw, mx, e, M, N,
+               kb_total, tiles_x, n_tiles);
+    IDM_LAUNCH_CHECK("gemm_persistent");
+    return 0;
 }
 
 // ------------------------------------------------------------------------------ host
@@ -542,8 +704,9 @@ extern "C" long long idm_gemm_bf16_workspace_floats(int M, int N, int splits) {
     return (long long)GT_COUNTER_SLOTS + (splits > 1 ? (long long)splits * M * N : 0);
 }
 
-static int g_gemm_cluster = 1;
+static int g_gemm_cluster = 1, g_gemm_persistent = 1;
 extern "C" void idm_gemm_set_cluster(int on) { g_gemm_cluster = on ? 1 : 0; }
+extern "C" void idm_gemm_set_persistent(int on) { g_gemm_persistent = on ? 1 : 0; }
 
 template <int EPI>
 static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, int M, int N, int K, int splits,
@@ -562,6 +725,15 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, i
         e.ws = workspace ? workspace + GT_COUNTER_SLOTS : nullptr;
     }
     CUtensorMap mw, mx;
+    if (splits == 1 && M > 256 && g_gemm_persistent) {
+        // many tokens: the persistent kernel; 256-token tiles unless 128 fill more of the SMs
+        const int tiles_x = (N + GT_BM - 1) / GT_BM;
+        const bool wide = (long long)tiles_x * ((M + 255) / 256) >= 120;
+        if (make_map(&mw, w, N, K, GT_BM)) return 1;
+        if (make_map(&mx, x, M, K, wide ? 256 : 128)) return 1;
+        return wide ? launch_persistent<256, 4, EPI>(mw, mx, e, M, N, kb_total, stream)
+                    : launch_persistent<128, 6, EPI>(mw, mx, e, M, N, kb_total, stream);
+    }
     const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     if (make_map(&mw, w, N, K, GT_BM)) return 1;
     if (make_map(&mx, x, M, K, bn)) return 1;
@@ -630,7 +802,7 @@ extern "C" int idm_gemm_bf16_qkv(const void* x, const void* w, float* workspace,
     a.q_out = (T*)q_out; a.k_new = (T*)k_new; a.v_new = (T*)v_new;
     a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
     a.write_cache = k_pool != nullptr;
-    a.token_seq = token_seq; a.positions = positions; a.slots = slots;
+    a.token_seq = token_seq; a.positions = positions; a.slots = slots; a.tiles4 = 0;
     return gemm_any<EPI_QKV>(x, w, e, workspace, M, (n_q + 2 * n_kv) * hd, K, splits, stream);
 }
 

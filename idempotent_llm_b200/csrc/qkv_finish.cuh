@@ -9,6 +9,15 @@
 
 #include "common.cuh"
 
+// four consecutive elements, one store
+__device__ __forceinline__ void store4(float* p, const float (&x)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&x)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1]), b = __floats2bfloat162_rn(x[2], x[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
 struct QkvArgs {
     const float* qkv; int n_partials; size_t partial_stride;
     int n_tokens, n_q, n_kv, hd;
@@ -17,6 +26,7 @@ struct QkvArgs {
     T* q_out; T* k_new; T* v_new;
     KVAddr cache; int write_cache;
     const int* token_seq; const int* positions; const int* slots;
+    int tiles4;               // the separate kernel: 1 = work on tiles of 128 features, four per lane
 };
 
 // where the token's key/value row of kv-head g starts in the pools
@@ -80,5 +90,57 @@ __device__ __forceinline__ void qkv_finish_row(const QkvArgs& a, int t, int head
             if (dst_a) { from_f32(dst_a[j], u); from_f32(dst_a[j + half], w); }
             if (dst_b) { from_f32(dst_b[j], u); from_f32(dst_b[j + half], w); }
         }
+    }
+}
+
+// The same for a tile of 128 consecutive features of the projection (whole heads: 128 % head_dim == 0)
+// held by one warp, four consecutive features per lane (lane l: features f0 + 4 l .. + 3): norm over
+// each head's lanes, rotation partner by shuffle, 8-byte stores.  page / prow: the token's place in
+// the cache (page number, row inside the page).  Every lane of the warp must call it.
+__device__ __forceinline__ void qkv_finish_tile4(const QkvArgs& a, float4 v, int t, int f0, int lane, int page, int prow) {
+    const int lph = a.hd >> 2;                        // lanes per head (a power of two)
+    const int head = f0 / a.hd + lane / lph, li = lane % lph;
+    const int heads = a.n_q + 2 * a.n_kv, half = a.hd >> 1;
+    const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv, live = head < heads;
+    const float* gamma = is_q ? a.gq : (is_k ? a.gk : nullptr);
+    float x[4] = {v.x, v.y, v.z, v.w};
+    const int d = li * 4;                             // first of this lane's dims within the head
+    // (every lane runs the shuffles, whatever its head is: they are warp-wide)
+    float ss = __fmaf_rn(x[3], x[3], __fmaf_rn(x[2], x[2], __fmaf_rn(x[1], x[1], __fmul_rn(x[0], x[0]))));
+    for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (live && gamma != nullptr) {
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.hd), a.eps)));
+        const float4 gm = *reinterpret_cast<const float4*>(gamma + d);
+        x[0] = __fmul_rn(__fmul_rn(x[0], inv), gm.x); x[1] = __fmul_rn(__fmul_rn(x[1], inv), gm.y);
+        x[2] = __fmul_rn(__fmul_rn(x[2], inv), gm.z); x[3] = __fmul_rn(__fmul_rn(x[3], inv), gm.w);
+    }
+    float other[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) other[i] = __shfl_xor_sync(0xffffffffu, x[i], lph >> 1);   // the rotation partner
+    if (live && (is_q || is_k) && a.cs != nullptr) {
+        const bool first = li < (lph >> 1);           // dims below head_dim / 2
+        const int j = first ? d : d - half;
+        const float4* c4 = reinterpret_cast<const float4*>(a.cs + (size_t)t * half + j);   // (cos, sin) of 4 dims
+        const float4 ca = c4[0], cb = c4[1];
+        const float cs_[4][2] = {{ca.x, ca.y}, {ca.z, ca.w}, {cb.x, cb.y}, {cb.z, cb.w}};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            x[i] = first ? __fmaf_rn(x[i], cs_[i][0], -__fmul_rn(other[i], cs_[i][1]))
+                         : __fmaf_rn(x[i], cs_[i][0], __fmul_rn(other[i], cs_[i][1]));
+    }
+    if (live) {
+        T* dst_a = nullptr; T* dst_b = nullptr;
+        if (is_q) {
+            dst_a = a.q_out + ((size_t)t * a.n_q + head) * a.hd + d;
+        } else {
+            const int g = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
+            if (a.write_cache)
+                dst_a = (is_k ? a.cache.k : a.cache.v) +
+                        (((size_t)page * a.n_kv + g) * IDM_PAGE + prow) * (size_t)a.hd + d;
+            T* packed = is_k ? a.k_new : a.v_new;
+            if (packed) dst_b = packed + ((size_t)t * a.n_kv + g) * a.hd + d;
+        }
+        if (dst_a) store4(dst_a, x);
+        if (dst_b) store4(dst_b, x);
     }
 }

@@ -325,7 +325,7 @@ def test_gemm_bfloat16(kernels, impl, M, N, K_):
 
 
 @pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (8, 1024, 2048), (64, 1024, 3072), (200, 512, 1024), (300, 384, 136),
-                                    (2048, 1024, 1024), (5, 151936, 64)])
+                                    (2048, 1024, 1024), (5, 151936, 64), (1030, 4096, 192), (700, 16000, 72)])
 def test_gemm_fused_store_and_residual(kernels, M, N, K_):
     K = kernels("bfloat16")
     x, w = _randn(M, K_, seed=74).bfloat16(), _randn(N, K_, seed=75).bfloat16()
@@ -347,7 +347,8 @@ def test_gemm_fused_store_and_residual(kernels, M, N, K_):
     assert K.gemm_status() == 0
 
 
-@pytest.mark.parametrize("M,inter,K_", [(1, 128, 64), (8, 3072, 1024), (7, 224, 96), (130, 136, 80), (2048, 288, 160)])
+@pytest.mark.parametrize("M,inter,K_", [(1, 128, 64), (8, 3072, 1024), (7, 224, 96), (130, 136, 80), (2048, 288, 160),
+                                        (1030, 2000, 192)])
 def test_gemm_fused_swiglu(kernels, M, inter, K_):
     K = kernels("bfloat16")
     x = _randn(M, K_, seed=77).bfloat16()
@@ -364,7 +365,8 @@ def test_gemm_fused_swiglu(kernels, M, inter, K_):
 
 
 @pytest.mark.parametrize("M,n_q,n_kv,hd,hidden", [(3, 6, 2, 32, 96), (70, 4, 2, 16, 64), (9, 16, 8, 128, 1024),
-                                                  (300, 8, 2, 128, 160), (64, 2, 1, 64, 72)])
+                                                  (300, 8, 2, 128, 160), (64, 2, 1, 64, 72), (1030, 24, 4, 128, 192),
+                                                  (520, 40, 12, 64, 136)])
 def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, hidden):
     K = kernels("bfloat16")
     starts, lens = [5, 64], [M // 2, M - M // 2]
@@ -372,7 +374,7 @@ def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, 
         starts, lens = [5], [M]
 
     def run(fused):
-        cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, 64 * 16, torch.bfloat16, "cuda:0", max_seqs=4)
+        cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, 64 * 32, torch.bfloat16, "cuda:0", max_seqs=4)
         slots = [cache.alloc_slot() for _ in lens]
         cache.reserve([(s_, st + L) for s_, st, L in zip(slots, starts, lens)]); cache.flush()
         packed, n, q_lens = pack_step_host(slots, starts, [[0] * L for L in lens])
@@ -391,12 +393,11 @@ def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, 
         return q, kn, vn, kv.k.clone(), kv.v.clone()
     a, b = run(True), run(False)
     for t_a, t_b, name in zip(a, b, ("q", "k_new", "v_new", "cache k", "cache v")):
-        if M <= 64:
-            # up to 64 tokens the slices are added inside a cluster and a row's sum of squares is taken
-            # four elements per lane: the same numbers added in another order
-            assert helpers.rel_err(t_a, t_b) < KTOL["bfloat16"], name
-        else:
-            assert torch.equal(t_a, t_b), name
+        # the same numbers; a row's sum of squares may be added in another order (four elements per
+        # lane in the separate kernel and in the cluster path, strided pairs in the tile epilogues)
+        assert helpers.rel_err(t_a, t_b) < KTOL["bfloat16"], name
+        if M <= 64 and 128 % hd == 0:
+            assert torch.equal(t_a, t_b), name + ": up to 64 tokens both paths finish rows the same way"
     assert K.gemm_status() == 0
 
 
