@@ -247,7 +247,8 @@ extern "C" int idm_kv_write_ring(const void* k_new, const void* v_new, void* k_p
 // ---------------------------------------------------------------------- SwiGLU
 // y[t, i] = g * sigmoid(g) * u  (src/detllm/ops/di_swiglu.py:43-45; float form tests/test_ops.py:240-242).
 // Plain layout: g = gu[t, i], u = gu[t, inter + i].  Tiled layout (the gate/up weight's rows in tiles
-// of 64 gate + 64 up rows): g = gu[t, 128 (i / 64) + i % 64], u = 64 further.
+// alternating: gate row of a feature, then its up row; 64 features per 128-row tile, zero rows past
+// the end): g = gu[t, 128 (i / 64) + 2 (i % 64)], u = the next column.
 // grid (column blocks, tokens): no division by a runtime size per element.
 __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ gu, int n_partials, size_t partial_stride,
                                                      T* __restrict__ y, int inter, int width, int tiled) {
@@ -256,8 +257,8 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ g
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= inter) return;
     const size_t t = blockIdx.y;
-    const int gi = tiled ? ((c >> 6) << 7) + (c & 63) : c;
-    const int ui = tiled ? gi + 64 : c + inter;
+    const int gi = tiled ? ((c >> 6) << 7) + 2 * (c & 63) : c;
+    const int ui = tiled ? gi + 1 : c + inter;
     const size_t base = t * (size_t)width;
     const float g = add_partials(0.f, gu, n_partials, partial_stride, base + gi);
     const float u = add_partials(0.f, gu, n_partials, partial_stride, base + ui);

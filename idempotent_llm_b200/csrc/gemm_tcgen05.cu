@@ -19,8 +19,8 @@
 //
 // Epilogues.  PARTIAL stores each K-slice's 32-bit tile to out[p].  The fused epilogues produce the
 // finished result inside the kernel: STORE (32-bit [M, N]), RESIDUAL (h[t, f] += result, the
-// 32-bit residual sum), SWIGLU (bfloat16 y = silu(gate) * up; the weight's rows are tiled so that
-// a 128-row tile holds 64 gate rows followed by the 64 up rows of the same features) and QKV (per-head
+// 32-bit residual sum), SWIGLU (bfloat16 y = silu(gate) * up; the weight's rows alternate: gate row
+// of a feature, then its up row, so a 128-row tile holds 64 features) and QKV (per-head
 // q/k norm, rotation, q out and cache write; a tile of 128 features must hold whole heads).  With K
 // split, every slice writes its tile to a workspace and the block that arrives last for the tile
 // (a counter it sets back to zero) adds the slices in ascending order and runs the epilogue, so the
@@ -86,17 +86,11 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, float4 v, int t, 
             *p = v;
         }
     } else if (EPI == EPI_SWIGLU) {
-        // lanes 0..15 hold gate features 4 lane .. 4 lane + 3 of this tile, lanes 16..31 the up rows of the same
-        const float ux = __shfl_down_sync(0xffffffffu, v.x, 16), uy = __shfl_down_sync(0xffffffffu, v.y, 16);
-        const float uz = __shfl_down_sync(0xffffffffu, v.z, 16), uw = __shfl_down_sync(0xffffffffu, v.w, 16);
-        if (lane < 16) {
-            const int fg = tile_x * 64 + lane * 4;
-            T* y = e.y + (size_t)t * e.inter + fg;
-            if (fg + 0 < e.inter) from_f32(y[0], silu_mul(v.x, ux));
-            if (fg + 1 < e.inter) from_f32(y[1], silu_mul(v.y, uy));
-            if (fg + 2 < e.inter) from_f32(y[2], silu_mul(v.z, uz));
-            if (fg + 3 < e.inter) from_f32(y[3], silu_mul(v.w, uw));
-        }
+        // a lane's four features of the tile are gate, up, gate, up of two features of y
+        const int fg = tile_x * 64 + lane * 2;
+        T* y = e.y + (size_t)t * e.inter + fg;
+        if (fg + 0 < e.inter) from_f32(y[0], silu_mul(v.x, v.y));
+        if (fg + 1 < e.inter) from_f32(y[1], silu_mul(v.z, v.w));
     } else if (EPI == EPI_QKV) {
         qkv_finish_tile4(e.q, v, t, f0, lane, meta_row[0], meta_row[1]);
     }
@@ -359,11 +353,11 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
                             }
                         }
                     } else if (EPI == EPI_SWIGLU) {
-                        // lanes 64..127 of the tile hold the up rows of the features whose gate rows lanes 0..63 hold
+                        // rows 2 i and 2 i + 1 of the tile are the gate and up rows of feature i of this tile's 64
                         const int fg = blockIdx.x * 64 + (fl & 63);                // the feature of y
                         if (fg < e.inter)
                             for (int t = fl >> 6; t < cols; t += 2) {                  // two token rows at a time
-                                const float g = xs[t * GT_BM + (fl & 63)], u = xs[t * GT_BM + 64 + (fl & 63)];
+                                const float g = xs[t * GT_BM + 2 * (fl & 63)], u = xs[t * GT_BM + 2 * (fl & 63) + 1];
                                 from_f32(e.y[(size_t)(t0 + t) * e.inter + fg], silu_mul(g, u));
                             }
                     } else if (EPI == EPI_QKV) {
@@ -549,7 +543,34 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_persistent_kernel(const __gri
                 float v[32];
                 tc_ld16(tmem + acc * BN + lane_base + (uint32_t)c0, v);
                 tc_ld16(tmem + acc * BN + lane_base + (uint32_t)c0 + 16, v + 16);
-                if (EPI == EPI_PARTIAL || EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+                if (EPI == EPI_SWIGLU) {
+                    // through shared memory, so that a thread ends up with 8 consecutive features of one
+                    // token (16 consecutive tile rows: gate, up, gate, up, ...) and writes them with one
+                    // 16-byte store; a warp covers four whole token rows of the tile
+                    const int cols = min(32, n_tokens - t0 - c0);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) xs[j * GT_BM + fl] = v[j];
+                    epi_sync();
+                    for (int item = fl; item < cols * 8; item += 128) {
+                        const int j = item >> 3, grp = item & 7;
+                        const float4* src = reinterpret_cast<const float4*>(xs + j * GT_BM + grp * 16);
+                        const float4 p0 = src[0], p1 = src[1], p2 = src[2], p3 = src[3];
+                        const float y8[8] = {silu_mul(p0.x, p0.y), silu_mul(p0.z, p0.w), silu_mul(p1.x, p1.y), silu_mul(p1.z, p1.w),
+                                             silu_mul(p2.x, p2.y), silu_mul(p2.z, p2.w), silu_mul(p3.x, p3.y), silu_mul(p3.z, p3.w)};
+                        const int fg = tx * 64 + grp * 8;
+                        T* dst = e.y + (size_t)(t0 + c0 + j) * e.inter + fg;
+                        if ((e.inter & 7) == 0 && fg + 8 <= e.inter) {
+                            const float lo4[4] = {y8[0], y8[1], y8[2], y8[3]}, hi4[4] = {y8[4], y8[5], y8[6], y8[7]};
+                            store4(dst, lo4);
+                            store4(dst + 4, hi4);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if (fg + i < e.inter) from_f32(dst[i], y8[i]);
+                        }
+                    }
+                    epi_sync();
+                } else if (EPI == EPI_PARTIAL || EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
                     if (f < n_features) {
                         float old[32];
                         if (EPI == EPI_RESIDUAL) {
@@ -567,14 +588,7 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_persistent_kernel(const __gri
 #pragma unroll
                     for (int j = 0; j < 32; ++j) xs[j * GT_BM + fl] = v[j];
                     epi_sync();
-                    if (EPI == EPI_SWIGLU) {
-                        const int fg = tx * 64 + (fl & 63);
-                        if (fg < e.inter)
-                            for (int j = fl >> 6; j < cols; j += 2) {
-                                const float g = xs[j * GT_BM + (fl & 63)], u = xs[j * GT_BM + 64 + (fl & 63)];
-                                from_f32(e.y[(size_t)(t0 + c0 + j) * e.inter + fg], silu_mul(g, u));
-                            }
-                    } else if (EPI == EPI_QKV) {
+                    if (EPI == EPI_QKV) {
                         const int hpt = GT_BM / e.q.hd, heads = e.q.n_q + 2 * e.q.n_kv;
                         for (int row = warp; row < cols * hpt; row += 4) {
                             const int c = row / hpt, hh = row % hpt;
@@ -777,8 +791,8 @@ extern "C" int idm_gemm_bf16_residual(const void* x, const void* w, float* h, fl
     return gemm_any<EPI_RESIDUAL>(x, w, e, workspace, M, N, K, splits, stream);
 }
 
-// y [M, inter] = silu(x . gate^T) * (x . up^T); w_tiled [tiles * 128, K]: tile j = gate rows 64j..64j+63,
-// then up rows 64j..64j+63 (rows past `inter` are zero)
+// y [M, inter] = silu(x . gate^T) * (x . up^T); w_tiled [tiles * 128, K]: rows 128 j + 2 i and 128 j + 2 i + 1
+// are the gate and the up row of feature 64 j + i (rows past `inter` are zero)
 extern "C" int idm_gemm_bf16_swiglu(const void* x, const void* w_tiled, void* y, float* workspace, int M, int inter,
                                     int K, int splits, cudaStream_t stream) {
     GemmEpi e = {};

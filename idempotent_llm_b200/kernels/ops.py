@@ -347,16 +347,13 @@ class Kernels:
                                                         self._stream()))
 
     def tile_gate_up(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
-        """Rows of gate and up interleaved in tiles of 64 + 64 (zero rows past the end), the layout
-        ``gemm_swiglu`` reads."""
+        """Rows of gate and up alternating (gate row of a feature, then its up row), padded with zero
+        rows to whole tiles of 64 features = 128 rows: the layout ``gemm_swiglu`` reads."""
         inter, Kd = gate.shape
         tiles = -(-inter // 64)
-        out = torch.zeros((tiles, 2, 64, Kd), dtype=gate.dtype, device=gate.device)
-        pad = tiles * 64 - inter
-        g = torch.nn.functional.pad(gate, (0, 0, 0, pad)) if pad else gate
-        u = torch.nn.functional.pad(up, (0, 0, 0, pad)) if pad else up
-        out[:, 0] = g.view(tiles, 64, Kd)
-        out[:, 1] = u.view(tiles, 64, Kd)
+        out = torch.zeros((tiles * 64, 2, Kd), dtype=gate.dtype, device=gate.device)
+        out[:inter, 0] = gate
+        out[:inter, 1] = up
         return out.view(tiles * 128, Kd).contiguous()
 
     def gemm_swiglu(self, x, w_tiled, inter: int) -> torch.Tensor:
