@@ -7,9 +7,14 @@ library's message when a launch is refused.  There is no CPU path: constructing
 ``Kernels`` without a CUDA device raises.
 
 Matrix products: the 32-bit library has its own FMA kernel (no tensor cores, no
-reduced-precision mode).  In bfloat16 the product goes to the library GEMM that
-torch wraps (cuBLASLt), as the reference sends every matrix product to
-``torch._int_mm`` (src/detllm/backends.py:88-135); outputs are 32-bit.
+reduced-precision mode).  In bfloat16 they run on the hand-written tcgen05
+kernels of ``csrc/gemm_tcgen05.cu`` (the reference sends every matrix product to
+a library, ``torch._int_mm``, src/detllm/backends.py:88-135); ``IDM_GEMM=library``
+switches to the GEMM torch wraps, which is kept only to compare against.
+
+Environment switches (all default to the fast path): ``IDM_GEMM``, ``IDM_FUSED``,
+``IDM_FUSED_MIN_TOKENS``, ``IDM_FUSED_MAX_SMALL``, ``IDM_PREFILL``, ``IDM_PDL``,
+``IDM_PDL_ATTN``, ``IDM_DECODE_MMA``.
 """
 
 from __future__ import annotations
