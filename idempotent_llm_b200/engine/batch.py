@@ -9,8 +9,9 @@ enters the computation.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List
+from typing import Dict, List, Sequence
 
+import numpy as np
 import torch
 
 
@@ -34,35 +35,36 @@ class StepContext:
     memo: Dict = field(default_factory=dict)   # per-step shared tables (position encodings)
 
 
-def pack_step_host(slots: List[int], starts: List[int], token_lists: List[List[int]]):
+def pack_step_host(slots: List[int], starts: List[int], token_lists: List[List[int]],
+                   extra: Sequence[int] = ()):
     """Host-side packing: returns one int32 tensor holding, back to back,
-    tokens[N], token_seq[N], positions[N], cu_q[S+1], slots[S], q_start[S], kv_len[S]."""
+    tokens[N], token_seq[N], positions[N], cu_q[S+1], slots[S], q_start[S], kv_len[S]
+    and then ``extra`` (the step's wanted rows), plus N and the sequences' token counts."""
     n_seq = len(slots)
     q_lens = [len(t) for t in token_lists]
     n = sum(q_lens)
-    buf = torch.empty(3 * n + 4 * n_seq + 1, dtype=torch.int32)
-    toks = buf[0:n]
-    tseq = buf[n:2 * n]
-    pos = buf[2 * n:3 * n]
     o = 3 * n
-    cu = buf[o:o + n_seq + 1]
-    sl = buf[o + n_seq + 1:o + 2 * n_seq + 1]
-    qs = buf[o + 2 * n_seq + 1:o + 3 * n_seq + 1]
-    kl = buf[o + 3 * n_seq + 1:o + 4 * n_seq + 1]
-    off = 0
-    cu[0] = 0
-    for i, (t, st) in enumerate(zip(token_lists, starts)):
-        L = len(t)
-        if L:
-            toks[off:off + L] = torch.as_tensor(t, dtype=torch.int32)
-            tseq[off:off + L] = i
-            pos[off:off + L] = torch.arange(st, st + L, dtype=torch.int32)
-        off += L
-        cu[i + 1] = off
-        sl[i] = slots[i]
-        qs[i] = st
-        kl[i] = st + L
-    return buf, n, q_lens
+    buf = np.empty(o + 4 * n_seq + 1 + len(extra), dtype=np.int32)
+    st = np.asarray(starts, dtype=np.int32).reshape(n_seq)
+    ql = np.asarray(q_lens, dtype=np.int32).reshape(n_seq)
+    if n == n_seq and (n_seq == 0 or min(q_lens) == 1):            # one token each
+        buf[0:n] = [t[0] for t in token_lists]
+        buf[n:2 * n] = np.arange(n_seq, dtype=np.int32)
+        buf[2 * n:o] = st
+    elif n:
+        buf[0:n] = np.concatenate([np.asarray(t, dtype=np.int64).reshape(-1) for t in token_lists])
+        seq_of = np.repeat(np.arange(n_seq, dtype=np.int32), ql)
+        first = np.concatenate([[0], np.cumsum(ql)[:-1]]).astype(np.int32)
+        buf[n:2 * n] = seq_of
+        buf[2 * n:o] = np.arange(n, dtype=np.int32) - first[seq_of] + st[seq_of]
+    buf[o] = 0
+    buf[o + 1:o + n_seq + 1] = np.cumsum(ql)
+    buf[o + n_seq + 1:o + 2 * n_seq + 1] = slots
+    buf[o + 2 * n_seq + 1:o + 3 * n_seq + 1] = st
+    buf[o + 3 * n_seq + 1:o + 4 * n_seq + 1] = st + ql
+    if len(extra):
+        buf[o + 4 * n_seq + 1:] = extra
+    return torch.from_numpy(buf), n, q_lens
 
 
 def context_from_packed(dev_buf: torch.Tensor, n: int, slots: List[int], q_lens: List[int],

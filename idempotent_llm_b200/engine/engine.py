@@ -75,8 +75,7 @@ class DecodeSession:
         self.starts = [cache.length(s) for s in self.slots]
         cache.reserve([(s, st + max_steps) for s, st in zip(self.slots, self.starts)])
         cache.flush()
-        packed, n, q_lens = pack_step_host(self.slots, self.starts, [[int(t)] for t in first_tokens])
-        full = torch.cat([packed, torch.arange(B, dtype=torch.int32)])
+        full, n, q_lens = pack_step_host(self.slots, self.starts, [[int(t)] for t in first_tokens], extra=range(B))
         self.dev = full.to(dev)
         self.history = torch.zeros((max_steps, B), dtype=torch.int32, device=dev)
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -169,8 +168,8 @@ class Engine:
         for s, t in zip(slots, toks):
             if not t:
                 raise ValueError(f"slot {s} brings no token")
-            bad = [x for x in t if not 0 <= x < V]
-            if bad:
+            if min(t) < 0 or max(t) >= V:
+                bad = [x for x in t if not 0 <= x < V]
                 raise ValueError(f"token id {bad[0]} is outside the vocabulary [0, {V})")
         if want is None:
             want = [[len(t) - 1] for t in toks]
@@ -185,14 +184,14 @@ class Engine:
             off += len(t)
         starts = [self.cache.length(s) for s in slots]
         self.cache.reserve([(s, st + len(t)) for s, st, t in zip(slots, starts, toks)])
-        packed, n, q_lens = pack_step_host(slots, starts, toks)
+        single = all(len(t) == 1 for t in toks)
+        graphed = single and self.use_graph and getattr(self.model, "graph_safe", True)
+        full, n, q_lens = pack_step_host(slots, starts, toks, extra=range(len(slots)) if graphed else rows)
         self.cache.flush()
-        single = all(q == 1 for q in q_lens)
-        if single and self.use_graph and getattr(self.model, "graph_safe", True):
+        if graphed:
             g = self._graphs.get(len(slots))
             if g is None:
                 g = self._graphs[len(slots)] = _DecodeGraph(self, len(slots))
-            full = torch.cat([packed, torch.arange(len(slots), dtype=torch.int32)])
             logits = g.run(self, full, slots, q_lens, starts)
             # the graph writes its logits into the same buffer at every replay: hand out a copy
             if rows == list(range(len(slots))):
@@ -201,10 +200,9 @@ class Engine:
                 logits = logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows \
                     else logits[:0].clone()
         else:
-            full = torch.cat([packed, torch.tensor(rows, dtype=torch.int32)])
             dev = self._upload(full)
             ctx = context_from_packed(dev, n, slots, q_lens, starts)
-            logits = self.model.forward(ctx, self.cache, dev[packed.numel():])
+            logits = self.model.forward(ctx, self.cache, dev[full.numel() - len(rows):])
         for s, st, t in zip(slots, starts, toks):
             self.cache.set_length(s, st + len(t))
         self.steps_run += 1
