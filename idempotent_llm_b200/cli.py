@@ -236,6 +236,35 @@ def cmd_kernel_bench(args) -> int:
             fl, byt = 2.0 * args.tokens * N * Kd, 2.0 * N * Kd
             print(f"gemm {name} [{args.tokens} x {Kd}] . [{N} x {Kd}]^T: {t * 1e6:.1f} us, {fl / t / 1e12:.1f} TFLOP/s, "
                   f"weights {byt / t / 1e9:.0f} GB/s")
+    elif args.kernel == "gemm_fused":
+        # the four products of a layer with their fused epilogues, as the parts call them
+        from .engine.batch import context_from_packed, pack_step_host
+        M = args.tokens
+        cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, -(-M // 64) * 64 + 64, torch.bfloat16, "cuda:0",
+                              max_seqs=1, max_seq_len=-(-M // 64) * 64 + 64)
+        slot = cache.alloc_slot()
+        cache.reserve([(slot, M)]); cache.flush()
+        packed, n, q_lens = pack_step_host([slot], [0], [[0] * M])
+        ctx = context_from_packed(packed.cuda(), n, [slot], q_lens, [0])
+        kv = cache.view(0)
+        rnd = lambda *shape: (torch.randn(*shape, device="cuda") * 0.05).bfloat16()
+        x, xo, xi = rnd(M, H) * 20, rnd(M, n_q * hd) * 20, rnd(M, I) * 20
+        w_qkv, w_o, w_down = rnd((n_q + 2 * n_kv) * hd, H), rnd(H, n_q * hd), rnd(H, I)
+        w_gu = K.tile_gate_up(rnd(I, H), rnd(I, H))
+        gq = torch.ones(hd, device="cuda"); gk = torch.ones(hd, device="cuda")
+        inv = 1e6 ** (-2.0 * torch.arange(0, hd // 2, dtype=torch.float64) / hd)
+        cs = K.rope_table(ctx.positions, inv.cuda())
+        h = torch.zeros(M, H, device="cuda")
+        runs = {"qkv (norm, rotation, cache write)": (lambda: K.gemm_qkv(x, w_qkv, n_q, n_kv, hd, gq, gk, 1e-6, cs, ctx, kv,
+                                                                           keep_new=False), (n_q + 2 * n_kv) * hd, H),
+                "o (residual add)": (lambda: K.gemm_residual(xo, w_o, h), H, n_q * hd),
+                "gate_up (SwiGLU)": (lambda: K.gemm_swiglu(x, w_gu, I), 2 * I, H),
+                "down (residual add)": (lambda: K.gemm_residual(xi, w_down, h), H, I)}
+        for name, (fn, N, Kd) in runs.items():
+            t = timed(fn)
+            fl, byt = 2.0 * M * N * Kd, 2.0 * N * Kd
+            print(f"gemm {name} [{M} x {Kd}] . [{N} x {Kd}]^T: {t * 1e6:.1f} us, {fl / t / 1e12:.1f} TFLOP/s, "
+                  f"weights {byt / t / 1e9:.0f} GB/s")
     else:
         raise ValueError(f"unknown kernel {args.kernel!r}")
     return 0
@@ -308,7 +337,7 @@ def main(argv=None) -> int:
     r.set_defaults(fn=cmd_random)
 
     k = sub.add_parser("kernel-bench", help="one kernel alone at a preset's layer sizes")
-    k.add_argument("--kernel", required=True, choices=["attention_decode", "attention_prefill", "gemm"])
+    k.add_argument("--kernel", required=True, choices=["attention_decode", "attention_prefill", "gemm", "gemm_fused"])
     k.add_argument("--size", default="qwen3-0.6b")
     k.add_argument("--batch", type=int, default=8)
     k.add_argument("--context", type=int, default=3000)

@@ -200,7 +200,7 @@ extern "C" int idm_qkv_finish(const float* qkv, int n_partials, long long partia
     QkvArgs a;
     a.qkv = qkv; a.n_partials = n_partials; a.partial_stride = (size_t)partial_stride;
     a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd;
-    a.gq = gq; a.gk = gk; a.eps = eps; a.cs = (const float2*)cs;
+    a.gq = gq; a.gk = gk; a.eps = eps; a.inv_hd = 1.0f / (float)hd; a.cs = (const float2*)cs;
     a.q_out = (T*)q_out; a.k_new = (T*)k_new; a.v_new = (T*)v_new;
     a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
     a.write_cache = k_pool != nullptr;

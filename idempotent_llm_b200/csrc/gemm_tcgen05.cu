@@ -416,27 +416,40 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
 // ------------------------------------------------------------------- persistent kernel (many tokens)
 // Above 256 tokens nothing is split and the product is bound by the tensor cores.  One block per SM
 // walks over output tiles of 128 features x BN tokens (BN = 256, or 128 when that fills more SMs):
-//   * warp 4 keeps the TMA ring full across tile borders;
-//   * warp 5 issues the MMAs into one of TWO accumulators in tensor memory (2 x BN columns);
-//   * warps 0-3 run the epilogue of the finished accumulator while the next tile's MMAs run.
+//   * warp 16 keeps the TMA ring full across tile borders;
+//   * warp 17 issues the MMAs into one of TWO accumulators in tensor memory (2 x BN columns);
+//   * warps 0-15 run the epilogue of the finished accumulator while the next tile's MMAs run: four
+//     groups of four warps (a warp reads the 32 accumulator lanes of its number modulo 4), which take
+//     the tile's chunks of 16 tokens in turn -- four warps per scheduler hide each other's latencies;
+//     with one group the q/k/v epilogue took three times as long as the tile's MMAs.
 // A 128 x 256 tile reads 12 KB of shared memory per 128 tensor-core cycles (128 x 128 reads 8 KB per
-// 64, the whole shared-memory bandwidth).  The fused epilogues work on chunks of 32 tokens through a
-// 16 KB buffer of their own, as the ring is never idle here.
+// 64, the whole shared-memory bandwidth).  The SwiGLU and q/k/v epilogues turn each chunk through an
+// 8 KB buffer per group (the ring is never idle here), so that a thread ends up with consecutive
+// features of one token.
+#define GP_GROUPS 4
+#define GP_EPI_WARPS (4 * GP_GROUPS)
+#define GP_THREADS (32 * (GP_EPI_WARPS + 2))
+#define GP_CHUNK 16
 template <int BN, int STAGES>
 struct PersistSmem {
     static constexpr int A_BYTES = GT_BM * GT_BK * 2;
     static constexpr int B_BYTES = BN * GT_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int XS_BYTES = 32 * GT_BM * 4;                // [32 tokens][128 features] floats
-    static constexpr int META_BYTES = BN * 8;                      // per token: page, row
+    static constexpr int XS_BYTES = GP_GROUPS * GP_CHUNK * GT_BM * 4;   // per group: [16 tokens][128 features] floats
+    static constexpr int META_BYTES = BN * 4;                      // per token: page * 64 + row
     static constexpr int XS_OFF = STAGES * STAGE_BYTES;
     static constexpr int META_OFF = XS_OFF + XS_BYTES;
     static constexpr int BAR_OFF = META_OFF + META_BYTES;
     static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
+__device__ __forceinline__ void group_sync(int g) { asm volatile("bar.sync %0, 128;" ::"r"(1 + g) : "memory"); }     // one group
+__device__ __forceinline__ void groups_sync() {                                                                      // all epilogue warps
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + GP_GROUPS), "r"(32 * GP_EPI_WARPS) : "memory");
+}
+
 template <int BN, int STAGES, int EPI>
-__global__ void __launch_bounds__(GT_THREADS) gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                      const __grid_constant__ CUtensorMap map_x,
                                                                      const GemmEpi e, int n_tokens, int n_features,
                                                                      int kb_total, int tiles_x, int n_tiles) {
@@ -457,18 +470,18 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_persistent_kernel(const __gri
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), GP_EPI_WARPS); }
         *abort_flag = 0;
         mbar_init_fence();
     }
-    if (warp == 5) tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+    if (warp == GP_EPI_WARPS + 1) tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     pdl_wait();
 
-    if (warp == 4) {
+    if (warp == GP_EPI_WARPS) {
         if (lane == 0) {
             uint32_t cnt = 0;                                      // k-blocks issued so far, over all tiles
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
@@ -486,7 +499,7 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_persistent_kernel(const __gri
                 if (!ok) break;
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == GP_EPI_WARPS + 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(GT_BM, BN);
             uint32_t cnt = 0, it = 0;
@@ -513,97 +526,123 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_persistent_kernel(const __gri
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
-        float* xs = (float*)(gen_base + S::XS_OFF);
+        const int quarter = warp & 3, grp = warp >> 2;             // accumulator lanes 32 quarter ..; group 0 or 1
+        float* xs = (float*)(gen_base + S::XS_OFF) + grp * (GP_CHUNK * GT_BM);
         int* meta = (int*)(gen_base + S::META_OFF);
-        const int fl = warp * 32 + lane;
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const int fl = quarter * 32 + lane;                        // feature within the tile = accumulator lane
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         uint32_t it = 0;
         bool ok = true;
+        Tile4Lane tl4 = {};
+        if (EPI == EPI_QKV) tl4 = qkv_tile4_lane(e.q, lane);
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
             const int tx = tile % tiles_x, f0 = tx * GT_BM, t0 = (tile / tiles_x) * BN;
             const int f = f0 + fl;
             const uint32_t acc = it & 1;
             if (EPI == EPI_QKV && e.q.write_cache) {
-                epi_sync();                                        // the previous tile's readers of meta are done
-                for (int tl = fl; tl < BN; tl += 128)
+                groups_sync();                                     // the previous tile's readers of meta are done
+                for (int tl = threadIdx.x; tl < BN; tl += 32 * GP_EPI_WARPS)
                     if (t0 + tl < n_tokens) {
                         const int t = t0 + tl;
                         const int pos = e.q.positions[t];
                         const int r = e.q.cache.ring ? pos % e.q.cache.ring : pos;
-                        meta[2 * tl] = e.q.cache.table[(size_t)e.q.slots[e.q.token_seq[t]] * e.q.cache.table_stride + r / IDM_PAGE];
-                        meta[2 * tl + 1] = r % IDM_PAGE;
+                        const int page = e.q.cache.table[(size_t)e.q.slots[e.q.token_seq[t]] * e.q.cache.table_stride + r / IDM_PAGE];
+                        meta[tl] = page * IDM_PAGE + r % IDM_PAGE;
                     }
+                groups_sync();
             }
             ok = mbar_wait(tfull_bar(acc), (it >> 1) & 1, abort_flag, &g_gemm_error);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (t0 + c0 >= n_tokens) break;                    // warp-uniform
-                float v[32];
-                tc_ld16(tmem + acc * BN + lane_base + (uint32_t)c0, v);
-                tc_ld16(tmem + acc * BN + lane_base + (uint32_t)c0 + 16, v + 16);
-                if (EPI == EPI_SWIGLU) {
-                    // through shared memory, so that a thread ends up with 8 consecutive features of one
-                    // token (16 consecutive tile rows: gate, up, gate, up, ...) and writes them with one
-                    // 16-byte store; a warp covers four whole token rows of the tile
-                    const int cols = min(32, n_tokens - t0 - c0);
+            for (int c0 = grp * GP_CHUNK; c0 < BN; c0 += GP_GROUPS * GP_CHUNK) {
+                if (t0 + c0 >= n_tokens) break;                    // uniform over the group
+                const int cols = min(GP_CHUNK, n_tokens - t0 - c0);
+                // q/k/v: the (cos, sin) of this warp's four token rows (rows quarter, quarter + 4, ...), asked for
+                // before anything else waits
+                float4 ca[GP_CHUNK / 4], cb[GP_CHUNK / 4];
+                if (EPI == EPI_QKV) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) xs[j * GT_BM + fl] = v[j];
-                    epi_sync();
-                    for (int item = fl; item < cols * 8; item += 128) {
-                        const int j = item >> 3, grp = item & 7;
-                        const float4* src = reinterpret_cast<const float4*>(xs + j * GT_BM + grp * 16);
-                        const float4 p0 = src[0], p1 = src[1], p2 = src[2], p3 = src[3];
-                        const float y8[8] = {silu_mul(p0.x, p0.y), silu_mul(p0.z, p0.w), silu_mul(p1.x, p1.y), silu_mul(p1.z, p1.w),
-                                             silu_mul(p2.x, p2.y), silu_mul(p2.z, p2.w), silu_mul(p3.x, p3.y), silu_mul(p3.z, p3.w)};
-                        const int fg = tx * 64 + grp * 8;
-                        T* dst = e.y + (size_t)(t0 + c0 + j) * e.inter + fg;
-                        if ((e.inter & 7) == 0 && fg + 8 <= e.inter) {
-                            const float lo4[4] = {y8[0], y8[1], y8[2], y8[3]}, hi4[4] = {y8[4], y8[5], y8[6], y8[7]};
-                            store4(dst, lo4);
-                            store4(dst + 4, hi4);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                if (fg + i < e.inter) from_f32(dst[i], y8[i]);
-                        }
+                    for (int r = 0; r < GP_CHUNK / 4; ++r) {
+                        ca[r] = cb[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        const int row = quarter + 4 * r;
+                        const float4* c4 = row < cols ? qkv_tile4_cs(e.q, tl4, t0 + c0 + row, f0, lane) : nullptr;
+                        if (c4) { ca[r] = __ldg(c4); cb[r] = __ldg(c4 + 1); }
                     }
-                    epi_sync();
-                } else if (EPI == EPI_PARTIAL || EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+                }
+                float v[GP_CHUNK];
+                tc_ld16(tmem + acc * BN + lane_base + (uint32_t)c0, v);
+                if (EPI == EPI_PARTIAL || EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
                     if (f < n_features) {
-                        float old[32];
+                        float old[GP_CHUNK];
                         if (EPI == EPI_RESIDUAL) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                old[j] = t0 + c0 + j < n_tokens ? e.out[(size_t)(t0 + c0 + j) * n_features + f] : 0.f;
+                            for (int j = 0; j < GP_CHUNK; ++j)
+                                old[j] = j < cols ? e.out[(size_t)(t0 + c0 + j) * n_features + f] : 0.f;
                         }
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (t0 + c0 + j < n_tokens)
+                        for (int j = 0; j < GP_CHUNK; ++j)
+                            if (j < cols)
                                 e.out[(size_t)(t0 + c0 + j) * n_features + f] = EPI == EPI_RESIDUAL ? old[j] + v[j] : v[j];
                     }
                 } else {
-                    const int cols = min(32, n_tokens - t0 - c0);
+                    // through shared memory, so that a thread ends up with consecutive features of one token
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) xs[j * GT_BM + fl] = v[j];
-                    epi_sync();
-                    if (EPI == EPI_QKV) {
-                        const int hpt = GT_BM / e.q.hd, heads = e.q.n_q + 2 * e.q.n_kv;
-                        for (int row = warp; row < cols * hpt; row += 4) {
-                            const int c = row / hpt, hh = row % hpt;
-                            const int head = f0 / e.q.hd + hh;
-                            if (head < heads) {
-                                const float* src = xs + c * GT_BM + hh * e.q.hd;
-                                const int page = meta[2 * (c0 + c)], prow = meta[2 * (c0 + c) + 1];
-                                qkv_finish_row(e.q, t0 + c0 + c, head, lane, [&](int j) { return src[j]; },
-                                               [&](int g) {
-                                                   return (((size_t)page * e.q.n_kv + g) * IDM_PAGE + prow) * (size_t)e.q.hd;
-                                               });
+                    for (int j = 0; j < GP_CHUNK; ++j) xs[j * GT_BM + fl] = v[j];
+                    group_sync(grp);
+                    if (EPI == EPI_SWIGLU) {
+                        // 8 consecutive features of y (16 tile rows: gate, up, gate, up, ...) per thread, one
+                        // 16-byte store; the group's 128 threads cover the chunk's 16 token rows
+                        const int j = fl >> 3, sub = fl & 7;
+                        if (j < cols) {
+                            const float4* src = reinterpret_cast<const float4*>(xs + j * GT_BM + sub * 16);
+                            const float4 p0 = src[0], p1 = src[1], p2 = src[2], p3 = src[3];
+                            const float y8[8] = {silu_mul(p0.x, p0.y), silu_mul(p0.z, p0.w), silu_mul(p1.x, p1.y), silu_mul(p1.z, p1.w),
+                                                 silu_mul(p2.x, p2.y), silu_mul(p2.z, p2.w), silu_mul(p3.x, p3.y), silu_mul(p3.z, p3.w)};
+                            const int fg = tx * 64 + sub * 8;
+                            T* dst = e.y + (size_t)(t0 + c0 + j) * e.inter + fg;
+                            if ((e.inter & 7) == 0 && fg + 8 <= e.inter) {
+                                store8(dst, y8);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    if (fg + i < e.inter) from_f32(dst[i], y8[i]);
                             }
                         }
+                    } else if (EPI == EPI_QKV && f0 >= (e.q.n_q + e.q.n_kv) * e.q.hd) {
+                        // a tile of value heads: nothing to norm or rotate, the rows go out as they are
+                        const int g0 = f0 / e.q.hd - e.q.n_q - e.q.n_kv;          // first value head of the tile
+#pragma unroll
+                        for (int r = 0; r < GP_CHUNK / 4; ++r) {
+                            const int row = quarter + 4 * r, t = t0 + c0 + row;
+                            const int fv = g0 * e.q.hd + lane * 4;                // feature among the value features
+                            if (row < cols && fv < e.q.n_kv * e.q.hd) {
+                                const float4 v4 = *reinterpret_cast<const float4*>(xs + row * GT_BM + lane * 4);
+                                const float y[4] = {v4.x, v4.y, v4.z, v4.w};
+                                const int g = fv / e.q.hd, d = fv % e.q.hd;
+                                if (e.q.write_cache) {
+                                    const int place = meta[c0 + row];
+                                    store4(e.q.cache.v + (((size_t)(place / IDM_PAGE) * e.q.n_kv + g) * IDM_PAGE + place % IDM_PAGE) *
+                                                             (size_t)e.q.hd + d, y);
+                                }
+                                if (e.q.v_new) store4(e.q.v_new + (size_t)t * e.q.n_kv * e.q.hd + fv, y);
+                            }
+                        }
+                    } else if (EPI == EPI_QKV) {
+                        // a warp takes whole token rows of the tile (whole heads: 128 % head_dim == 0), four
+                        // features per lane, as the separate kernel does
+#pragma unroll
+                        for (int r = 0; r < GP_CHUNK / 4; ++r) {
+                            // the four rows' arithmetic is independent: no branch around it, only the
+                            // stores of rows past the end are left out
+                            const int row = quarter + 4 * r;
+                            const float4 v4 = *reinterpret_cast<const float4*>(xs + row * GT_BM + lane * 4);
+                            const int place = meta[c0 + row];
+                            qkv_finish_tile4_pre(e.q, tl4, v4, t0 + c0 + row, f0, lane, place / IDM_PAGE, place % IDM_PAGE,
+                                                 ca[r], cb[r], row < cols);
+                        }
                     }
-                    epi_sync();                                    // the buffer is free for the next chunk
+                    group_sync(grp);                               // the buffer is free for the group's next chunk
                 }
             }
             tc_fence_before();
@@ -613,7 +652,7 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_persistent_kernel(const __gri
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem, TMEM_COLS);
+    if (warp == GP_EPI_WARPS + 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 template <int BN, int STAGES, int EPI>
@@ -635,7 +674,7 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const
     const int tiles_x = (N + GT_BM - 1) / GT_BM, tiles_y = (M + BN - 1) / BN;
     const int n_tiles = tiles_x * tiles_y;
     const int grid = n_tiles < n_sm ? n_tiles : n_sm;
-    idm_launch(gemm_persistent_kernel<BN, STAGES, EPI>, dim3(grid), dim3(GT_THREADS), S::TOTAL, stream, mw, mx, e, M, N,
+    idm_launch(gemm_persistent_kernel<BN, STAGES, EPI>, dim3(grid), dim3(GP_THREADS), S::TOTAL, stream, mw, mx, e, M, N,
                kb_total, tiles_x, n_tiles);
     IDM_LAUNCH_CHECK("gemm_persistent");
     return 0;
@@ -812,7 +851,7 @@ extern "C" int idm_gemm_bf16_qkv(const void* x, const void* w, float* workspace,
     QkvArgs& a = e.q;
     a.qkv = nullptr; a.n_partials = 0; a.partial_stride = 0;
     a.n_tokens = M; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd;
-    a.gq = gq; a.gk = gk; a.eps = eps; a.cs = (const float2*)cs;
+    a.gq = gq; a.gk = gk; a.eps = eps; a.inv_hd = 1.0f / (float)hd; a.cs = (const float2*)cs;
     a.q_out = (T*)q_out; a.k_new = (T*)k_new; a.v_new = (T*)v_new;
     a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
     a.write_cache = k_pool != nullptr;

@@ -18,10 +18,22 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&x)[4]) {
     *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
 }
 
+// eight consecutive elements, one store (16 bytes in bfloat16, two of 16 in 32-bit)
+__device__ __forceinline__ void store8(float* p, const float (&x)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(x[4], x[5], x[6], x[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&x)[8]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1]), b = __floats2bfloat162_rn(x[2], x[3]);
+    const __nv_bfloat162 c = __floats2bfloat162_rn(x[4], x[5]), d = __floats2bfloat162_rn(x[6], x[7]);
+    *reinterpret_cast<uint4*>(p) = make_uint4(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b),
+                                              *reinterpret_cast<const uint32_t*>(&c), *reinterpret_cast<const uint32_t*>(&d));
+}
+
 struct QkvArgs {
     const float* qkv; int n_partials; size_t partial_stride;
     int n_tokens, n_q, n_kv, hd;
-    const float* gq; const float* gk; float eps;
+    const float* gq; const float* gk; float eps; float inv_hd;   // inv_hd = 1 / hd
     const float2* cs;
     T* q_out; T* k_new; T* v_new;
     KVAddr cache; int write_cache;
@@ -36,6 +48,19 @@ struct QkvLocateFromTables {
         return kv_offset(a.cache, a.slots[a.token_seq[t]], a.positions[t], g);
     }
 };
+
+// 1 / sqrt(ss / hd + eps) for a head's sum of squares.  Every kernel that norms a head uses this one
+// function, with its roundings pinned, so that fused and separate paths give the same bits.  The 32-bit
+// library divides and takes the root exactly; the bfloat16 library uses the hardware's reciprocal square
+// root (2 units in the last place of 32-bit, far below the rounding of the result), which is what keeps the
+// tile epilogues of the projection from being bound by these instructions.
+__device__ __forceinline__ float head_inv_rms(const QkvArgs& a, float ss) {
+#if defined(IDM_F32)
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.hd), a.eps)));
+#else
+    return rsqrtf(__fmaf_rn(ss, a.inv_hd, a.eps));
+#endif
+}
 
 template <typename Load, typename Locate>
 __device__ __forceinline__ void qkv_finish_row(const QkvArgs& a, int t, int head, int lane, Load load, Locate locate) {
@@ -70,7 +95,7 @@ __device__ __forceinline__ void qkv_finish_row(const QkvArgs& a, int t, int head
     float inv = 1.f;
     if (gamma) {
         ss = warp_sum(ss);
-        inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.hd), a.eps)));
+        inv = head_inv_rms(a, ss);
     }
     const bool rotate = (is_q || is_k) && a.cs != nullptr;
 #pragma unroll
@@ -97,20 +122,50 @@ __device__ __forceinline__ void qkv_finish_row(const QkvArgs& a, int t, int head
 // held by one warp, four consecutive features per lane (lane l: features f0 + 4 l .. + 3): norm over
 // each head's lanes, rotation partner by shuffle, 8-byte stores.  page / prow: the token's place in
 // the cache (page number, row inside the page).  Every lane of the warp must call it.
-__device__ __forceinline__ void qkv_finish_tile4(const QkvArgs& a, float4 v, int t, int f0, int lane, int page, int prow) {
-    const int lph = a.hd >> 2;                        // lanes per head (a power of two)
-    const int head = f0 / a.hd + lane / lph, li = lane % lph;
-    const int heads = a.n_q + 2 * a.n_kv, half = a.hd >> 1;
-    const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv, live = head < heads;
-    const float* gamma = is_q ? a.gq : (is_k ? a.gk : nullptr);
+//
+// What a lane needs that does not change from token to token (head_dim is a power of two here):
+struct Tile4Lane {
+    int sh;                   // log2(lanes per head)
+    int d;                    // first of this lane's four dims within its head
+    int cs_j;                 // first of its four (cos, sin) pairs in a token's row of the table
+    bool first;               // its dims lie below head_dim / 2
+    float4 gq, gk;            // the norm weights of its dims
+};
+__device__ __forceinline__ Tile4Lane qkv_tile4_lane(const QkvArgs& a, int lane) {
+    Tile4Lane L;
+    const int lph = a.hd >> 2;                        // lanes per head
+    L.sh = 31 - __clz(lph);
+    const int li = lane & (lph - 1);
+    L.d = li * 4;
+    L.first = li < (lph >> 1);
+    L.cs_j = L.first ? L.d : L.d - (a.hd >> 1);
+    L.gq = a.gq ? *reinterpret_cast<const float4*>(a.gq + L.d) : make_float4(0.f, 0.f, 0.f, 0.f);
+    L.gk = a.gk ? *reinterpret_cast<const float4*>(a.gk + L.d) : make_float4(0.f, 0.f, 0.f, 0.f);
+    return L;
+}
+// the lane's (cos, sin) of token t for the tile at feature f0, or nullptr if its head is not rotated
+__device__ __forceinline__ const float4* qkv_tile4_cs(const QkvArgs& a, const Tile4Lane& L, int t, int f0, int lane) {
+    const int head = (f0 >> (L.sh + 2)) + (lane >> L.sh);
+    if (a.cs == nullptr || head >= a.n_q + a.n_kv) return nullptr;
+    return reinterpret_cast<const float4*>(a.cs + (size_t)t * (a.hd >> 1) + L.cs_j);
+}
+// ca, cb: what qkv_tile4_cs points to (unused if it is nullptr)
+// row_live = false: the arithmetic runs (the shuffles are warp-wide) but nothing is stored
+__device__ __forceinline__ void qkv_finish_tile4_pre(const QkvArgs& a, const Tile4Lane& L, float4 v, int t, int f0, int lane,
+                                                     int page, int prow, const float4& ca, const float4& cb,
+                                                     bool row_live = true) {
+    const int lph = 1 << L.sh;
+    const int head = (f0 >> (L.sh + 2)) + (lane >> L.sh);
+    const int heads = a.n_q + 2 * a.n_kv;
+    const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv, live = head < heads && row_live;
+    const bool normed = is_q ? a.gq != nullptr : (is_k && a.gk != nullptr);
     float x[4] = {v.x, v.y, v.z, v.w};
-    const int d = li * 4;                             // first of this lane's dims within the head
     // (every lane runs the shuffles, whatever its head is: they are warp-wide)
     float ss = __fmaf_rn(x[3], x[3], __fmaf_rn(x[2], x[2], __fmaf_rn(x[1], x[1], __fmul_rn(x[0], x[0]))));
     for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (live && gamma != nullptr) {
-        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.hd), a.eps)));
-        const float4 gm = *reinterpret_cast<const float4*>(gamma + d);
+    if (live && normed) {
+        const float inv = head_inv_rms(a, ss);
+        const float4 gm = is_q ? L.gq : L.gk;
         x[0] = __fmul_rn(__fmul_rn(x[0], inv), gm.x); x[1] = __fmul_rn(__fmul_rn(x[1], inv), gm.y);
         x[2] = __fmul_rn(__fmul_rn(x[2], inv), gm.z); x[3] = __fmul_rn(__fmul_rn(x[3], inv), gm.w);
     }
@@ -118,29 +173,32 @@ __device__ __forceinline__ void qkv_finish_tile4(const QkvArgs& a, float4 v, int
 #pragma unroll
     for (int i = 0; i < 4; ++i) other[i] = __shfl_xor_sync(0xffffffffu, x[i], lph >> 1);   // the rotation partner
     if (live && (is_q || is_k) && a.cs != nullptr) {
-        const bool first = li < (lph >> 1);           // dims below head_dim / 2
-        const int j = first ? d : d - half;
-        const float4* c4 = reinterpret_cast<const float4*>(a.cs + (size_t)t * half + j);   // (cos, sin) of 4 dims
-        const float4 ca = c4[0], cb = c4[1];
         const float cs_[4][2] = {{ca.x, ca.y}, {ca.z, ca.w}, {cb.x, cb.y}, {cb.z, cb.w}};
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-            x[i] = first ? __fmaf_rn(x[i], cs_[i][0], -__fmul_rn(other[i], cs_[i][1]))
-                         : __fmaf_rn(x[i], cs_[i][0], __fmul_rn(other[i], cs_[i][1]));
+            x[i] = L.first ? __fmaf_rn(x[i], cs_[i][0], -__fmul_rn(other[i], cs_[i][1]))
+                           : __fmaf_rn(x[i], cs_[i][0], __fmul_rn(other[i], cs_[i][1]));
     }
     if (live) {
         T* dst_a = nullptr; T* dst_b = nullptr;
         if (is_q) {
-            dst_a = a.q_out + ((size_t)t * a.n_q + head) * a.hd + d;
+            dst_a = a.q_out + ((size_t)t * a.n_q + head) * a.hd + L.d;
         } else {
             const int g = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
             if (a.write_cache)
                 dst_a = (is_k ? a.cache.k : a.cache.v) +
-                        (((size_t)page * a.n_kv + g) * IDM_PAGE + prow) * (size_t)a.hd + d;
+                        (((size_t)page * a.n_kv + g) * IDM_PAGE + prow) * (size_t)a.hd + L.d;
             T* packed = is_k ? a.k_new : a.v_new;
-            if (packed) dst_b = packed + ((size_t)t * a.n_kv + g) * a.hd + d;
+            if (packed) dst_b = packed + ((size_t)t * a.n_kv + g) * a.hd + L.d;
         }
         if (dst_a) store4(dst_a, x);
         if (dst_b) store4(dst_b, x);
     }
+}
+__device__ __forceinline__ void qkv_finish_tile4(const QkvArgs& a, float4 v, int t, int f0, int lane, int page, int prow) {
+    const Tile4Lane L = qkv_tile4_lane(a, lane);
+    const float4* c4 = qkv_tile4_cs(a, L, t, f0, lane);
+    float4 ca = make_float4(0.f, 0.f, 0.f, 0.f), cb = ca;
+    if (c4) { ca = c4[0]; cb = c4[1]; }
+    qkv_finish_tile4_pre(a, L, v, t, f0, lane, page, prow, ca, cb);
 }

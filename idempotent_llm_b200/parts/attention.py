@@ -82,9 +82,8 @@ class GQAAttention(Mixer):
         windowed = kv.ring > 0 and not ctx.single_token
         finish = (s.n_heads, 0 if s.kv_from_other else s.n_kv_heads, s.head_dim, self.q_gamma, self.k_gamma,
                   s.qk_norm_eps, cs, ctx, kv if (writes_cache and not windowed) else None)
-        if fused and 128 % s.head_dim == 0 and x.shape[0] <= 64:
-            # up to 64 tokens norm, rotation and the cache write are the epilogue of the projection; with
-            # many tokens the per-head finish would hold up the next tile's tensor-core work
+        if fused and 128 % s.head_dim == 0:
+            # norm, rotation and the cache write are the epilogue of the projection
             q, k_new, v_new = K.gemm_qkv(x, self.w_qkv, *finish, keep_new=writes_cache and windowed)
         else:
             qkv = K.gemm_store(x, self.w_qkv)[None] if fused else K.gemm(x, self.w_qkv)   # [P, N, (n_q [+ 2 n_kv]) * hd]
