@@ -93,7 +93,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t tmem_o = tmem + 128;                          // S buffers at columns 0 and 64, O from 128
     pdl_wait();                                                  // set-up done; now the previous kernel's results
 
-    const int tile = blockIdx.x, head = blockIdx.y;
+    const int tile = blockIdx.y, head = blockIdx.x;              // blocks start in this order: all heads of the longest tile first
     const int seq = a.tile_seq[tile], tstart = a.tile_start[tile];
     const int g = head / (a.n_q / a.n_kv);
     const int tok0 = a.cu_q[seq] + tstart;                       // first token (packed row) of the tile
@@ -186,30 +186,41 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty(b & 1));
             const bool diagonal = (b + 1) * AP_BN - 1 > p_first;   // some key of the block lies past row 0's position
-            float m_blk = -INFINITY;
+            if (diagonal) {
 #pragma unroll
-            for (int j = 0; j < AP_BN; ++j) {
-                float s = __uint_as_float(sr[j]) * a.scale_log2;
-                if (diagonal && b * AP_BN + j > p_r) s = -INFINITY;
-                sr[j] = __float_as_uint(s);
-                m_blk = fmaxf(m_blk, s);
+                for (int j = 0; j < AP_BN; ++j)
+                    if (b * AP_BN + j > p_r) sr[j] = 0xff800000u;  // -inf: p becomes 0 exactly
             }
+            // the maximum of the raw scores (the scale is positive), four chains side by side
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < AP_BN; j += 4) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], __uint_as_float(sr[j + u]));
+            }
+            const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;
             float alpha = 1.f;
             if (m_blk > m_ref + AP_RESCALE_STEP || m_ref == -INFINITY) {
                 // (m_ref is -inf only before the first block, whose key 0 every row may see)
                 alpha = exp2f(m_ref - m_blk);                      // 0 the first time
                 m_ref = m_blk;
             }
-            float row_sum = 0.f;
+            // p = 2^(s * scale - m_ref): one fused multiply-add and one exponential per score
+            const float neg_m = -m_ref;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t packed[AP_BN / 2];
 #pragma unroll
-            for (int j = 0; j < AP_BN; j += 2) {
-                const float p0 = exp2f(__uint_as_float(sr[j]) - m_ref);
-                const float p1 = exp2f(__uint_as_float(sr[j + 1]) - m_ref);
-                row_sum += p0 + p1;
-                const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                packed[j / 2] = *reinterpret_cast<const uint32_t*>(&pk);
+            for (int j = 0; j < AP_BN; j += 4) {
+                const float p0 = exp2f(fmaf(__uint_as_float(sr[j]), a.scale_log2, neg_m));
+                const float p1 = exp2f(fmaf(__uint_as_float(sr[j + 1]), a.scale_log2, neg_m));
+                const float p2 = exp2f(fmaf(__uint_as_float(sr[j + 2]), a.scale_log2, neg_m));
+                const float p3 = exp2f(fmaf(__uint_as_float(sr[j + 3]), a.scale_log2, neg_m));
+                sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
+                const __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1), pb = __floats2bfloat162_rn(p2, p3);
+                packed[j / 2] = *reinterpret_cast<const uint32_t*>(&pa);
+                packed[j / 2 + 1] = *reinterpret_cast<const uint32_t*>(&pb);
             }
+            const float row_sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if (b >= 1) {
                 ok = mbar_wait(o_done, (b - 1) & 1, abort_flag, &g_attn_prefill_error);   // P is free, O is settled
                 if (!ok) break;
@@ -291,7 +302,7 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
                     cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(n_tiles, a.n_q);
+    dim3 grid(a.n_q, n_tiles);
     idm_launch(attention_prefill_kernel<HD>, dim3(grid), dim3(AP_THREADS), S::TOTAL, stream, mq, mk, mv, a);
     IDM_LAUNCH_CHECK("attention_prefill");
     return 0;
@@ -308,7 +319,8 @@ extern "C" int idm_attention_prefill(const void* q, void* out, const void* k_poo
                                      cudaStream_t stream) {
     if (n_tiles == 0 || n_tokens == 0) return 0;
     IDM_REQUIRE(idm_attention_prefill_supports(hd), "attention_prefill: head_dim=%d has no kernel here", hd);
-    IDM_REQUIRE(n_kv > 0 && n_q % n_kv == 0 && n_q <= 65535, "attention_prefill: bad head counts %d/%d", n_q, n_kv);
+    IDM_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention_prefill: bad head counts %d/%d", n_q, n_kv);
+    IDM_REQUIRE(n_tiles <= 65535, "attention_prefill: %d tiles in one step; at most 65535", n_tiles);
     CUtensorMap mq, mk, mv;
     {
         cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)n_q, (cuuint64_t)n_tokens};

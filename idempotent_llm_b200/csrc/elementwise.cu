@@ -92,12 +92,57 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec4_kernel(float* __restrict
     }
 }
 
+// Many rows with nothing to add (the residual was added by the product before): one warp per row, no
+// block-wide barrier.  Lane l stands for the threads l, l + 32, ... of the kernel above (its warps
+// 0 .. 7), sums each of those warps by the same butterfly and adds the eight totals in the same order:
+// the same bits, whichever of the two kernels runs.
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ h, const float* __restrict__ gamma,
+                                                           float eps, T* __restrict__ x, const int* __restrict__ rows,
+                                                           int n_rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (i >= n_rows) return;
+    const int r = rows ? rows[i] : i;
+    const float* hr = h + (size_t)r * hidden;
+    float4 v[8];
+    float s[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        const int c = (32 * w + lane) * 4;
+        v[w] = c < hidden ? *reinterpret_cast<const float4*>(hr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        s[w] = v[w].x * v[w].x + v[w].y * v[w].y + v[w].z * v[w].z + v[w].w * v[w].w;
+    }
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s[w] = warp_sum(s[w]);
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += s[w];
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    T* xr = x + (size_t)i * hidden;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        const int c = (32 * w + lane) * 4;
+        if (c < hidden) {
+            const float4 gm = *reinterpret_cast<const float4*>(gamma + c);
+            from_f32(xr[c + 0], v[w].x * inv * gm.x); from_f32(xr[c + 1], v[w].y * inv * gm.y);
+            from_f32(xr[c + 2], v[w].z * inv * gm.z); from_f32(xr[c + 3], v[w].w * inv * gm.w);
+        }
+    }
+}
+
 extern "C" int idm_add_rmsnorm(float* h, const float* delta, int n_partials, long long partial_stride,
                                const float* gamma, float eps, void* x, const int* rows, int n_rows,
                                int hidden, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     IDM_REQUIRE(hidden > 0 && n_rows > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
     IDM_REQUIRE((size_t)hidden * 4 <= 160 * 1024, "add_rmsnorm: hidden=%d does not fit shared memory", hidden);
+    if (hidden % 4 == 0 && hidden <= 1024 && (delta == nullptr || n_partials == 0) && n_rows >= 64) {
+        idm_launch(rmsnorm_rows_kernel, dim3((n_rows + 7) / 8), dim3(256), 0, stream, (const float*)h, gamma, eps, (T*)x, rows,
+                   n_rows, hidden);
+        IDM_LAUNCH_CHECK("add_rmsnorm");
+        return 0;
+    }
     if (hidden % 4 == 0 && hidden <= 1024 && n_partials <= 16 && (partial_stride % 4) == 0) {
         // NOTE: the sum of squares is taken over the same values in a different thread layout than
         // the general kernel; which kernel runs depends on `hidden` and the number of partials only

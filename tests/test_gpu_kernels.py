@@ -67,6 +67,24 @@ def test_add_rmsnorm(kernels, dtype, hidden, eps):
     assert torch.equal(xr, x[rows.long()])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [1024, 72, 520])
+def test_rmsnorm_of_many_rows_has_the_bits_of_few_rows(kernels, dtype, hidden):
+    """From 64 rows on a warp norms a row by itself; a row's result must not depend on how many rows there are."""
+    K = kernels(dtype)
+    n = 203
+    h = _randn(n, hidden, seed=5, scale=3.0).float().cuda()
+    h[::7] *= 100.0
+    gamma = (1 + _randn(hidden, seed=6, scale=0.2)).float().cuda()
+    many = K.add_rmsnorm(h, None, gamma, 1e-6)
+    few = torch.cat([K.add_rmsnorm(h[i:i + 29].contiguous(), None, gamma, 1e-6) for i in range(0, n, 29)])
+    assert torch.equal(many, few)
+    v = h.double().cpu()
+    assert helpers.rel_err(many, v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.double().cpu()) < KTOL[dtype]
+    rows = torch.arange(n - 1, -1, -1, dtype=torch.int32).cuda()
+    assert torch.equal(K.add_rmsnorm(h, None, gamma, 1e-6, rows=rows), many.flip(0))
+
+
 def test_rope_table(kernels):
     K = kernels("float32")
     pos = torch.tensor([0, 1, 63, 4095, 40959], dtype=torch.int32)
