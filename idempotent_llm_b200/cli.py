@@ -137,7 +137,10 @@ def cmd_bench(args) -> int:
     ctx = args.prompt_len + args.decode_steps + 16
     lm = api.from_random(cfg, seed=0, dtype=dtype, max_tokens=max(args.batch * (-(-ctx // 64) * 64),
                                                                    -(-args.prefill_len // 64) * 64 * args.batch),
-                         max_seqs=args.batch)
+                         max_seqs=args.batch, use_graph=not args.no_graph)
+    # --profile-range: the CUDA profiler is switched on around the timed decode steps or the last
+    # prompt step only (for `ncu --profile-from-start off`)
+    prof = torch.cuda.profiler
     eng = lm.engine
     g = torch.Generator().manual_seed(0)
     V = cfg.vocab_size
@@ -149,12 +152,16 @@ def cmd_bench(args) -> int:
         cur = eng.sample(eng.step([(s, [t]) for s, t in zip(slots, cur)]), 0.0, 0, list(range(args.batch)),
                          [0] * args.batch)
     torch.cuda.synchronize()
+    if args.profile_range == "decode":
+        prof.start()
     t0 = time.perf_counter()
     for _ in range(args.decode_steps):
         cur = eng.sample(eng.step([(s, [t]) for s, t in zip(slots, cur)]), 0.0, 0, list(range(args.batch)),
                          [0] * args.batch)
     torch.cuda.synchronize()
     decode_tps = args.batch * args.decode_steps / (time.perf_counter() - t0)
+    if args.profile_range == "decode":
+        prof.stop()
     for s in slots:
         eng.close(s)
     pids = torch.randint(min(100, V - 1), min(50000, V), (args.batch, args.prefill_len), generator=g).tolist()
@@ -162,10 +169,14 @@ def cmd_bench(args) -> int:
     for it in range(2):
         slots = [eng.open() for _ in pids]
         torch.cuda.synchronize()
+        if args.profile_range == "prefill" and it == 1:
+            prof.start()
         t0 = time.perf_counter()
         eng.step(list(zip(slots, pids)))
         torch.cuda.synchronize()
         prefill_tps = args.batch * args.prefill_len / (time.perf_counter() - t0)
+        if args.profile_range == "prefill" and it == 1:
+            prof.stop()
         for s in slots:
             eng.close(s)
     print(f"{args.model} {args.size} batch={args.batch}: decode {decode_tps:.1f} tok/s, prefill {prefill_tps:.0f} tok/s")
@@ -316,6 +327,9 @@ def main(argv=None) -> int:
     b.add_argument("--prompt-len", type=int, default=128)
     b.add_argument("--decode-steps", type=int, default=64)
     b.add_argument("--prefill-len", type=int, default=2048)
+    b.add_argument("--no-graph", action="store_true", help="single-token steps launch their kernels one by one")
+    b.add_argument("--profile-range", choices=["decode", "prefill"], default=None,
+                   help="switch the CUDA profiler on around the timed decode steps or the last prompt step")
     b.set_defaults(fn=cmd_bench)
 
     g = sub.add_parser("generate", help="token ids in, token ids out")

@@ -1,6 +1,6 @@
 """Each part alone against the plain implementation's function for it; a schedule that names a
-layer twice and shares a cache; and a toy mixer with state of its own that is registered, built
-and stepped from this file alone (GPU)."""
+layer twice and shares a cache; and toy parts -- a mixer with state of its own, a feed-forward that
+routes, another position encoding -- that are registered, built and stepped from this file alone (GPU)."""
 
 from dataclasses import dataclass
 
@@ -14,7 +14,8 @@ from idempotent_llm_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, 
                                         RotarySpec, RunEntry)
 from idempotent_llm_b200.engine import CausalLM, Engine, cache_needs, declare_weights
 from idempotent_llm_b200.engine.batch import context_from_packed, pack_step_host
-from idempotent_llm_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Mixer, Runtime
+from idempotent_llm_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward, Mixer,
+                                       PositionEncoding, Runtime)
 from idempotent_llm_b200.weights import TensorDecl, random_weights
 
 pytestmark = pytest.mark.gpu
@@ -269,3 +270,153 @@ def test_toy_mixer_with_its_own_state_is_registered_built_and_stepped(tmp_path, 
             eng.close(s)
     toks, _ = lm.generate(reqs, 4)
     assert toks.shape == (3, 4) and int(toks.min()) >= 0
+
+
+# ------------------------------------- a toy feed-forward with routing and a toy position encoding
+@dataclass(frozen=True)
+class ToyRoutedSpec:
+    hidden: int
+    n_experts: int
+    kind: str = "toy_routed"
+
+
+class ToyRoutedFeedForward(FeedForward):
+    """Each token goes to the expert with the largest router probability; output = p_top * (W_expert . x).
+    Router logits, softmax and the product in 32-bit; plain torch on the device without a host
+    synchronisation, so single-token steps with this part still run as captured graphs."""
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        return [TensorDecl(prefix + "router.weight", (spec.n_experts, spec.hidden)),
+                TensorDecl(prefix + "experts.weight", (spec.n_experts, spec.hidden, spec.hidden))]
+
+    def __init__(self, spec, weights, prefix, rt):
+        self.router = weights[prefix + "router.weight"].float()
+        self.experts = weights[prefix + "experts.weight"].float()
+
+    def forward(self, x, ctx):
+        x = x.float()
+        p = torch.softmax(x @ self.router.T * 4.0, dim=-1)
+        top = p.argmax(dim=-1)
+        y = torch.bmm(self.experts[top], x.unsqueeze(-1)).squeeze(-1) * p.gather(-1, top[:, None])
+        return y.unsqueeze(0)
+
+
+@dataclass(frozen=True)
+class ToyScaledRotarySpec:
+    theta: float
+    dim: int
+    factor: float
+    kind: str = "toy_scaled_rotary"
+
+
+class ToyScaledRotary(PositionEncoding):
+    """Rotation by position / factor: another position encoding behind the same ``tables(ctx)``."""
+
+    def __init__(self, spec, weights, prefix, rt):
+        j = torch.arange(0, spec.dim // 2, dtype=torch.float64)
+        self.spec, self.rt = spec, rt
+        self.inv_freq = (float(spec.theta) ** (-2.0 * j / spec.dim) / spec.factor).to(rt.device)
+
+    def tables(self, ctx):
+        key = ("toy_scaled_rotary", self.spec)
+        if key not in ctx.memo:
+            ctx.memo[key] = self.rt.kernels.rope_table(ctx.positions, self.inv_freq)
+        return ctx.memo[key]
+
+
+@dataclass(frozen=True)
+class ToyRoutedConfig:
+    vocab_size: int = 83
+    hidden_size: int = 40
+    n_experts: int = 3
+    factor: float = 4.0
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: d[k] for k in ("vocab_size", "hidden_size", "n_experts", "factor") if k in d})
+
+    def to_model_spec(self):
+        norm = NormSpec(self.hidden_size, 1e-5)
+        attn = lambda pos: AttentionSpec(hidden=self.hidden_size, n_heads=2, n_kv_heads=2, head_dim=16, softmax_scale=0.25,
+                                         qk_norm=True, qk_norm_eps=1e-5, position=pos)
+        layers = (LayerSpec("model.layers.0.", attn(ToyScaledRotarySpec(1e4, 16, self.factor)),
+                            ToyRoutedSpec(self.hidden_size, self.n_experts), norm, norm),
+                  LayerSpec("model.layers.1.", attn(RotarySpec(1e4, 16, 512)), GatedMLPSpec(self.hidden_size, 56), norm, norm))
+        return ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=self.vocab_size, hidden=self.hidden_size,
+                         layers=layers, schedule=tuple(RunEntry(i, i) for i in range(2)),
+                         final_norm=norm, tie_embeddings=True, max_positions=512)
+
+
+def _toy_routed_plain(w, ids, cfg: ToyRoutedConfig):
+    """Returns the logits and the smallest gap between the two largest router probabilities."""
+    ids = torch.as_tensor(ids)
+    T = ids.numel()
+    h = w["model.embed_tokens.weight"][ids]
+    acfg = dict(num_attention_heads=2, num_key_value_heads=2, head_dim=16, hidden_size=cfg.hidden_size,
+                rms_norm_eps=1e-5, rope_theta=1e4)
+    gap = 1.0
+    for i in range(2):
+        p = f"model.layers.{i}."
+        x = plain.rmsnorm(h, w[p + "input_layernorm.weight"], 1e-5)
+        pos = torch.arange(T, dtype=F64) / (cfg.factor if i == 0 else 1.0)
+        a, _ = plain.attention_block(x, w, p, acfg, pos, None)
+        h = h + a
+        x = plain.rmsnorm(h, w[p + "post_attention_layernorm.weight"], 1e-5)
+        if i == 0:
+            pr = torch.softmax(x @ w[p + "router.weight"].T * 4.0, dim=-1)
+            two = pr.topk(2, dim=-1).values
+            gap = min(gap, float((two[:, 0] - two[:, 1]).min()))
+            top = pr.argmax(-1)
+            h = h + torch.stack([w[p + "experts.weight"][top[t]] @ x[t] * pr[t, top[t]] for t in range(T)])
+        else:
+            h = h + plain.mlp_block(x, w, p)
+    return plain.rmsnorm(h, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T, gap
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_feed_forward_with_routing_and_toy_position_encoding(tmp_path, dtype):
+    """A feed-forward that routes and a position encoding of another kind, both defined here, are
+    registered, loaded through the registry and stepped (prompts, unequal batches, single tokens in
+    captured graphs) against a plain computation -- with no change to the library's files."""
+    import json
+    import idempotent_llm_b200 as idm
+    from idempotent_llm_b200.weights import write_safetensors
+    FEED_FORWARDS.register("toy_routed", ToyRoutedFeedForward)
+    POSITIONS.register("toy_scaled_rotary", ToyScaledRotary)
+    idm.register_architecture("ToyRoutedForCausalLM", ToyRoutedConfig)
+    cfg = ToyRoutedConfig()
+    spec = cfg.to_model_spec()
+    reqs = [helpers.rand_ids(n, cfg.vocab_size, 40 + n) for n in (11, 37, 5)]
+    # weights whose routing is decisive for these requests: a token near a tie could go to another
+    # expert in reduced precision, which is no fault of the engine
+    for seed in range(40):
+        w = random_weights(declare_weights(spec), seed, 0.2, dtype=torch.bfloat16)
+        w64 = _w64(w)
+        refs, gaps = zip(*[_toy_routed_plain(w64, r, cfg) for r in reqs])
+        if min(gaps) > 0.08:
+            break
+    else:
+        pytest.fail("no seed gives decisive routing")
+    (tmp_path / "config.json").write_text(json.dumps({"architectures": ["ToyRoutedForCausalLM"], "vocab_size": cfg.vocab_size,
+                                                      "hidden_size": cfg.hidden_size}))
+    write_safetensors(str(tmp_path / "model.safetensors"), list(w.items()))
+    lm = idm.load(str(tmp_path), dtype=dtype, max_tokens=64 * 6, max_seqs=3)
+    eng = lm.engine
+    assert lm.model.graph_safe, "nothing in this model synchronises with the host"
+    tol = helpers.TOL[dtype]
+    for r, ref in zip(reqs, refs):
+        s = eng.open()
+        assert helpers.rel_err(eng.step([(s, r)], [list(range(len(r)))]), ref) < tol
+        eng.close(s)
+    for _ in range(2):
+        slots = [eng.open() for _ in reqs]
+        cut = [len(r) - 3 for r in reqs]
+        lg = eng.step([(s, r[:c]) for s, r, c in zip(slots, reqs, cut)], [list(range(c)) for c in cut])
+        assert helpers.rel_err(lg, torch.cat([ref[:c] for ref, c in zip(refs, cut)])) < tol
+        for k in range(3):
+            lg = eng.step([(s, [r[c + k]]) for s, r, c in zip(slots, reqs, cut)])
+            assert helpers.rel_err(lg, torch.stack([ref[c + k] for ref, c in zip(refs, cut)])) < tol
+        for s in slots:
+            eng.close(s)
+    assert eng._graphs, "the single-token steps ran as captured graphs"
