@@ -2,7 +2,8 @@
 //
 // One block per (tile of 128 consecutive query tokens of one sequence, q-head).  Keys and values
 // come from the paged cache (the step's own keys were written before), one page of 64 keys per
-// iteration, fetched by TMA.  Per iteration:
+// iteration, fetched by TMA two pages ahead (with one buffer for the keys each Q . K^T waited a whole
+// trip to L2 for its operand).  Per iteration:
 //   S = Q . K^T        tcgen05.mma, both operands in shared memory, S [128 x 64] in tensor memory
 //   softmax            one thread per query row reads its row of S (tcgen05.ld): scale, causal
 //                      mask, running maximum, p = 2^(s - m), running sum -- all 32-bit, no shuffles
@@ -48,12 +49,15 @@ template <int HD>
 struct PrefillSmem {
     static constexpr int HT = HD / 64;                 // 64-wide tiles along head_dim
     static constexpr int Q_BYTES = HT * AP_BM * 128;
-    static constexpr int K_BYTES = HT * AP_BN * 128;
+    static constexpr int K_BYTES = HT * AP_BN * 128;   // per stage, two stages
     static constexpr int V_BYTES = HT * AP_BN * 128;   // per stage, two stages
     static constexpr int P_BYTES = AP_BM * 128;
-    static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + K_BYTES, P_OFF = V_OFF + 2 * V_BYTES;
+    static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + 2 * K_BYTES, P_OFF = V_OFF + 2 * V_BYTES;
     static constexpr int BAR_OFF = P_OFF + P_BYTES;
-    static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+    static constexpr int NEED = BAR_OFF + 256;         // from the first 1024-byte border on
+    // two blocks per SM: 2 x (TOTAL + 1 KB the system keeps per block) must stay within 228 KB, which
+    // leaves 512 bytes to reach the border (the array is declared with that alignment; the kernel checks)
+    static constexpr int TOTAL = NEED + (HD == 128 ? 512 : 1024);
 };
 
 template <int HD>
@@ -62,24 +66,31 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                          const __grid_constant__ CUtensorMap map_v, PrefillArgs a) {
     using S = PrefillSmem<HD>;
     constexpr int HT = S::HT;
-    extern __shared__ uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    if (base - smem_u32(smem_raw) + S::NEED > S::TOTAL) {        // (never seen: the array starts on a 1024-byte border)
+        if (threadIdx.x == 0) atomicExch(&g_attn_prefill_error, 2);
+        return;
+    }
     uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t bars = base + S::BAR_OFF;
     // barriers (8 bytes each)
-    const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 16, p_full = bars + 24, o_done = bars + 32;
-    auto v_full = [&](int i) { return bars + 40 + 8u * i; };
-    auto v_empty = [&](int i) { return bars + 56 + 8u * i; };
-    auto s_full = [&](int i) { return bars + 72 + 8u * i; };
-    auto s_empty = [&](int i) { return bars + 88 + 8u * i; };
-    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gbase + S::BAR_OFF + 104);
+    const uint32_t q_full = bars, p_full = bars + 40, o_done = bars + 48;
+    auto k_full = [&](int i) { return bars + 8 + 8u * i; };
+    auto k_empty = [&](int i) { return bars + 24 + 8u * i; };
+    auto v_full = [&](int i) { return bars + 56 + 8u * i; };
+    auto v_empty = [&](int i) { return bars + 72 + 8u * i; };
+    auto s_full = [&](int i) { return bars + 88 + 8u * i; };
+    auto s_empty = [&](int i) { return bars + 104 + 8u * i; };
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gbase + S::BAR_OFF + 120);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(p_full, 4); mbar_init(o_done, 1);
+        mbar_init(q_full, 1); mbar_init(p_full, 4); mbar_init(o_done, 1);
         for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full(i), 1); mbar_init(k_empty(i), 1);
             mbar_init(v_full(i), 1); mbar_init(v_empty(i), 1); mbar_init(s_full(i), 1); mbar_init(s_empty(i), 4);
         }
         *abort_flag = 0;
@@ -114,10 +125,11 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int b = 0; b < nb; ++b) {
                 const int page = a.table[(size_t)slot * a.table_stride + b];
                 const int row = (page * a.n_kv + g) * IDM_PAGE;
-                if (b >= 1 && !mbar_wait(k_empty, (b - 1) & 1, abort_flag, &g_attn_prefill_error)) break;
-                mbar_expect_tx(k_full, S::K_BYTES);
-                for (int h = 0; h < HT; ++h) tma_load_2d(base + S::K_OFF + h * AP_BN * 128, &map_k, h * 64, row, k_full);
-                const int vb = b & 1;
+                const int vb = b & 1;                            // this block's key and value buffers
+                if (b >= 2 && !mbar_wait(k_empty(vb), ((b >> 1) - 1) & 1, abort_flag, &g_attn_prefill_error)) break;
+                mbar_expect_tx(k_full(vb), S::K_BYTES);
+                for (int h = 0; h < HT; ++h)
+                    tma_load_2d(base + S::K_OFF + vb * S::K_BYTES + h * AP_BN * 128, &map_k, h * 64, row, k_full(vb));
                 if (b >= 2 && !mbar_wait(v_empty(vb), ((b >> 1) - 1) & 1, abort_flag, &g_attn_prefill_error)) break;
                 mbar_expect_tx(v_full(vb), S::V_BYTES);
                 for (int h = 0; h < HT; ++h)
@@ -134,18 +146,18 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const uint64_t ad = umma_desc_kmajor(base + S::Q_OFF + (kk / 4) * AP_BM * 128) + 2 * (kk % 4);
-                    const uint64_t bd = umma_desc_kmajor(base + S::K_OFF + (kk / 4) * AP_BN * 128) + 2 * (kk % 4);
+                    const uint64_t bd = umma_desc_kmajor(base + S::K_OFF + (b & 1) * S::K_BYTES + (kk / 4) * AP_BN * 128) + 2 * (kk % 4);
                     tc_mma_bf16(d, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
                 }
                 tc_commit(s_full(b & 1));
-                tc_commit(k_empty);
+                tc_commit(k_empty(b & 1));
             };
             bool ok = mbar_wait(q_full, 0, abort_flag, &g_attn_prefill_error) &&
-                      mbar_wait(k_full, 0, abort_flag, &g_attn_prefill_error);
+                      mbar_wait(k_full(0), 0, abort_flag, &g_attn_prefill_error);
             if (ok) { tc_fence_after(); mma_s(0); }
             for (int b = 0; b < nb && ok; ++b) {
                 if (b + 1 < nb) {
-                    ok = mbar_wait(k_full, (b + 1) & 1, abort_flag, &g_attn_prefill_error);
+                    ok = mbar_wait(k_full((b + 1) & 1), ((b + 1) >> 1) & 1, abort_flag, &g_attn_prefill_error);
                     if (ok && b + 1 >= 2)
                         ok = mbar_wait(s_empty((b + 1) & 1), (((b + 1) >> 1) - 1) & 1, abort_flag, &g_attn_prefill_error);
                     if (!ok) break;
