@@ -24,7 +24,9 @@
 // q/k norm, rotation, q out and cache write; a tile of 128 features must hold whole heads).  With K
 // split, every slice writes its tile to a workspace and the block that arrives last for the tile
 // (a counter it sets back to zero) adds the slices in ascending order and runs the epilogue, so the
-// value does not depend on which block that is.
+// value does not depend on which block that is.  (Up to 64 tokens the slices are added inside a
+// thread-block cluster instead; above 256 tokens nothing is split and the persistent kernels further
+// down run: see there.)
 //
 // Every wait on an mbarrier is bounded by a cycle count; a wait that runs out sets the error flag
 // (idm_gemm_status), all roles leave their loops, tensor memory is freed and the block returns.
@@ -655,6 +657,220 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __gri
     if (warp == GP_EPI_WARPS + 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// ------------------------------------------------- q/k/v projection of many tokens, tokens on the lanes
+// The same persistent scheme with the operands' roles exchanged: the MMA's M axis carries 128 tokens
+// (rows of x), its N axis 256 features (rows of w: whole heads), so an accumulator lane is a token and
+// a thread reads its token's whole head along the columns.  The per-head norm is then a sum inside the
+// thread, the rotation partner (d, d + head_dim / 2) a register of the same thread: no shuffles and no
+// turn through shared memory.  A head of a tile goes to one warp per 32 tokens; per tile 2 or 4 heads
+// x 4 token quarters keep 8 or 16 of the 16 epilogue warps busy, far below the time of the tile's MMAs.
+#define GQ_BN 256
+#define GQ_STAGES 4
+struct QkvTokensSmem {
+    static constexpr int A_BYTES = GT_BM * GT_BK * 2;              // 128 tokens
+    static constexpr int B_BYTES = GQ_BN * GT_BK * 2;              // 256 features
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFF = GQ_STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                     const __grid_constant__ CUtensorMap map_x,
+                                                                     const GemmEpi e, int n_tokens, int n_features,
+                                                                     int kb_total, int tiles_x, int n_tiles) {
+    using S = QkvTokensSmem;
+    constexpr int STAGES = GQ_STAGES, BN = GQ_BN;
+    constexpr int TMEM_COLS = 2 * BN;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + S::BAR_OFF;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + S::BAR_OFF + 8 * (2 * STAGES + 4));
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), GP_EPI_WARPS); }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == GP_EPI_WARPS + 1) tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    pdl_wait();
+
+    if (warp == GP_EPI_WARPS) {
+        if (lane == 0) {
+            uint32_t cnt = 0;
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                const int f0 = (tile % tiles_x) * BN, t0 = (tile / tiles_x) * GT_BM;
+                bool ok = true;
+                for (int i = 0; i < kb_total && ok; ++i, ++cnt) {
+                    const int s = cnt % STAGES;
+                    ok = mbar_wait(empty_bar(s), ((cnt / STAGES) & 1) ^ 1, abort_flag, &g_gemm_error);
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+                    const uint32_t a_dst = base + s * S::STAGE_BYTES;
+                    tma_load_2d(a_dst, &map_x, i * GT_BK, t0, full_bar(s));
+                    tma_load_2d(a_dst + S::A_BYTES, &map_w, i * GT_BK, f0, full_bar(s));
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == GP_EPI_WARPS + 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(GT_BM, BN);
+            uint32_t cnt = 0, it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t acc = it & 1;
+                ok = mbar_wait(tempty_bar(acc), ((it >> 1) & 1) ^ 1, abort_flag, &g_gemm_error);
+                if (!ok) break;
+                tc_fence_after();
+                for (int i = 0; i < kb_total && ok; ++i, ++cnt) {
+                    const int s = cnt % STAGES;
+                    ok = mbar_wait(full_bar(s), (cnt / STAGES) & 1, abort_flag, &g_gemm_error);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * S::STAGE_BYTES;
+                    const uint64_t a_desc = umma_desc_kmajor(a_addr), b_desc = umma_desc_kmajor(a_addr + S::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < GT_BK / GT_UMMA_K; ++k)
+                        tc_mma_bf16(tmem + acc * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty_bar(s));
+                }
+                if (ok) tc_commit(tfull_bar(acc));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const QkvArgs& a = e.q;
+        const int quarter = warp & 3, grp = warp >> 2;             // accumulator lanes 32 quarter ..; heads grp, grp + 4, ...
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int hd = a.hd, half = hd >> 1, heads = a.n_q + 2 * a.n_kv, hpt = BN / hd;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+            const int f0 = (tile % tiles_x) * BN, t0 = (tile / tiles_x) * GT_BM;
+            const uint32_t acc = it & 1;
+            const int t = t0 + quarter * 32 + lane;                // this thread's token
+            const bool live = t < n_tokens;
+            // where the token's key/value rows lie in the cache (asked for before the accumulator is waited for)
+            size_t place = 0;
+            if (live && a.write_cache && f0 + BN > a.n_q * hd) {
+                const int pos = a.positions[t];
+                const int r = a.cache.ring ? pos % a.cache.ring : pos;
+                const int page = a.cache.table[(size_t)a.slots[a.token_seq[t]] * a.cache.table_stride + r / IDM_PAGE];
+                place = (size_t)page * a.n_kv * IDM_PAGE + r % IDM_PAGE;       // row of kv-head 0; kv-head g: + g * IDM_PAGE
+            }
+            ok = mbar_wait(tfull_bar(acc), (it >> 1) & 1, abort_flag, &g_gemm_error);
+            if (!ok) break;
+            tc_fence_after();
+            for (int hh = grp; hh < hpt; hh += GP_GROUPS) {
+                const int head = f0 / hd + hh;
+                if (head >= heads) break;                          // the last tile may reach past the last head
+                const uint32_t col0 = tmem + acc * BN + lane_base + (uint32_t)(hh * hd);
+                const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
+                const float* gamma = is_q ? a.gq : (is_k ? a.gk : nullptr);
+                T* dst_a = nullptr; T* dst_b = nullptr;
+                if (live) {
+                    if (is_q) {
+                        dst_a = a.q_out + ((size_t)t * a.n_q + head) * hd;
+                    } else {
+                        const int g = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
+                        if (a.write_cache) dst_a = (is_k ? a.cache.k : a.cache.v) + (place + (size_t)g * IDM_PAGE) * hd;
+                        T* packed = is_k ? a.k_new : a.v_new;
+                        if (packed) dst_b = packed + ((size_t)t * a.n_kv + g) * hd;
+                    }
+                }
+                float inv = 1.f;
+                if (gamma != nullptr) {                            // the head's sum of squares: a first pass over its columns
+                    float ss = 0.f;
+#pragma unroll 1
+                    for (int c = 0; c < hd; c += 16) {
+                        float v[16];
+                        tc_ld16(col0 + (uint32_t)c, v);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) ss = __fmaf_rn(v[i], v[i], ss);
+                    }
+                    inv = head_inv_rms(a, ss);
+                }
+                const bool rotate = (is_q || is_k) && a.cs != nullptr;
+                const float2* cs = a.cs + (size_t)(live ? t : 0) * half;
+                // dims d and d + half together: norm, rotation, 16 dims of each half per step
+#pragma unroll 1
+                for (int c = 0; c < half; c += 16) {
+                    float lo[16], hi[16];
+                    tc_ld16(col0 + (uint32_t)c, lo);
+                    tc_ld16(col0 + (uint32_t)(half + c), hi);
+                    if (gamma != nullptr) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            lo[i] = __fmul_rn(__fmul_rn(lo[i], inv), __ldg(gamma + c + i));
+                            hi[i] = __fmul_rn(__fmul_rn(hi[i], inv), __ldg(gamma + half + c + i));
+                        }
+                    }
+                    if (rotate) {
+#pragma unroll
+                        for (int i = 0; i < 16; i += 2) {
+                            const float4 c2 = __ldg(reinterpret_cast<const float4*>(cs + c + i));   // (cos, sin) of two dims
+                            const float u0 = lo[i], w0 = hi[i], u1 = lo[i + 1], w1 = hi[i + 1];
+                            lo[i] = __fmaf_rn(u0, c2.x, -__fmul_rn(w0, c2.y));
+                            hi[i] = __fmaf_rn(w0, c2.x, __fmul_rn(u0, c2.y));
+                            lo[i + 1] = __fmaf_rn(u1, c2.z, -__fmul_rn(w1, c2.w));
+                            hi[i + 1] = __fmaf_rn(w1, c2.z, __fmul_rn(u1, c2.w));
+                        }
+                    }
+                    if (dst_a) {
+                        store8(dst_a + c, *reinterpret_cast<const float(*)[8]>(lo)); store8(dst_a + c + 8, *reinterpret_cast<const float(*)[8]>(lo + 8));
+                        store8(dst_a + half + c, *reinterpret_cast<const float(*)[8]>(hi)); store8(dst_a + half + c + 8, *reinterpret_cast<const float(*)[8]>(hi + 8));
+                    }
+                    if (dst_b) {
+                        store8(dst_b + c, *reinterpret_cast<const float(*)[8]>(lo)); store8(dst_b + c + 8, *reinterpret_cast<const float(*)[8]>(lo + 8));
+                        store8(dst_b + half + c, *reinterpret_cast<const float(*)[8]>(hi)); store8(dst_b + half + c + 8, *reinterpret_cast<const float(*)[8]>(hi + 8));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == GP_EPI_WARPS + 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+static int launch_qkv_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
+                             cudaStream_t stream) {
+    using S = QkvTokensSmem;
+    static bool configured = false;
+    static int n_sm = 0;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_qkv_tokens_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        IDM_REQUIRE(err == cudaSuccess, "gemm: cannot get %d bytes of shared memory: %s", S::TOTAL, cudaGetErrorString(err));
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    const int tiles_x = (N + GQ_BN - 1) / GQ_BN, tiles_y = (M + GT_BM - 1) / GT_BM;
+    const int n_tiles = tiles_x * tiles_y;
+    const int grid = n_tiles < n_sm ? n_tiles : n_sm;
+    idm_launch(gemm_qkv_tokens_kernel, dim3(grid), dim3(GP_THREADS), S::TOTAL, stream, mw, mx, e, M, N, kb_total, tiles_x,
+               n_tiles);
+    IDM_LAUNCH_CHECK("gemm_qkv_tokens");
+    return 0;
+}
+
 template <int BN, int STAGES, int EPI>
 static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
                              cudaStream_t stream) {
@@ -778,6 +994,13 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, i
         e.ws = workspace ? workspace + GT_COUNTER_SLOTS : nullptr;
     }
     CUtensorMap mw, mx;
+    if (EPI == EPI_QKV && splits == 1 && M > 256 && g_gemm_persistent && GQ_BN % e.q.hd == 0 && e.q.hd % 32 == 0 &&
+        (e.q.hd * 2) % 16 == 0) {
+        // many tokens: tokens on the accumulator's lanes, 256 features (whole heads) per tile
+        if (make_map(&mw, w, N, K, GQ_BN)) return 1;
+        if (make_map(&mx, x, M, K, GT_BM)) return 1;
+        return launch_qkv_tokens(mw, mx, e, M, N, kb_total, stream);
+    }
     if (splits == 1 && M > 256 && g_gemm_persistent) {
         // many tokens: the persistent kernel; 256-token tiles unless 128 fill more of the SMs
         const int tiles_x = (N + GT_BM - 1) / GT_BM;

@@ -384,7 +384,7 @@ def test_gemm_fused_swiglu(kernels, M, inter, K_):
 
 @pytest.mark.parametrize("M,n_q,n_kv,hd,hidden", [(3, 6, 2, 32, 96), (70, 4, 2, 16, 64), (9, 16, 8, 128, 1024),
                                                   (300, 8, 2, 128, 160), (64, 2, 1, 64, 72), (1030, 24, 4, 128, 192),
-                                                  (520, 40, 12, 64, 136)])
+                                                  (520, 40, 12, 64, 136), (300, 6, 2, 32, 96), (260, 3, 1, 16, 64)])
 def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, hidden):
     K = kernels("bfloat16")
     starts, lens = [5, 64], [M // 2, M - M // 2]
