@@ -66,25 +66,34 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t rank) {
-    uint32_t remote;
-    float4 v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
-    return v;
-}
-
 // The finished row of 128 features of one token, four consecutive features per lane, through the
 // fused epilogues (the cluster path: each block of a cluster finishes some of the tile's rows).
+// What a row's epilogue reads besides the product, fetched while the product is still being made: the
+// residual stream's old values (RESIDUAL) or the token's (cos, sin) (QKV).
+struct RowOperand { float4 a, b; bool have; };
+template <int EPI>
+__device__ __forceinline__ RowOperand row_operand(const GemmEpi& e, const Tile4Lane& L, int t, int f0, int lane, int n_features) {
+    RowOperand r;
+    r.a = r.b = make_float4(0.f, 0.f, 0.f, 0.f);
+    r.have = true;
+    if (EPI == EPI_RESIDUAL) {
+        const int f = f0 + lane * 4;
+        if (f < n_features) r.a = __ldcg(reinterpret_cast<const float4*>(e.out + (size_t)t * n_features + f));
+    } else if (EPI == EPI_QKV) {
+        const float4* c4 = qkv_tile4_cs(e.q, L, t, f0, lane);
+        if (c4) { r.a = __ldg(c4); r.b = __ldg(c4 + 1); }
+    }
+    return r;
+}
+
 template <int EPI>
 __device__ __forceinline__ void epilogue_row(const GemmEpi& e, float4 v, int t, int f0, int tile_x, int lane,
-                                             int n_features, const int* meta_row) {
+                                             int n_features, const int* meta_row, const Tile4Lane& L, const RowOperand& pre) {
     const int f = f0 + lane * 4;
     if (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
         if (f < n_features) {
             float4* p = reinterpret_cast<float4*>(e.out + (size_t)t * n_features + f);
-            if (EPI == EPI_RESIDUAL) { const float4 o = *p; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+            if (EPI == EPI_RESIDUAL) { const float4 o = pre.a; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
             *p = v;
         }
     } else if (EPI == EPI_SWIGLU) {
@@ -94,18 +103,28 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, float4 v, int t, 
         if (fg + 0 < e.inter) from_f32(y[0], silu_mul(v.x, v.y));
         if (fg + 1 < e.inter) from_f32(y[1], silu_mul(v.z, v.w));
     } else if (EPI == EPI_QKV) {
-        qkv_finish_tile4(e.q, v, t, f0, lane, meta_row[0], meta_row[1]);
+        qkv_finish_tile4_pre(e.q, L, v, t, f0, lane, meta_row[0], meta_row[1], pre.a, pre.b);
     }
 }
 
 // ---------------------------------------------------------------------------- kernel
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool PUSH = false>
 struct GemmSmem {
     static constexpr int A_BYTES = GT_BM * GT_BK * 2;
     static constexpr int B_BYTES = BN * GT_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BARRIER_BYTES = 2048;          // barriers and flags, then per-token cache rows (QKV)
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;   // + slack to align to 1024
+    // PUSH (the cluster path): behind the barriers, the rows this block finishes, one copy per block of
+    // the cluster (others write them while this block's ring may still be in use): S x ceil(BN / S) rows
+    // of 128 floats for a cluster of S <= 16 blocks
+    static constexpr int recv_rows() {
+        int most = 0;
+        for (int s = 2; s <= 16; ++s) { const int r = s * ((BN + s - 1) / s); most = r > most ? r : most; }
+        return most;
+    }
+    static constexpr int RECV_BYTES = PUSH ? recv_rows() * GT_BM * 4 : 0;
+    static constexpr int RECV_BAR = 512;                // offset of the arrival barrier inside the barrier area
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + BARRIER_BYTES + RECV_BYTES + 1024;   // + slack to align to 1024
 };
 
 template <int BN, int STAGES, int EPI, bool CL>
@@ -113,7 +132,8 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap map_x,
                                                                   const GemmEpi e, int n_tokens,
                                                                   int n_features, int kb_total, int kb_per_split) {
-    using S = GemmSmem<BN, STAGES>;
+    constexpr bool PUSH = CL;
+    using S = GemmSmem<BN, STAGES, PUSH>;
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;          // allocation: a power of two >= 32
     pdl_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
@@ -126,6 +146,8 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
     const uint32_t accum_bar = bars + 8u * (2 * STAGES);
     volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + STAGES * S::STAGE_BYTES + 8 * (2 * STAGES + 1));
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    const uint32_t recv_bar = bars + S::RECV_BAR;         // PUSH: all slices of this block's rows have arrived
+    const uint32_t recv_base = bars + S::BARRIER_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int f0 = blockIdx.x * GT_BM, t0 = blockIdx.y * BN;
@@ -135,6 +157,12 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         mbar_init(accum_bar, 1);
+        if (PUSH) {
+            // the rows this block finishes arrive as bytes: 128 floats per row from every block of the cluster
+            const int S_ = (int)gridDim.z, rank = (int)cluster_rank(), cols = min(BN, n_tokens - t0);
+            mbar_init(recv_bar, 1);
+            if (rank < cols) mbar_expect_tx(recv_bar, (uint32_t)(S_ * ((cols - rank + S_ - 1) / S_) * GT_BM * 4));
+        }
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -144,7 +172,10 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (PUSH) cluster_sync_all();                         // every block's arrival barrier exists before anyone arrives there
     const uint32_t tmem_d = *tmem_slot;
+    Tile4Lane tl4 = {};                                          // (cluster path, warps 0-3: see the epilogue)
+    RowOperand pre = {};
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
@@ -177,6 +208,8 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
                 const int s = i % STAGES;
                 ok = mbar_wait(full_bar(s), (i / STAGES) & 1, abort_flag, &g_gemm_error);
                 if (!ok) break;
+
+                if (i == 0)
                 tc_fence_after();
                 const uint32_t a_addr = base + s * S::STAGE_BYTES;
                 const uint64_t a_desc = umma_desc_kmajor(a_addr), b_desc = umma_desc_kmajor(a_addr + S::A_BYTES);
@@ -204,6 +237,13 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
                 meta[2 * tl + 1] = r % IDM_PAGE;
             }
         }
+        // cluster path: what the first row this warp will finish needs besides the product, asked for now
+        if (CL && EPI != EPI_PARTIAL) {
+            pdl_wait();
+            if (EPI == EPI_QKV) tl4 = qkv_tile4_lane(e.q, lane);
+            const int t_first = (int)cluster_rank() + (int)gridDim.z * warp;
+            if (t_first < min(BN, n_tokens - t0)) pre = row_operand<EPI>(e, tl4, t0 + t_first, f0, lane, n_features);
+        }
         if (mbar_wait(accum_bar, 0, abort_flag, &g_gemm_error)) {
             tc_fence_after();
             pdl_wait();                                           // (already satisfied: the activations came after it)
@@ -227,16 +267,44 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
                         }
                     }
                 }
-            } else if (CL) {
-                // cluster path: this block's slice of the tile goes to its own shared memory
-                float* xs = (float*)gen_base;
+            } else if (PUSH) {
+                // Cluster path (up to 64 tokens, K split).  Block r of the cluster finishes the token rows r, r + S, ...:
+                // every block sends its K-slice of those rows into r's shared memory (copy number = the
+                // sender's rank) with stores that count their bytes at r's barrier; r waits for the bytes
+                // of its rows, adds the S copies in ascending order and runs the epilogue.  No block waits
+                // for any other than through that barrier, and no sender waits at all.
+                const int S_ = (int)gridDim.z, rank = (int)cluster_rank();
+                const int cols = min(BN, n_tokens - t0);
+                const int slots = (BN + S_ - 1) / S_;             // rows a block can own
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 16) {
-                    if (t0 + c0 >= n_tokens) break;
+                    if (c0 >= cols) break;
                     float v[16];
                     tc_ld16(tmem_d + lane_base + (uint32_t)c0, v);
+                    int owner = c0 % S_, slot = c0 / S_;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) xs[(c0 + j) * GT_BM + fl] = v[j];
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j < cols)
+                            st_async_f32(recv_base + (uint32_t)(((rank * slots + slot) * GT_BM + fl) * 4), recv_bar, (uint32_t)owner, v[j]);
+                        if (++owner == S_) { owner = 0; ++slot; }
+                    }
+                }
+                if (rank < cols && mbar_wait_cluster(recv_bar, 0, abort_flag, &g_gemm_error)) {
+                    const int* meta = (const int*)(gen_base + STAGES * S::STAGE_BYTES + 1024);
+                    const float* recv = (const float*)(gen_base + STAGES * S::STAGE_BYTES + S::BARRIER_BYTES);
+                    for (int slot = warp; rank + S_ * slot < cols; slot += 4) {
+                        const int t = rank + S_ * slot;
+                        const RowOperand op = (slot == warp && pre.have) ? pre : row_operand<EPI>(e, tl4, t0 + t, f0, lane, n_features);
+                        float4 part[16];
+#pragma unroll
+                        for (int r = 0; r < 16; ++r)
+                            if (r < S_) part[r] = *reinterpret_cast<const float4*>(recv + ((r * slots + slot) * GT_BM + lane * 4));
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int r = 0; r < 16; ++r)
+                            if (r < S_) { acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w; }
+                        epilogue_row<EPI>(e, acc, t0 + t, f0, blockIdx.x, lane, n_features, meta + 2 * t, tl4, op);
+                    }
                 }
             } else {
                 float* xs = (float*)gen_base;                     // [BN][128] tile; the pipeline's stages are free now
@@ -385,31 +453,6 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
     }
     tc_fence_before();
     __syncthreads();
-    if (CL) {
-        // Every block of the cluster holds its K-slice of the tile in shared memory.  Block `rank`
-        // finishes the token rows rank, rank + S, ...: it adds the S slices in ascending order, read
-        // through distributed shared memory, and runs the epilogue on the row.  Two cluster barriers:
-        // all slices written before anyone reads; nobody leaves while others may still read.
-        cluster_sync_all();
-        if (warp < 4 && !*abort_flag) {
-            const uint32_t S_ = gridDim.z, rank = cluster_rank();
-            const int cols = min(BN, n_tokens - t0);
-            const int* meta = (const int*)(gen_base + STAGES * S::STAGE_BYTES + 1024);
-            for (int t = (int)rank + (int)S_ * warp; t < cols; t += (int)S_ * 4) {
-                const uint32_t addr = base + (uint32_t)(t * GT_BM + lane * 4) * 4u;
-                float4 part[16];
-#pragma unroll
-                for (int r = 0; r < 16; ++r)
-                    if (r < (int)S_) part[r] = ld_cluster_f4(addr, (uint32_t)r);
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int r = 0; r < 16; ++r)
-                    if (r < (int)S_) { acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w; }
-                epilogue_row<EPI>(e, acc, t0 + t, f0, blockIdx.x, lane, n_features, meta + 2 * t);
-            }
-        }
-        cluster_sync_all();
-    }
     if (warp == 5) {
         tmem_dealloc(tmem_d, TMEM_COLS);
     }
@@ -910,7 +953,7 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int k, int box_
 template <int BN, int STAGES, int EPI>
 static int launch_gemm_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
                                int kb_per_split, int splits, cudaStream_t stream) {
-    using S = GemmSmem<BN, STAGES>;
+    using S = GemmSmem<BN, STAGES, true>;
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI, true>,
@@ -1016,9 +1059,9 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, i
     // up to 64 tokens with K split: the slices are added inside a thread-block cluster
     if (EPI != EPI_PARTIAL && splits > 1 && splits <= 16 && M <= 64 && N % 4 == 0 && g_gemm_cluster) {
         switch (bn) {
-            case 16: return launch_gemm_cluster<16, 6, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
-            case 32: return launch_gemm_cluster<32, 6, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
-            default: return launch_gemm_cluster<64, 4, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
+            case 16: return launch_gemm_cluster<16, 5, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
+            case 32: return launch_gemm_cluster<32, 4, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
+            default: return launch_gemm_cluster<64, 3, EPI>(mw, mx, e, M, N, kb_total, per, splits, stream);
         }
     }
     switch (bn) {

@@ -46,6 +46,38 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// The same for a barrier that blocks of other SMs of the cluster arrive at (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word) {
+    if (mbar_try_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_cluster(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > TC_WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicExch(error_word, 1);
+            return false;
+        }
+    }
+}
+// One float into the shared memory of block `rank` of the cluster (same address as here), counted in
+// bytes at that block's barrier `bar`: who waits there sees the value, and the sender waits for nothing.
+__device__ __forceinline__ void st_async_f32(uint32_t local_addr, uint32_t local_bar, uint32_t rank, float v) {
+    uint32_t remote, remote_bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(local_bar), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];"
+                 ::"r"(remote), "f"(v), "r"(remote_bar) : "memory");
+}
+
 // ----------------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
