@@ -208,8 +208,6 @@ __global__ void __launch_bounds__(GT_THREADS) gemm_tcgen05_kernel(const __grid_c
                 const int s = i % STAGES;
                 ok = mbar_wait(full_bar(s), (i / STAGES) & 1, abort_flag, &g_gemm_error);
                 if (!ok) break;
-
-                if (i == 0)
                 tc_fence_after();
                 const uint32_t a_addr = base + s * S::STAGE_BYTES;
                 const uint64_t a_desc = umma_desc_kmajor(a_addr), b_desc = umma_desc_kmajor(a_addr + S::A_BYTES);
