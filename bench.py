@@ -39,7 +39,7 @@ def peaks():
             p["hbm_gbs"] = float(m.get("hbm_gbs", p["hbm_gbs"]))
             p["bf16_tflops"] = float(m.get("bf16_tflops", p["bf16_tflops"]))
             p["source"] = "measured"
-        except (ValueError, OSError):
+        except (ValueError, OSError, TypeError, AttributeError):
             pass
     return p
 
