@@ -552,11 +552,16 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __gri
                 ok = mbar_wait(tempty_bar(acc), ((it >> 1) & 1) ^ 1, abort_flag, &g_gemm_error);   // epilogue drained it
                 if (!ok) break;
                 tc_fence_after();
+                // (the look at the next stage's barrier is issued before this stage's MMAs, so that its answer
+                // is there when they have been issued: asking afterwards cost ~100 ns per k-block, a quarter
+                // of the time the tensor core needs for it)
+                bool ready = mbar_try(full_bar(cnt % STAGES), (cnt / STAGES) & 1);
                 for (int i = 0; i < kb_total && ok; ++i, ++cnt) {
                     const int s = cnt % STAGES;
-                    ok = mbar_wait(full_bar(s), (cnt / STAGES) & 1, abort_flag, &g_gemm_error);
+                    if (!ready) ok = mbar_wait(full_bar(s), (cnt / STAGES) & 1, abort_flag, &g_gemm_error);
                     if (!ok) break;
                     tc_fence_after();
+                    ready = i + 1 < kb_total && mbar_try(full_bar((cnt + 1) % STAGES), ((cnt + 1) / STAGES) & 1);
                     const uint32_t a_addr = base + s * S::STAGE_BYTES;
                     const uint64_t a_desc = umma_desc_kmajor(a_addr), b_desc = umma_desc_kmajor(a_addr + S::A_BYTES);
 #pragma unroll
