@@ -106,14 +106,14 @@ template <> struct Vec16<__nv_bfloat16> {
     }
 };
 
-// g * sigmoid(g) * u with the hardware exponential and reciprocal (relative error ~1e-6, far below the
+// g * sigmoid(g) * u with the hardware exponential and division (relative error ~1e-6, far below the
 // bfloat16 rounding of the result).  Every kernel that applies the activation uses this one formula,
 // so fused and separate paths give the same bits.  (src/detllm/ops/di_swiglu.py:43-45)
 __device__ __forceinline__ float silu_mul(float g, float u) {
 #if defined(IDM_F32)
     return g / (1.0f + expf(-g)) * u;                       // the 32-bit path stays exact
 #else
-    return __fmul_rn(__fmul_rn(g, __frcp_rn(1.0f + __expf(-g))), u);
+    return __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), u);
 #endif
 }
 

@@ -602,8 +602,13 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __gri
             ok = mbar_wait(tfull_bar(acc), (it >> 1) & 1, abort_flag, &g_gemm_error);
             if (!ok) break;
             tc_fence_after();
-#pragma unroll 1
-            for (int c0 = grp * GP_CHUNK; c0 < BN; c0 += GP_GROUPS * GP_CHUNK) {
+            // the accumulator columns of a chunk are asked for while the chunk before is worked on (two sets of
+            // registers in turn; the loop is unrolled so that which set is which is known at compile time)
+            uint32_t raw[2][GP_CHUNK];
+            if (t0 + grp * GP_CHUNK < n_tokens) tc_ld16_issue(tmem + acc * BN + lane_base + (uint32_t)(grp * GP_CHUNK), raw[0]);
+#pragma unroll
+            for (int ci = 0; ci < BN / (GP_GROUPS * GP_CHUNK); ++ci) {
+                const int c0 = grp * GP_CHUNK + ci * GP_GROUPS * GP_CHUNK;
                 if (t0 + c0 >= n_tokens) break;                    // uniform over the group
                 const int cols = min(GP_CHUNK, n_tokens - t0 - c0);
                 // q/k/v: the (cos, sin) of this warp's four token rows (rows quarter, quarter + 4, ...), asked for
@@ -619,7 +624,11 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __gri
                     }
                 }
                 float v[GP_CHUNK];
-                tc_ld16(tmem + acc * BN + lane_base + (uint32_t)c0, v);
+                tc_ld_wait();
+#pragma unroll
+                for (int j = 0; j < GP_CHUNK; ++j) v[j] = __uint_as_float(raw[ci & 1][j]);
+                if (ci + 1 < BN / (GP_GROUPS * GP_CHUNK) && t0 + c0 + GP_GROUPS * GP_CHUNK < n_tokens)
+                    tc_ld16_issue(tmem + acc * BN + lane_base + (uint32_t)(c0 + GP_GROUPS * GP_CHUNK), raw[(ci + 1) & 1]);
                 if (EPI == EPI_PARTIAL || EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
                     if (f < n_features) {
                         float old[GP_CHUNK];
