@@ -33,6 +33,12 @@
 #define AP_THREADS 192
 #define AP_TMEM_COLS 256
 #define AP_RESCALE_STEP 8.0f
+// A tile's key blocks may be cut into up to AP_MAX_SPLIT runs, each worked by a block of its own; a run
+// has at least AP_MIN_RUN key blocks.  (At most three blocks at a tile's end hold masked keys, so with
+// four every row sees the whole first block of every run: no run leaves a row without a key.)
+#define AP_MAX_SPLIT 4
+#define AP_MIN_RUN 4
+#define AP_COUNTERS 2048
 
 __device__ int g_attn_prefill_error = 0;
 
@@ -43,6 +49,10 @@ struct PrefillArgs {
     const int* table; int table_stride;
     int n_q, n_kv;
     float scale_log2;
+    int max_split;                                     // runs a tile's key blocks may be cut into (1: never cut)
+    int max_run;                                       // key blocks a run should not exceed
+    int* counters;                                     // [n_tiles * n_q] arrivals, zero between launches
+    float* parts;                                      // [n_tiles * n_q, max_split] partial results, PART floats each
 };
 
 template <int HD>
@@ -58,6 +68,8 @@ struct PrefillSmem {
     // two blocks per SM: 2 x (TOTAL + 1 KB the system keeps per block) must stay within 228 KB, which
     // leaves 512 bytes to reach the border (the array is declared with that alignment; the kernel checks)
     static constexpr int TOTAL = NEED + (HD == 128 ? 512 : 1024);
+    // a run's partial result: the unnormalised output as [HD / 4][128 rows] float4, then (max, sum) per row
+    static constexpr int PART = AP_BM * HD + 2 * AP_BM;
 };
 
 template <int HD>
@@ -87,6 +99,24 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
+
+    // blocks start in this order: all heads (and runs) of the longest tile first.  What is read here was
+    // written before the step began, not by the kernel before this one.
+    const int tile = blockIdx.y, head = blockIdx.x / a.max_split, run = blockIdx.x % a.max_split;
+    const int seq = a.tile_seq[tile], tstart = a.tile_start[tile];
+    const int g = head / (a.n_q / a.n_kv);
+    const int tok0 = a.cu_q[seq] + tstart;                       // first token (packed row) of the tile
+    const int q_len = a.cu_q[seq + 1] - a.cu_q[seq];
+    const int rows_valid = min(AP_BM, q_len - tstart);
+    const int p_first = a.q_start[seq] + tstart;                 // position of row 0
+    const int p_last = p_first + rows_valid - 1;
+    const int kv_len = a.kv_len[seq];
+    const int nb_tile = p_last / AP_BN + 1;                      // the tile's key blocks 0 .. nb_tile-1
+    const int n_runs = min(a.max_split, max(1, min((nb_tile + a.max_run - 1) / a.max_run, nb_tile / AP_MIN_RUN)));
+    if (run >= n_runs) return;                                   // (the whole block, before anything is set up)
+    const int b_first = run * nb_tile / n_runs;                  // this block's run of key blocks
+    const int nb = (run + 1) * nb_tile / n_runs - b_first;
+
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1); mbar_init(p_full, 4); mbar_init(o_done, 1);
         for (int i = 0; i < 2; ++i) {
@@ -104,17 +134,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t tmem_o = tmem + 128;                          // S buffers at columns 0 and 64, O from 128
     pdl_wait();                                                  // set-up done; now the previous kernel's results
 
-    const int tile = blockIdx.y, head = blockIdx.x;              // blocks start in this order: all heads of the longest tile first
-    const int seq = a.tile_seq[tile], tstart = a.tile_start[tile];
-    const int g = head / (a.n_q / a.n_kv);
-    const int tok0 = a.cu_q[seq] + tstart;                       // first token (packed row) of the tile
-    const int q_len = a.cu_q[seq + 1] - a.cu_q[seq];
-    const int rows_valid = min(AP_BM, q_len - tstart);
-    const int p_first = a.q_start[seq] + tstart;                 // position of row 0
-    const int p_last = p_first + rows_valid - 1;
-    const int kv_len = a.kv_len[seq];
-    const int nb = p_last / AP_BN + 1;                           // key blocks 0 .. nb-1
-
+    // from here on b counts the run's own key blocks (buffers and barrier phases go by it); the block's
+    // place among the sequence's keys is b_first + b
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -123,7 +144,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tma_load_3d(base + S::Q_OFF + h * AP_BM * 128, &map_q, h * 64, head, tok0, q_full);
             const int slot = a.slots[seq];
             for (int b = 0; b < nb; ++b) {
-                const int page = a.table[(size_t)slot * a.table_stride + b];
+                const int page = a.table[(size_t)slot * a.table_stride + b_first + b];
                 const int row = (page * a.n_kv + g) * IDM_PAGE;
                 const int vb = b & 1;                            // this block's key and value buffers
                 if (b >= 2 && !mbar_wait(k_empty(vb), ((b >> 1) - 1) & 1, abort_flag, &g_attn_prefill_error)) break;
@@ -197,11 +218,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty(b & 1));
-            const bool diagonal = (b + 1) * AP_BN - 1 > p_first;   // some key of the block lies past row 0's position
+            const int key0 = (b_first + b) * AP_BN;               // position of the block's first key
+            const bool diagonal = key0 + AP_BN - 1 > p_first;     // some key of the block lies past row 0's position
             if (diagonal) {
 #pragma unroll
                 for (int j = 0; j < AP_BN; ++j)
-                    if (b * AP_BN + j > p_r) sr[j] = 0xff800000u;  // -inf: p becomes 0 exactly
+                    if (key0 + j > p_r) sr[j] = 0xff800000u;      // -inf: p becomes 0 exactly
             }
             // the maximum of the raw scores (the scale is positive), four chains side by side
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -213,7 +235,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;
             float alpha = 1.f;
             if (m_blk > m_ref + AP_RESCALE_STEP || m_ref == -INFINITY) {
-                // (m_ref is -inf only before the first block, whose key 0 every row may see)
+                // (m_ref is -inf only before the run's first block, all of whose keys every row may see)
                 alpha = exp2f(m_ref - m_blk);                      // 0 the first time
                 m_ref = m_blk;
             }
@@ -223,10 +245,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             uint32_t packed[AP_BN / 2];
 #pragma unroll
             for (int j = 0; j < AP_BN; j += 4) {
-                const float p0 = exp2f(fmaf(__uint_as_float(sr[j]), a.scale_log2, neg_m));
-                const float p1 = exp2f(fmaf(__uint_as_float(sr[j + 1]), a.scale_log2, neg_m));
-                const float p2 = exp2f(fmaf(__uint_as_float(sr[j + 2]), a.scale_log2, neg_m));
-                const float p3 = exp2f(fmaf(__uint_as_float(sr[j + 3]), a.scale_log2, neg_m));
+                const float p0 = ex2_hw(fmaf(__uint_as_float(sr[j]), a.scale_log2, neg_m));
+                const float p1 = ex2_hw(fmaf(__uint_as_float(sr[j + 1]), a.scale_log2, neg_m));
+                const float p2 = ex2_hw(fmaf(__uint_as_float(sr[j + 2]), a.scale_log2, neg_m));
+                const float p3 = ex2_hw(fmaf(__uint_as_float(sr[j + 3]), a.scale_log2, neg_m));
                 sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
                 const __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1), pb = __floats2bfloat162_rn(p2, p3);
                 packed[j / 2] = *reinterpret_cast<const uint32_t*>(&pa);
@@ -259,10 +281,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
             }
             // rows of V past the sequence's end hold whatever the page held before: zero them
-            if ((b + 1) * AP_BN > kv_len) {
+            if (key0 + AP_BN > kv_len) {
                 ok = mbar_wait(v_full(b & 1), (b >> 1) & 1, abort_flag, &g_attn_prefill_error);
                 if (!ok) break;
-                const int first_bad = kv_len - b * AP_BN;          // >= 1
+                const int first_bad = kv_len - key0;               // >= 1
                 uint8_t* vb = gbase + S::V_OFF + (b & 1) * S::V_BYTES;
                 for (int idx = r; idx < (AP_BN - first_bad) * HT * 8; idx += AP_BM) {
                     const int chunk = idx % 8, rest = idx / 8;
@@ -276,10 +298,84 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (lane == 0) mbar_arrive(p_full);
         }
         if (ok) ok = mbar_wait(o_done, (nb - 1) & 1, abort_flag, &g_attn_prefill_error);
-        if (ok) {
+        T* orow = a.out + ((size_t)(tok0 + r) * a.n_q + head) * HD;
+        if (ok && n_runs > 1) {
+            // This run's result goes to its place among the tile's; the block that comes last adds them
+            // all, in the order of the runs whoever it is, so the sum does not depend on who came last.
+            tc_fence_after();
+            float* part0 = a.parts + (size_t)(tile * a.n_q + head) * a.max_split * S::PART;
+            float4* mine = reinterpret_cast<float4*>(part0 + (size_t)run * S::PART);
+#pragma unroll 1
+            for (int c = 0; c < HD; c += 16) {
+                float o[16];
+                tc_ld16(tmem_o + lane_base + c, o);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    mine[(c / 4 + k) * AP_BM + r] = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
+            }
+            reinterpret_cast<float2*>(mine + (HD / 4) * AP_BM)[r] = make_float2(m_ref, l);
+            __threadfence();
+            volatile int* last_flag = (volatile int*)(gbase + S::BAR_OFF + 128);
+            asm volatile("bar.sync 1, 128;" ::: "memory");         // the four softmax warps
+            if (r == 0) {
+                int* counter = a.counters + tile * a.n_q + head;
+                const int is_last = atomicAdd(counter, 1) == n_runs - 1;
+                if (is_last) *counter = 0;                         // ready for the next launch
+                *last_flag = is_last;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*last_flag) {
+                __threadfence();
+                float f[AP_MAX_SPLIT], m_all = -INFINITY, l_all = 0.f;
+#pragma unroll
+                for (int i = 0; i < AP_MAX_SPLIT; ++i) {
+                    f[i] = -INFINITY;
+                    if (i < n_runs) {
+                        f[i] = __ldcg(reinterpret_cast<const float2*>(part0 + (size_t)i * S::PART + AP_BM * HD) + r).x;
+                        m_all = fmaxf(m_all, f[i]);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < AP_MAX_SPLIT; ++i) {
+                    if (i < n_runs) {
+                        const float l_i = __ldcg(reinterpret_cast<const float2*>(part0 + (size_t)i * S::PART + AP_BM * HD) + r).y;
+                        f[i] = exp2f(f[i] - m_all);
+                        l_all += f[i] * l_i;
+                    }
+                }
+                const float inv = 1.0f / l_all;
+#pragma unroll 1
+                for (int c = 0; c < HD; c += 16) {
+                    float o[16];
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) o[k] = 0.f;
+#pragma unroll
+                    for (int i = 0; i < AP_MAX_SPLIT; ++i) {
+                        if (i < n_runs) {
+                            const float4* src = reinterpret_cast<const float4*>(part0 + (size_t)i * S::PART);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const float4 t = __ldcg(src + (c / 4 + k) * AP_BM + r);
+                                o[4 * k] += f[i] * t.x; o[4 * k + 1] += f[i] * t.y;
+                                o[4 * k + 2] += f[i] * t.z; o[4 * k + 3] += f[i] * t.w;
+                            }
+                        }
+                    }
+                    if (r < rows_valid) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv);
+                            w[i] = *reinterpret_cast<const uint32_t*>(&pk);
+                        }
+                        *reinterpret_cast<uint4*>(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(orow + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
+                }
+            }
+        } else if (ok) {
             tc_fence_after();
             const float inv = 1.0f / l;
-            T* orow = a.out + ((size_t)(tok0 + r) * a.n_q + head) * HD;
 #pragma unroll 1
             for (int c = 0; c < HD; c += 16) {
                 float o[16];
@@ -314,7 +410,7 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
                     cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(a.n_q, n_tiles);
+    dim3 grid(a.n_q * a.max_split, n_tiles);
     idm_launch(attention_prefill_kernel<HD>, dim3(grid), dim3(AP_THREADS), S::TOTAL, stream, mq, mk, mv, a);
     IDM_LAUNCH_CHECK("attention_prefill");
     return 0;
@@ -322,17 +418,40 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
 
 extern "C" int idm_attention_prefill_supports(int hd) { return hd == 64 || hd == 128; }
 
+// How many key blocks a run may have, for a step whose tiles have `key_blocks` in all (over all heads)
+// and `longest` in the longest: a fair share of the work of the SMs' block slots and a quarter, so that
+// only tiles that would keep one SM busy long after the others ended are cut.  A run's partial result
+// goes through memory, which costs about as much as four key blocks.
+extern "C" int idm_attention_prefill_max_run(long long key_blocks, int longest, int n_tiles, int n_q) {
+    if ((long long)n_tiles * n_q > AP_COUNTERS) return longest;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long share = (key_blocks + 2 * sms - 1) / (2 * sms);
+    const long long run = share + share / 4 + 2;
+    return (int)(run < AP_MIN_RUN ? AP_MIN_RUN : run > longest ? longest : run);
+}
+// Floats of scratch for that: arrival counters (zero at the first launch, left at zero by every launch),
+// then the runs' partial results.
+extern "C" long long idm_attention_prefill_scratch_floats(int n_tiles, int n_q, int hd, int split) {
+    if (split <= 1) return 0;
+    return (long long)AP_COUNTERS + (long long)n_tiles * n_q * split * (AP_BM * hd + 2 * AP_BM);
+}
+
 // q [n_tokens, n_q, hd]; out [n_tokens, n_q * hd]; the cache entry's pools [n_pages, n_kv, 64, hd];
 // tiles: (sequence, first token of the tile within the sequence's tokens of this step), longest first.
 extern "C" int idm_attention_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, int n_pages,
                                      const int* table, int table_stride, const int* tile_seq, const int* tile_start,
                                      int n_tiles, const int* cu_q, const int* q_start, const int* kv_len,
                                      const int* slots, int n_tokens, int n_q, int n_kv, int hd, float scale,
-                                     cudaStream_t stream) {
+                                     int split, int max_run, float* scratch, cudaStream_t stream) {
     if (n_tiles == 0 || n_tokens == 0) return 0;
     IDM_REQUIRE(idm_attention_prefill_supports(hd), "attention_prefill: head_dim=%d has no kernel here", hd);
     IDM_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention_prefill: bad head counts %d/%d", n_q, n_kv);
     IDM_REQUIRE(n_tiles <= 65535, "attention_prefill: %d tiles in one step; at most 65535", n_tiles);
+    IDM_REQUIRE(split >= 1 && split <= AP_MAX_SPLIT && (split == 1 || (scratch && (long long)n_tiles * n_q <= AP_COUNTERS)),
+                "attention_prefill: split=%d of %d tiles x %d heads (at most %d, with scratch, for at most %d of them)",
+                split, n_tiles, n_q, AP_MAX_SPLIT, AP_COUNTERS);
     CUtensorMap mq, mk, mv;
     {
         cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)n_q, (cuuint64_t)n_tokens};
@@ -354,6 +473,7 @@ extern "C" int idm_attention_prefill(const void* q, void* out, const void* k_poo
     a.out = (T*)out; a.tile_seq = tile_seq; a.tile_start = tile_start; a.cu_q = cu_q; a.q_start = q_start;
     a.kv_len = kv_len; a.slots = slots; a.table = table; a.table_stride = table_stride;
     a.n_q = n_q; a.n_kv = n_kv; a.scale_log2 = scale * 1.4426950408889634f;
+    a.max_split = split; a.max_run = max_run < 1 ? 1 : max_run; a.counters = (int*)scratch; a.parts = scratch ? scratch + AP_COUNTERS : nullptr;
     return hd == 64 ? launch_prefill<64>(mq, mk, mv, a, n_tiles, stream)
                     : launch_prefill<128>(mq, mk, mv, a, n_tiles, stream);
 }

@@ -106,6 +106,14 @@ template <> struct Vec16<__nv_bfloat16> {
     }
 };
 
+// 2^x by the hardware unit alone: relative error ~2e-7 * |x| rounding aside, results below 2^-126
+// become 0.  (exp2f without fast-math wraps the same instruction in a range fix of three more.)
+__device__ __forceinline__ float ex2_hw(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // g * sigmoid(g) * u with the hardware exponential and division (relative error ~1e-6, far below the
 // bfloat16 rounding of the result).  Every kernel that applies the activation uses this one formula,
 // so fused and separate paths give the same bits.  (src/detllm/ops/di_swiglu.py:43-45)

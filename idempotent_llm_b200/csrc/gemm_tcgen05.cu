@@ -717,8 +717,11 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __gri
 // (rows of x), its N axis 256 features (rows of w: whole heads), so an accumulator lane is a token and
 // a thread reads its token's whole head along the columns.  The per-head norm is then a sum inside the
 // thread, the rotation partner (d, d + head_dim / 2) a register of the same thread: no shuffles and no
-// turn through shared memory.  A head of a tile goes to one warp per 32 tokens; per tile 2 or 4 heads
-// x 4 token quarters keep 8 or 16 of the 16 epilogue warps busy, far below the time of the tile's MMAs.
+// turn through shared memory.  A head of a tile goes to one warp per 32 tokens; where a tile has fewer
+// heads than there are groups of epilogue warps (2 heads of 128), the dims of a head are shared out among
+// the groups left over: each adds up the head's squares for itself and finishes its part of the dims.
+// The epilogue is memory latency (a thread walks rows of its own: 32 lines per request), so it wants
+// every warp busy and the rotation table asked for before the accumulator is read.
 #define GQ_BN 256
 #define GQ_STAGES 4
 struct QkvTokensSmem {
@@ -829,7 +832,11 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __gri
             ok = mbar_wait(tfull_bar(acc), (it >> 1) & 1, abort_flag, &g_gemm_error);
             if (!ok) break;
             tc_fence_after();
-            for (int hh = grp; hh < hpt; hh += GP_GROUPS) {
+            // groups beyond the tile's heads share a head's dims: part `part` of `n_parts`
+            const int n_parts = (hpt < GP_GROUPS && (half / (GP_GROUPS / hpt)) % 16 == 0) ? GP_GROUPS / hpt : 1;
+            const int part = n_parts > 1 ? grp / hpt : 0;
+            const int c_first = part * (half / n_parts), c_end = c_first + half / n_parts;
+            for (int hh = n_parts > 1 ? grp % hpt : grp; hh < hpt; hh += GP_GROUPS) {
                 const int head = f0 / hd + hh;
                 if (head >= heads) break;                          // the last tile may reach past the last head
                 const uint32_t col0 = tmem + acc * BN + lane_base + (uint32_t)(hh * hd);
@@ -862,7 +869,12 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __gri
                 const float2* cs = a.cs + (size_t)(live ? t : 0) * half;
                 // dims d and d + half together: norm, rotation, 16 dims of each half per step
 #pragma unroll 1
-                for (int c = 0; c < half; c += 16) {
+                for (int c = c_first; c < c_end; c += 16) {
+                    float cs4[4][8];                               // (cos, sin) of the 16 dims, 32 bytes a piece
+                    if (rotate) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) load8_readonly(reinterpret_cast<const float*>(cs + c + 4 * i), cs4[i]);
+                    }
                     float lo[16], hi[16];
                     tc_ld16(col0 + (uint32_t)c, lo);
                     tc_ld16(col0 + (uint32_t)(half + c), hi);
@@ -875,23 +887,17 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __gri
                     }
                     if (rotate) {
 #pragma unroll
-                        for (int i = 0; i < 16; i += 2) {
-                            const float4 c2 = __ldg(reinterpret_cast<const float4*>(cs + c + i));   // (cos, sin) of two dims
-                            const float u0 = lo[i], w0 = hi[i], u1 = lo[i + 1], w1 = hi[i + 1];
-                            lo[i] = __fmaf_rn(u0, c2.x, -__fmul_rn(w0, c2.y));
-                            hi[i] = __fmaf_rn(w0, c2.x, __fmul_rn(u0, c2.y));
-                            lo[i + 1] = __fmaf_rn(u1, c2.z, -__fmul_rn(w1, c2.w));
-                            hi[i + 1] = __fmaf_rn(w1, c2.z, __fmul_rn(u1, c2.w));
+                        for (int i = 0; i < 16; i += 4) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float u = lo[i + j], w = hi[i + j];
+                                lo[i + j] = __fmaf_rn(u, cs4[i / 4][2 * j], -__fmul_rn(w, cs4[i / 4][2 * j + 1]));
+                                hi[i + j] = __fmaf_rn(w, cs4[i / 4][2 * j], __fmul_rn(u, cs4[i / 4][2 * j + 1]));
+                            }
                         }
                     }
-                    if (dst_a) {
-                        store8(dst_a + c, *reinterpret_cast<const float(*)[8]>(lo)); store8(dst_a + c + 8, *reinterpret_cast<const float(*)[8]>(lo + 8));
-                        store8(dst_a + half + c, *reinterpret_cast<const float(*)[8]>(hi)); store8(dst_a + half + c + 8, *reinterpret_cast<const float(*)[8]>(hi + 8));
-                    }
-                    if (dst_b) {
-                        store8(dst_b + c, *reinterpret_cast<const float(*)[8]>(lo)); store8(dst_b + c + 8, *reinterpret_cast<const float(*)[8]>(lo + 8));
-                        store8(dst_b + half + c, *reinterpret_cast<const float(*)[8]>(hi)); store8(dst_b + half + c + 8, *reinterpret_cast<const float(*)[8]>(hi + 8));
-                    }
+                    if (dst_a) { store16(dst_a + c, lo); store16(dst_a + half + c, hi); }
+                    if (dst_b) { store16(dst_b + c, lo); store16(dst_b + half + c, hi); }
                 }
             }
             tc_fence_before();
@@ -1049,8 +1055,9 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, i
         e.ws = workspace ? workspace + GT_COUNTER_SLOTS : nullptr;
     }
     CUtensorMap mw, mx;
+    auto on32 = [](const void* p) { return ((uintptr_t)p & 31) == 0; };   // (null counts: that output is not written)
     if (EPI == EPI_QKV && splits == 1 && M > 256 && g_gemm_persistent && GQ_BN % e.q.hd == 0 && e.q.hd % 32 == 0 &&
-        (e.q.hd * 2) % 16 == 0) {
+        on32(e.q.q_out) && on32(e.q.k_new) && on32(e.q.v_new) && on32(e.q.cache.k) && on32(e.q.cache.v) && on32(e.q.cs)) {
         // many tokens: tokens on the accumulator's lanes, 256 features (whole heads) per tile
         if (make_map(&mw, w, N, K, GQ_BN)) return 1;
         if (make_map(&mx, x, M, K, GT_BM)) return 1;

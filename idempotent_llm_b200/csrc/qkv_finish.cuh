@@ -30,6 +30,26 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&x)[8]) {
                                               *reinterpret_cast<const uint32_t*>(&c), *reinterpret_cast<const uint32_t*>(&d));
 }
 
+// sixteen consecutive bfloat16 elements as one 32-byte store, and eight floats as one 32-byte load (the
+// 256-bit forms of sm_100): a thread that walks a row of its own fills whole 32-byte sectors with one
+// request each, where narrower accesses cost the memory pipeline two.  Addresses on 32-byte borders.
+__device__ __forceinline__ void store16(__nv_bfloat16* p, const float (&x)[16]) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const __nv_bfloat162 t = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&t);
+    }
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 :: "l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+__device__ __forceinline__ void load8_readonly(const float* p, float (&v)[8]) {
+    asm volatile("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+                 : "l"(p));
+}
+
 struct QkvArgs {
     const float* qkv; int n_partials; size_t partial_stride;
     int n_tokens, n_q, n_kv, hd;

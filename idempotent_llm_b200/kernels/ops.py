@@ -35,6 +35,10 @@ class KernelError(RuntimeError):
     pass
 
 
+# the handle of the current stream of a device as an integer, without building a stream object
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _p(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
@@ -54,6 +58,7 @@ class Kernels:
         self.lib = builder.load(_DT[dtype])
         self.launches = 0                     # kernels of this library launched so far
         self._scratch = {}
+        self._device_index = device.index if device.index is not None else 0
         self._retired = []
         L = self.lib
         for name in ("idm_embed", "idm_add_rmsnorm", "idm_rope_table", "idm_qkv_finish", "idm_kv_write_ring",
@@ -74,6 +79,8 @@ class Kernels:
         self.gemm_impl = os.environ.get("IDM_GEMM", "tcgen05")
         if dtype == torch.bfloat16:
             L.idm_gemm_bf16_workspace_floats.restype = c_longlong
+            L.idm_attention_prefill_scratch_floats.restype = c_longlong
+            L.idm_attention_prefill_max_run.restype = c_int
         # fused epilogues of the tensor-core product (residual add, SwiGLU, q/k/v finish): parts use
         # them when this is True and fall back to separate kernels otherwise
         self.fused = (dtype == torch.bfloat16 and self.gemm_impl == "tcgen05"
@@ -86,13 +93,20 @@ class Kernels:
         self.fused_max_small = int(os.environ.get("IDM_FUSED_MAX_SMALL", "64"))
         # "tcgen05": prompts' attention on the tensor cores; "general": the one-warp-per-query kernel
         self.prefill_impl = os.environ.get("IDM_PREFILL", "tcgen05")
+        # the most key blocks (of 64) one block of that kernel works through before a tile is cut into
+        # runs for several blocks; 0: by the step's size
+        self.prefill_run = int(os.environ.get("IDM_PREFILL_RUN", "0"))
         self.page = L.idm_page_tokens()
+        self._gemm_plans = {}          # (M, N, K) -> (splits of the inner axis, workspace floats)
 
     def use_fused(self, n_tokens: int) -> bool:
         return self.fused and (n_tokens >= self.fused_min_tokens or n_tokens <= self.fused_max_small)
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
+        # (the stream object torch builds for current_stream() costs several microseconds per launch)
+        if _raw_stream is not None:
+            return c_void_p(_raw_stream(self._device_index))
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
 
     def _check(self, rc: int, n_launches: int = 1):
@@ -236,14 +250,26 @@ class Kernels:
                     items.append((ctx.host_starts[i] + min(st + 127, L - 1), i, st))
             items.sort(key=lambda t: -t[0])
             host = torch.tensor([[i for _, i, _ in items], [st for _, _, st in items]], dtype=torch.int32)
-            tiles = ctx.memo["prefill_tiles"] = (host.to(self.device), len(items))
-        dev, n_tiles = tiles
+            blocks = [last // 64 + 1 for last, _, _ in items]        # key blocks of each tile
+            dev = host.to(self.device)
+            tiles = ctx.memo["prefill_tiles"] = (dev, dev[0].data_ptr(), dev[1].data_ptr(), len(items), sum(blocks),
+                                                 blocks[0])
+        _, tile_seq, tile_start, n_tiles, key_blocks, longest = tiles
+        plan = ctx.memo.get(("prefill_runs", n_q, hd, self.prefill_run))
+        if plan is None:
+            max_run = self.prefill_run or self.lib.idm_attention_prefill_max_run(
+                c_longlong(key_blocks * n_q), c_int(longest), c_int(n_tiles), c_int(n_q))
+            split = min(4, -(-longest // max_run))
+            need = self.lib.idm_attention_prefill_scratch_floats(c_int(n_tiles), c_int(n_q), c_int(hd), c_int(split))
+            plan = ctx.memo[("prefill_runs", n_q, hd, self.prefill_run)] = (max_run, split, need)
+        max_run, split, need = plan
+        scratch = self.scratch("attention_prefill", need) if need else None
         self._check(self.lib.idm_attention_prefill(
             c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_int(kv.k.shape[0]),
-            c_void_p(_p(kv.table)), c_int(kv.table.shape[1]), c_void_p(dev[0].data_ptr()),
-            c_void_p(dev[1].data_ptr()), c_int(n_tiles), c_void_p(_p(ctx.cu_q)), c_void_p(_p(ctx.q_start)),
+            c_void_p(_p(kv.table)), c_int(kv.table.shape[1]), c_void_p(tile_seq), c_void_p(tile_start), c_int(n_tiles), c_void_p(_p(ctx.cu_q)), c_void_p(_p(ctx.q_start)),
             c_void_p(_p(ctx.kv_len)), c_void_p(_p(ctx.slots)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads),
-            c_int(hd), c_float(scale), self._stream()))
+            c_int(hd), c_float(scale), c_int(split), c_int(max_run), c_void_p(_p(scratch)),
+            self._stream()))
         return out
 
     def attention_prefill_status(self) -> int:
@@ -326,9 +352,11 @@ class Kernels:
             raise KernelError(f"gemm: input rows have {Kd} elements, weight rows {K2}")
         if Kd % 8:
             raise KernelError(f"gemm: the inner size {Kd} must be a multiple of 8 for the fused kernels")
-        P = self.lib.idm_gemm_bf16_splits(c_int(M), c_int(N), c_int(Kd))
-        ws = self.scratch("gemm_ws", self.lib.idm_gemm_bf16_workspace_floats(c_int(M), c_int(N), c_int(P)))
-        return M, N, Kd, P, ws
+        plan = self._gemm_plans.get((M, N, Kd))
+        if plan is None:
+            P = self.lib.idm_gemm_bf16_splits(c_int(M), c_int(N), c_int(Kd))
+            plan = self._gemm_plans[(M, N, Kd)] = (P, self.lib.idm_gemm_bf16_workspace_floats(c_int(M), c_int(N), c_int(P)))
+        return M, N, Kd, plan[0], self.scratch("gemm_ws", plan[1])
 
     def gemm_store(self, x, w) -> torch.Tensor:
         """``x . w^T`` finished in 32-bit ``[M, N]``."""

@@ -231,6 +231,58 @@ def test_attention_prefill_tensor_core_kernel(kernels, n_q, n_kv, hd):
     assert (got - vs[4][5, 0]).abs().max() < 0.05, "the far key did not dominate"
 
 
+@pytest.mark.parametrize("max_run", [1000, 11, 4, 0])
+@pytest.mark.parametrize("n_q,n_kv,hd", [(2, 1, 128), (3, 3, 64)])
+def test_attention_prefill_with_a_tile_s_keys_cut_into_runs(kernels, max_run, n_q, n_kv, hd):
+    """Long tiles of a short step are worked by several blocks, each a run of the tile's key blocks, and
+    the last to end adds the runs up.  Queries of the last tiles look at one key in the first run, at one
+    in a middle run and at the last key before the diagonal; a second launch gives the same bits, and
+    the arrival counters are back at zero (a third launch, of other sequences, is right too)."""
+    K = kernels("bfloat16")
+    hist, new = [0, 450, 0], [1300, 900, 130]
+    lens = [h + n for h, n in zip(hist, new)]
+    cache, slots, ks, vs = _cache_with(K, "bfloat16", n_kv, hd, None, lens, seed=130, max_tokens=64 * 64)
+    kv = cache.view(0)
+    scale = 1.0 / math.sqrt(hd)
+    q = [_randn(n, n_q, hd, seed=140 + i) for i, n in enumerate(new)]
+    planted = [(0, 1299, 0, 7), (0, 1250, n_q - 1, 700), (0, 1200, 0, 1151), (1, 899, n_q - 1, 449), (1, 600, 0, 1000)]
+    for i, t, h, key in planted:
+        q[i][t, h] = ks[i][key, h // (n_q // n_kv)] * 4.0
+    qd = torch.cat(q).to(torch.bfloat16).cuda()
+    packed, n, q_lens = pack_step_host(slots, hist, [[0] * m for m in new])
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, hist)
+    old = K.prefill_run
+    K.prefill_run = max_run
+    try:
+        out = K.attention_prefill(qd, kv, ctx, scale).view(-1, n_q, hd)
+        again = K.attention_prefill(qd, kv, ctx, scale).view(-1, n_q, hd)
+        torch.cuda.synchronize()
+        assert K.attention_prefill_status() == 0, "a bounded wait inside the kernel ran out"
+        assert torch.equal(out, again), "the sum of the runs depends on which block came last"
+        gen = K.attention_generic(qd, kv, ctx, None, None, scale, None).view(-1, n_q, hd)
+        assert torch.isfinite(out).all()
+        assert helpers.rel_err(out, gen) < 2 * KTOL["bfloat16"]
+        off = [0, new[0], new[0] + new[1]]
+        for i, t, h, key in planted:
+            ref = _attn_ref(qd[off[i] + t].double().cpu(), ks[i], vs[i], scale, None, hist[i] + t)
+            assert helpers.rel_err(out[off[i] + t], ref) < KTOL["bfloat16"], f"sequence {i} token {t}"
+            got = out[off[i] + t, h].double().cpu()
+            assert (got - vs[i][key, h // (n_q // n_kv)]).abs().max() < 0.05, f"key {key} did not dominate"
+        for i, m in enumerate(new):
+            for t in [0, 1, 127, 128, m // 2, m - 2, m - 1]:
+                ref = _attn_ref(qd[off[i] + t].double().cpu(), ks[i], vs[i], scale, None, hist[i] + t)
+                assert helpers.rel_err(out[off[i] + t], ref) < KTOL["bfloat16"], f"sequence {i} token {t} of {m}"
+        # other sequences, other counters in use: only the last two
+        packed, n2, q_lens2 = pack_step_host(slots[1:], hist[1:], [[0] * m for m in new[1:]])
+        ctx2 = context_from_packed(packed.cuda(), n2, slots[1:], q_lens2, hist[1:])
+        out2 = K.attention_prefill(qd[new[0]:].contiguous(), kv, ctx2, scale).view(-1, n_q, hd)
+        torch.cuda.synchronize()
+        assert K.attention_prefill_status() == 0
+        assert torch.equal(out2, out[new[0]:]), "a tile's result depends on what else the step holds"
+    finally:
+        K.prefill_run = old
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_qkv_finish_norm_rotation_and_cache_write(kernels, dtype):
     K = kernels(dtype)
