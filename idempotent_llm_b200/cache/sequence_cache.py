@@ -194,6 +194,9 @@ class SequenceCache:
             if new_len > self.max_seq_len:
                 raise CacheError(f"a sequence of {new_len} tokens exceeds the cache's limit of "
                                  f"{self.max_seq_len} tokens per sequence")
+        full = [g for g in self.groups if g.kind == "full"]
+        if all(n <= PAGE_TOKENS * len(g.pages_of.get(s, ())) for g in full for s, n in wanted):
+            return                                   # (most single-token steps: the last page has room)
         for g in self.groups:
             if g.kind == "full":
                 need = sum(g.pages_needed(s, n) for s, n in wanted)

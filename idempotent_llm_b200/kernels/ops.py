@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -43,6 +44,48 @@ def _p(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+# Every entry point of the libraries: result type and, per argument, p pointer (or stream) / i int /
+# f float / q long long, in the order of the C declarations in csrc/ (a test reads the declarations
+# and compares).
+SIGNATURES = {
+    "idm_last_error": (ctypes.c_char_p, ""),
+    "idm_dtype_name": (ctypes.c_char_p, ""),
+    "idm_page_tokens": (c_int, ""),
+    "idm_set_pdl": (None, "i"),
+    "idm_embed": (c_int, "pppiip"),
+    "idm_add_rmsnorm": (c_int, "ppiqpfppiip"),
+    "idm_rope_table": (c_int, "pppiip"),
+    "idm_qkv_finish": (c_int, "piqiiiippfpppppppiipppp"),
+    "idm_kv_write_ring": (c_int, "pppppiippppiiip"),
+    "idm_swiglu": (c_int, "piqpiiip"),
+    "idm_sample_scratch_floats": (c_longlong, "ii"),
+    "idm_sample": (c_int, "piifpppp"),
+    "idm_decode_advance": (c_int, "pppppppiip"),
+    "idm_attention_generic": (c_int, "pppppiipppppppiiiifip"),
+    "idm_attention_decode_supports": (c_int, "i"),
+    "idm_attention_decode_chunk": (c_int, ""),
+    "idm_attention_decode_scratch_floats": (c_longlong, "iiii"),
+    "idm_attention_decode": (c_int, "pppppiipppiiiiifip"),
+    "idm_attention_decode_static": (c_int, "pppppiippiiiiifip"),
+    "idm_attention_prefill_supports": (c_int, "i"),
+    "idm_attention_prefill_max_run": (c_int, "qiii"),
+    "idm_attention_prefill_scratch_floats": (c_longlong, "iiii"),
+    "idm_attention_prefill": (c_int, "ppppipippippppiiiifiipp"),
+    "idm_attention_prefill_status": (c_int, ""),
+    "idm_gemm_f32": (c_int, "pppiiip"),
+    "idm_gemm_bf16_splits": (c_int, "iii"),
+    "idm_gemm_bf16_workspace_floats": (c_longlong, "iii"),
+    "idm_gemm_set_cluster": (None, "i"),
+    "idm_gemm_set_persistent": (None, "i"),
+    "idm_gemm_bf16": (c_int, "pppiiiip"),
+    "idm_gemm_bf16_store": (c_int, "ppppiiiip"),
+    "idm_gemm_bf16_residual": (c_int, "ppppiiiip"),
+    "idm_gemm_bf16_swiglu": (c_int, "ppppiiiip"),
+    "idm_gemm_bf16_qkv": (c_int, "pppiiiiiippfpppppppiipppp"),
+    "idm_gemm_status": (c_int, ""),
+}
+
+
 class Kernels:
     def __init__(self, dtype: torch.dtype, device):
         device = torch.device(device)
@@ -61,26 +104,18 @@ class Kernels:
         self._device_index = device.index if device.index is not None else 0
         self._retired = []
         L = self.lib
-        for name in ("idm_embed", "idm_add_rmsnorm", "idm_rope_table", "idm_qkv_finish", "idm_kv_write_ring",
-                     "idm_swiglu", "idm_sample", "idm_attention_generic", "idm_attention_decode",
-                     "idm_attention_decode_supports", "idm_decode_advance"):
-            getattr(L, name).restype = c_int
-        L.idm_attention_decode_scratch_floats.restype = c_longlong
-        L.idm_sample_scratch_floats.restype = c_longlong
-        if dtype == torch.float32:
-            L.idm_gemm_f32.restype = c_int
-        else:
-            for name in ("idm_gemm_bf16", "idm_gemm_bf16_splits", "idm_gemm_status", "idm_gemm_bf16_store",
-                         "idm_gemm_bf16_residual", "idm_gemm_bf16_swiglu", "idm_gemm_bf16_qkv", "idm_attention_prefill",
-                         "idm_attention_prefill_supports", "idm_attention_prefill_status"):
-                getattr(L, name).restype = c_int
+        # argument and result types of every entry point: with them set, plain integers (addresses,
+        # sizes), floats and None (a null pointer) go in as they are -- no ctypes object per argument
+        kinds = {"p": c_void_p, "i": c_int, "f": c_float, "q": c_longlong}
+        for name, (result, args) in SIGNATURES.items():
+            fn = getattr(L, name, None)
+            if fn is None:
+                continue                      # an entry point of the other precision's library
+            fn.restype = result
+            fn.argtypes = [kinds[a] for a in args]
         # "tcgen05": the hand-written tensor-core kernel; "library": the GEMM torch wraps (kept to
         # compare against)
         self.gemm_impl = os.environ.get("IDM_GEMM", "tcgen05")
-        if dtype == torch.bfloat16:
-            L.idm_gemm_bf16_workspace_floats.restype = c_longlong
-            L.idm_attention_prefill_scratch_floats.restype = c_longlong
-            L.idm_attention_prefill_max_run.restype = c_int
         # fused epilogues of the tensor-core product (residual add, SwiGLU, q/k/v finish): parts use
         # them when this is True and fall back to separate kernels otherwise
         self.fused = (dtype == torch.bfloat16 and self.gemm_impl == "tcgen05"
@@ -106,8 +141,8 @@ class Kernels:
     def _stream(self):
         # (the stream object torch builds for current_stream() costs several microseconds per launch)
         if _raw_stream is not None:
-            return c_void_p(_raw_stream(self._device_index))
-        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+            return _raw_stream(self._device_index)
+        return torch.cuda.current_stream(self.device).cuda_stream
 
     def _check(self, rc: int, n_launches: int = 1):
         if rc != 0:
@@ -135,8 +170,8 @@ class Kernels:
         self._need(table, self.dtype, "embed table")
         n, hidden = tokens.numel(), table.shape[1]
         h = torch.empty((n, hidden), dtype=torch.float32, device=self.device)
-        self._check(self.lib.idm_embed(c_void_p(_p(tokens)), c_void_p(_p(table)), c_void_p(_p(h)),
-                                       c_int(n), c_int(hidden), self._stream()))
+        self._check(self.lib.idm_embed(_p(tokens), _p(table), _p(h),
+                                       n, hidden, self._stream()))
         return h
 
     def add_rmsnorm(self, h, delta, gamma, eps: float, rows=None) -> torch.Tensor:
@@ -155,9 +190,9 @@ class Kernels:
             self._need(rows, torch.int32, "rows")
         n_out = n if rows is None else rows.numel()
         x = torch.empty((n_out, hidden), dtype=self.dtype, device=self.device)
-        self._check(self.lib.idm_add_rmsnorm(c_void_p(_p(h)), c_void_p(_p(delta)), c_int(P), c_longlong(stride),
-                                             c_void_p(_p(gamma)), c_float(eps), c_void_p(_p(x)),
-                                             c_void_p(_p(rows)), c_int(n_out), c_int(hidden), self._stream()))
+        self._check(self.lib.idm_add_rmsnorm(_p(h), _p(delta), P, stride,
+                                             _p(gamma), eps, _p(x),
+                                             _p(rows), n_out, hidden, self._stream()))
         return x
 
     def rope_table(self, positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
@@ -165,8 +200,8 @@ class Kernels:
         self._need(inv_freq, torch.float64, "inv_freq")
         n, half = positions.numel(), inv_freq.numel()
         cs = torch.empty((n, half, 2), dtype=torch.float32, device=self.device)
-        self._check(self.lib.idm_rope_table(c_void_p(_p(positions)), c_void_p(_p(inv_freq)), c_void_p(_p(cs)),
-                                            c_int(n), c_int(half), self._stream()))
+        self._check(self.lib.idm_rope_table(_p(positions), _p(inv_freq), _p(cs),
+                                            n, half, self._stream()))
         return cs
 
     def qkv_finish(self, qkv, n_q, n_kv, hd, q_gamma, k_gamma, eps, cs, ctx, kv, keep_new: bool):
@@ -189,13 +224,13 @@ class Kernels:
         if kv is not None:
             self._check_kv(kv, n_kv, hd)
         self._check(self.lib.idm_qkv_finish(
-            c_void_p(_p(qkv)), c_int(P), c_longlong(n * width), c_int(n), c_int(n_q), c_int(n_kv), c_int(hd),
-            c_void_p(_p(q_gamma)), c_void_p(_p(k_gamma)), c_float(eps), c_void_p(_p(cs)),
-            c_void_p(_p(q)), c_void_p(_p(k_new)), c_void_p(_p(v_new)),
-            c_void_p(_p(kv.k) if kv is not None else None), c_void_p(_p(kv.v) if kv is not None else None),
-            c_void_p(_p(kv.table) if kv is not None else None),
-            c_int(kv.table.shape[1] if kv is not None else 0), c_int(kv.ring if kv is not None else 0),
-            c_void_p(_p(ctx.token_seq)), c_void_p(_p(ctx.positions)), c_void_p(_p(ctx.slots)), self._stream()))
+            _p(qkv), P, n * width, n, n_q, n_kv, hd,
+            _p(q_gamma), _p(k_gamma), eps, _p(cs),
+            _p(q), _p(k_new), _p(v_new),
+            (_p(kv.k) if kv is not None else None), (_p(kv.v) if kv is not None else None),
+            (_p(kv.table) if kv is not None else None),
+            (kv.table.shape[1] if kv is not None else 0), (kv.ring if kv is not None else 0),
+            _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots), self._stream()))
         return q, k_new, v_new
 
     def _check_kv(self, kv, n_kv, hd):
@@ -207,10 +242,10 @@ class Kernels:
         n, n_kv, hd = k_new.shape
         self._check_kv(kv, n_kv, hd)
         self._check(self.lib.idm_kv_write_ring(
-            c_void_p(_p(k_new)), c_void_p(_p(v_new)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)),
-            c_void_p(_p(kv.table)), c_int(kv.table.shape[1]), c_int(kv.ring), c_void_p(_p(ctx.token_seq)),
-            c_void_p(_p(ctx.positions)), c_void_p(_p(ctx.slots)), c_void_p(_p(ctx.kv_len)), c_int(n),
-            c_int(n_kv), c_int(hd), self._stream()))
+            _p(k_new), _p(v_new), _p(kv.k), _p(kv.v),
+            _p(kv.table), kv.table.shape[1], kv.ring, _p(ctx.token_seq),
+            _p(ctx.positions), _p(ctx.slots), _p(ctx.kv_len), n,
+            n_kv, hd, self._stream()))
 
     def attention(self, q, kv, ctx, k_new, v_new, scale: float, window) -> torch.Tensor:
         """Causal attention of the step's queries over the cache entry; returns [N, n_q * hd]."""
@@ -222,17 +257,17 @@ class Kernels:
         # 32-bit keeps ONE kernel for prompts and single tokens, so its logits are the same bits
         # however a sequence is cut into steps; bfloat16 takes the bandwidth-bound decode kernel
         if (self.dtype != torch.float32 and ctx.single_token and k_new is None
-                and self.lib.idm_attention_decode_supports(c_int(hd))):
+                and self.lib.idm_attention_decode_supports(hd)):
             return self.attention_decode(q, kv, ctx.slots, ctx.kv_len, ctx.max_kv_len, scale, w, out)
         if (self.dtype == torch.bfloat16 and self.prefill_impl == "tcgen05" and not ctx.single_token
-                and k_new is None and not w and kv.ring == 0 and self.lib.idm_attention_prefill_supports(c_int(hd))):
+                and k_new is None and not w and kv.ring == 0 and self.lib.idm_attention_prefill_supports(hd)):
             return self.attention_prefill(q, kv, ctx, scale, out)
         self._check(self.lib.idm_attention_generic(
-            c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_void_p(_p(kv.table)),
-            c_int(kv.table.shape[1]), c_int(kv.ring), c_void_p(_p(k_new)), c_void_p(_p(v_new)),
-            c_void_p(_p(ctx.token_seq)), c_void_p(_p(ctx.positions)), c_void_p(_p(ctx.slots)),
-            c_void_p(_p(ctx.q_start)), c_void_p(_p(ctx.cu_q)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads),
-            c_int(hd), c_float(scale), c_int(w), self._stream()))
+            _p(q), _p(out), _p(kv.k), _p(kv.v), _p(kv.table),
+            kv.table.shape[1], kv.ring, _p(k_new), _p(v_new),
+            _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots),
+            _p(ctx.q_start), _p(ctx.cu_q), n, n_q, kv.n_kv_heads,
+            hd, scale, w, self._stream()))
         return out
 
     def attention_prefill(self, q, kv, ctx, scale: float, out=None) -> torch.Tensor:
@@ -258,17 +293,17 @@ class Kernels:
         plan = ctx.memo.get(("prefill_runs", n_q, hd, self.prefill_run))
         if plan is None:
             max_run = self.prefill_run or self.lib.idm_attention_prefill_max_run(
-                c_longlong(key_blocks * n_q), c_int(longest), c_int(n_tiles), c_int(n_q))
+                key_blocks * n_q, longest, n_tiles, n_q)
             split = min(4, -(-longest // max_run))
-            need = self.lib.idm_attention_prefill_scratch_floats(c_int(n_tiles), c_int(n_q), c_int(hd), c_int(split))
+            need = self.lib.idm_attention_prefill_scratch_floats(n_tiles, n_q, hd, split)
             plan = ctx.memo[("prefill_runs", n_q, hd, self.prefill_run)] = (max_run, split, need)
         max_run, split, need = plan
         scratch = self.scratch("attention_prefill", need) if need else None
         self._check(self.lib.idm_attention_prefill(
-            c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_int(kv.k.shape[0]),
-            c_void_p(_p(kv.table)), c_int(kv.table.shape[1]), c_void_p(tile_seq), c_void_p(tile_start), c_int(n_tiles), c_void_p(_p(ctx.cu_q)), c_void_p(_p(ctx.q_start)),
-            c_void_p(_p(ctx.kv_len)), c_void_p(_p(ctx.slots)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads),
-            c_int(hd), c_float(scale), c_int(split), c_int(max_run), c_void_p(_p(scratch)),
+            _p(q), _p(out), _p(kv.k), _p(kv.v), kv.k.shape[0],
+            _p(kv.table), kv.table.shape[1], tile_seq, tile_start, n_tiles, _p(ctx.cu_q), _p(ctx.q_start),
+            _p(ctx.kv_len), _p(ctx.slots), n, n_q, kv.n_kv_heads,
+            hd, scale, split, max_run, _p(scratch),
             self._stream()))
         return out
 
@@ -280,11 +315,11 @@ class Kernels:
         n, n_q, hd = q.shape
         out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
         self._check(self.lib.idm_attention_generic(
-            c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_void_p(_p(kv.table)),
-            c_int(kv.table.shape[1]), c_int(kv.ring), c_void_p(_p(k_new)), c_void_p(_p(v_new)),
-            c_void_p(_p(ctx.token_seq)), c_void_p(_p(ctx.positions)), c_void_p(_p(ctx.slots)),
-            c_void_p(_p(ctx.q_start)), c_void_p(_p(ctx.cu_q)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads),
-            c_int(hd), c_float(scale), c_int(int(window) if window else 0), self._stream()))
+            _p(q), _p(out), _p(kv.k), _p(kv.v), _p(kv.table),
+            kv.table.shape[1], kv.ring, _p(k_new), _p(v_new),
+            _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots),
+            _p(ctx.q_start), _p(ctx.cu_q), n, n_q, kv.n_kv_heads,
+            hd, scale, (int(window) if window else 0), self._stream()))
         return out
 
     def attention_decode(self, q, kv, slots, kv_len, max_kv_len: int, scale: float, window: int,
@@ -294,13 +329,13 @@ class Kernels:
         if out is None:
             out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
         n_chunks = -(-max_kv_len // self.lib.idm_attention_decode_chunk())
-        need = self.lib.idm_attention_decode_scratch_floats(c_int(n), c_int(n_q), c_int(n_chunks), c_int(hd))
+        need = self.lib.idm_attention_decode_scratch_floats(n, n_q, n_chunks, hd)
         scratch = self.scratch("attention_decode", need)
         self._check(self.lib.idm_attention_decode(
-            c_void_p(_p(q)), c_void_p(_p(out)), c_void_p(_p(kv.k)), c_void_p(_p(kv.v)), c_void_p(_p(kv.table)),
-            c_int(kv.table.shape[1]), c_int(kv.ring), c_void_p(_p(slots)), c_void_p(_p(kv_len)),
-            c_void_p(_p(scratch)), c_int(n), c_int(n_q), c_int(kv.n_kv_heads), c_int(hd), c_int(max_kv_len),
-            c_float(scale), c_int(window), self._stream()))
+            _p(q), _p(out), _p(kv.k), _p(kv.v), _p(kv.table),
+            kv.table.shape[1], kv.ring, _p(slots), _p(kv_len),
+            _p(scratch), n, n_q, kv.n_kv_heads, hd, max_kv_len,
+            scale, window, self._stream()))
         return out
 
     def swiglu(self, gu: torch.Tensor, tiled_inter: Optional[int] = None) -> torch.Tensor:
@@ -317,8 +352,8 @@ class Kernels:
             if width != -(-inter // 64) * 128:
                 raise KernelError(f"tiled gate-up rows have {width} elements, expected {-(-inter // 64) * 128}")
         y = torch.empty((n, inter), dtype=self.dtype, device=self.device)
-        self._check(self.lib.idm_swiglu(c_void_p(_p(gu)), c_int(P), c_longlong(n * width), c_void_p(_p(y)),
-                                        c_int(n), c_int(inter), c_int(tiled), self._stream()))
+        self._check(self.lib.idm_swiglu(_p(gu), P, n * width, _p(y),
+                                        n, inter, tiled, self._stream()))
         return y
 
     def gemm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -331,15 +366,15 @@ class Kernels:
             raise KernelError(f"gemm: input rows have {Kd} elements, weight rows {K2}")
         if self.dtype == torch.float32:
             out = torch.empty((1, M, N), dtype=torch.float32, device=self.device)
-            self._check(self.lib.idm_gemm_f32(c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(out)), c_int(M),
-                                              c_int(N), c_int(Kd), self._stream()))
+            self._check(self.lib.idm_gemm_f32(_p(x), _p(w), _p(out), M,
+                                              N, Kd, self._stream()))
             return out
         if self.gemm_impl == "library" or Kd % 8 or M == 0:
             return self._gemm_library(x, w)
-        P = self.lib.idm_gemm_bf16_splits(c_int(M), c_int(N), c_int(Kd))
+        P = self.lib.idm_gemm_bf16_splits(M, N, Kd)
         out = torch.empty((P, M, N), dtype=torch.float32, device=self.device)
-        self._check(self.lib.idm_gemm_bf16(c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(out)), c_int(M), c_int(N),
-                                           c_int(Kd), c_int(P), self._stream()))
+        self._check(self.lib.idm_gemm_bf16(_p(x), _p(w), _p(out), M, N,
+                                           Kd, P, self._stream()))
         return out
 
     # ---- fused epilogues (bfloat16 only) ------------------------------------------------------------
@@ -354,8 +389,8 @@ class Kernels:
             raise KernelError(f"gemm: the inner size {Kd} must be a multiple of 8 for the fused kernels")
         plan = self._gemm_plans.get((M, N, Kd))
         if plan is None:
-            P = self.lib.idm_gemm_bf16_splits(c_int(M), c_int(N), c_int(Kd))
-            plan = self._gemm_plans[(M, N, Kd)] = (P, self.lib.idm_gemm_bf16_workspace_floats(c_int(M), c_int(N), c_int(P)))
+            P = self.lib.idm_gemm_bf16_splits(M, N, Kd)
+            plan = self._gemm_plans[(M, N, Kd)] = (P, self.lib.idm_gemm_bf16_workspace_floats(M, N, P))
         return M, N, Kd, plan[0], self.scratch("gemm_ws", plan[1])
 
     def gemm_store(self, x, w) -> torch.Tensor:
@@ -363,8 +398,8 @@ class Kernels:
         M, N, Kd, P, ws = self._gemm_shape(x, w)
         out = torch.empty((M, N), dtype=torch.float32, device=self.device)
         if M:
-            self._check(self.lib.idm_gemm_bf16_store(c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(out)),
-                                                     c_void_p(_p(ws)), c_int(M), c_int(N), c_int(Kd), c_int(P),
+            self._check(self.lib.idm_gemm_bf16_store(_p(x), _p(w), _p(out),
+                                                     _p(ws), M, N, Kd, P,
                                                      self._stream()))
         return out
 
@@ -375,8 +410,8 @@ class Kernels:
         if tuple(h.shape) != (M, N):
             raise KernelError(f"residual stream {tuple(h.shape)} does not match the product {(M, N)}")
         if M:
-            self._check(self.lib.idm_gemm_bf16_residual(c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(h)),
-                                                        c_void_p(_p(ws)), c_int(M), c_int(N), c_int(Kd), c_int(P),
+            self._check(self.lib.idm_gemm_bf16_residual(_p(x), _p(w), _p(h),
+                                                        _p(ws), M, N, Kd, P,
                                                         self._stream()))
 
     def tile_gate_up(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -396,8 +431,8 @@ class Kernels:
             raise KernelError(f"tiled gate/up weight has {N} rows, expected {-(-inter // 64) * 128}")
         y = torch.empty((M, inter), dtype=self.dtype, device=self.device)
         if M:
-            self._check(self.lib.idm_gemm_bf16_swiglu(c_void_p(_p(x)), c_void_p(_p(w_tiled)), c_void_p(_p(y)),
-                                                      c_void_p(_p(ws)), c_int(M), c_int(inter), c_int(Kd), c_int(P),
+            self._check(self.lib.idm_gemm_bf16_swiglu(_p(x), _p(w_tiled), _p(y),
+                                                      _p(ws), M, inter, Kd, P,
                                                       self._stream()))
         return y
 
@@ -417,13 +452,13 @@ class Kernels:
             self._check_kv(kv, n_kv, hd)
         if M:
             self._check(self.lib.idm_gemm_bf16_qkv(
-                c_void_p(_p(x)), c_void_p(_p(w)), c_void_p(_p(ws)), c_int(M), c_int(Kd), c_int(P), c_int(n_q),
-                c_int(n_kv), c_int(hd), c_void_p(_p(q_gamma)), c_void_p(_p(k_gamma)), c_float(eps),
-                c_void_p(_p(cs)), c_void_p(_p(q)), c_void_p(_p(k_new)), c_void_p(_p(v_new)),
-                c_void_p(_p(kv.k) if kv is not None else None), c_void_p(_p(kv.v) if kv is not None else None),
-                c_void_p(_p(kv.table) if kv is not None else None),
-                c_int(kv.table.shape[1] if kv is not None else 0), c_int(kv.ring if kv is not None else 0),
-                c_void_p(_p(ctx.token_seq)), c_void_p(_p(ctx.positions)), c_void_p(_p(ctx.slots)), self._stream()))
+                _p(x), _p(w), _p(ws), M, Kd, P, n_q,
+                n_kv, hd, _p(q_gamma), _p(k_gamma), eps,
+                _p(cs), _p(q), _p(k_new), _p(v_new),
+                (_p(kv.k) if kv is not None else None), (_p(kv.v) if kv is not None else None),
+                (_p(kv.table) if kv is not None else None),
+                (kv.table.shape[1] if kv is not None else 0), (kv.ring if kv is not None else 0),
+                _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots), self._stream()))
         return q, k_new, v_new
 
     def gemm_status(self) -> int:
@@ -447,9 +482,9 @@ class Kernels:
             if keys.numel() != B:
                 raise KernelError("one key per row")
         out = torch.empty((B,), dtype=torch.int32, device=self.device)
-        scratch = self.scratch("sample", self.lib.idm_sample_scratch_floats(c_int(B), c_int(V)))
-        self._check(self.lib.idm_sample(c_void_p(_p(logits)), c_int(B), c_int(V), c_float(temperature),
-                                        c_void_p(_p(keys)), c_void_p(_p(out)), c_void_p(_p(scratch)), self._stream()))
+        scratch = self.scratch("sample", self.lib.idm_sample_scratch_floats(B, V))
+        self._check(self.lib.idm_sample(_p(logits), B, V, temperature,
+                                        _p(keys), _p(out), _p(scratch), self._stream()))
         return out
 
 
@@ -457,9 +492,9 @@ class Kernels:
         """tokens <- sampled; positions, q_start, kv_len += 1; history[step] <- sampled; step += 1."""
         n = tokens.numel()
         self._check(self.lib.idm_decode_advance(
-            c_void_p(_p(tokens)), c_void_p(_p(positions)), c_void_p(_p(q_start)), c_void_p(_p(kv_len)),
-            c_void_p(_p(sampled)), c_void_p(_p(history)), c_void_p(_p(step_counter)), c_int(n),
-            c_int(history.shape[0]), self._stream()))
+            _p(tokens), _p(positions), _p(q_start), _p(kv_len),
+            _p(sampled), _p(history), _p(step_counter), n,
+            history.shape[0], self._stream()))
 
 
 def M_is_zero(x) -> bool:
