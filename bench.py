@@ -131,8 +131,9 @@ def decode_point(lm, batch: int, context: int, steps: int, warmup: int, seed: in
 
 
 def e2e_point(lm, batch: int, context: int, steps: int, warmup: int, seed: int):
-    """The same decode through the public step/sample calls: every step copies its tokens from
-    pinned host memory to the device and reads the chosen tokens back."""
+    """The same decode through the public ``step_sample`` call (what ``generate`` runs per step):
+    every step copies its tokens from pinned host memory to the device and reads the chosen tokens
+    back."""
     import torch
     eng, cfg = lm.engine, lm.config
     V = cfg.vocab_size
@@ -147,7 +148,7 @@ def e2e_point(lm, batch: int, context: int, steps: int, warmup: int, seed: int):
 
     def one(step):
         nonlocal cur
-        cur = eng.sample(eng.step([(s, [t]) for s, t in zip(slots, cur)]), 0.0, 0, reqs, [step] * batch)
+        cur, _ = eng.step_sample([(s, [t]) for s, t in zip(slots, cur)], 0.0, 0, reqs, [step] * batch)
     for i in range(warmup):
         one(i)
     torch.cuda.synchronize()

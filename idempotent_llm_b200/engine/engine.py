@@ -22,22 +22,31 @@ from .batch import StepContext, context_from_packed, pack_step_host
 
 
 class _DecodeGraph:
-    """A captured single-token step for a fixed number of sequences."""
+    """A captured single-token step for a fixed number of sequences; with ``temperature`` given, the
+    pick of one token per row from the logits is part of the graph (``keys``: rows draw with keys of
+    their own, which come with the step's other inputs)."""
 
-    def __init__(self, engine: "Engine", n_seqs: int):
+    def __init__(self, engine: "Engine", n_seqs: int, temperature: Optional[float] = None, keys: bool = False):
         self.n = n_seqs
         dev = engine.device
-        self.size = 7 * n_seqs + 1 + n_seqs
+        self.packed_size = 7 * n_seqs + 1 + n_seqs
+        # the rows' 64-bit keys lie behind the packed step on an 8-byte border
+        self.keys_at = (self.packed_size + 1) // 2 * 2
+        self.size = self.keys_at + (2 * n_seqs if keys else 0)
         self.host = torch.zeros(self.size, dtype=torch.int32, pin_memory=True)
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=dev)
+        self.temperature, self.keys = temperature, keys
         self.graph = None
         self.logits = None
+        self.picked = None              # int32 [n_seqs] on the device, if the pick is part of the graph
         self.uploaded = None            # event: the last host->device copy of `host` is done
 
-    def run(self, engine: "Engine", packed: torch.Tensor, slots, q_lens, starts) -> torch.Tensor:
+    def run(self, engine: "Engine", packed: torch.Tensor, slots, q_lens, starts, keys=None) -> torch.Tensor:
         if self.uploaded is not None:
             self.uploaded.synchronize()
-        self.host.copy_(packed)
+        self.host[:self.packed_size].copy_(packed)
+        if self.keys:
+            self.host[self.keys_at:].view(torch.int64).copy_(keys)
         self.dev.copy_(self.host, non_blocking=True)
         if self.uploaded is None:
             self.uploaded = torch.cuda.Event()
@@ -45,15 +54,21 @@ class _DecodeGraph:
         if self.graph is None:
             ctx = context_from_packed(self.dev, self.n, slots, q_lens, starts,
                                       max_kv_len=engine.cache.max_seq_len)
-            rows = self.dev[7 * self.n + 1:]
-            for _ in range(2):                       # warm-up outside capture (lazy library state)
+            rows = self.dev[7 * self.n + 1:self.packed_size]
+            dev_keys = self.dev[self.keys_at:].view(torch.int64) if self.keys else None
+            K = engine.rt.kernels
+
+            def body():
                 ctx.memo.clear()
-                engine.model.forward(ctx, engine.cache, rows)
+                self.logits = engine.model.forward(ctx, engine.cache, rows)
+                if self.temperature is not None:
+                    self.picked = K.sample(self.logits, self.temperature, dev_keys)
+            for _ in range(2):                       # warm-up outside capture (lazy library state)
+                body()
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            ctx.memo.clear()
             with torch.cuda.graph(g, pool=engine._graph_pool):
-                self.logits = engine.model.forward(ctx, engine.cache, rows)
+                body()
             if engine._graph_pool is None:
                 engine._graph_pool = g.pool()
             self.graph = g
@@ -137,7 +152,7 @@ class Engine:
         self.cache = SequenceCache(cache_needs(model.spec), max_tokens, model.rt.dtype, self.device,
                                    max_seqs=max_seqs, max_seq_len=max_seq_len)
         self.use_graph = use_graph and self.device.type == "cuda"
-        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._graphs: Dict[object, _DecodeGraph] = {}    # by batch size, or (batch size, temperature, keys)
         self._graph_pool = None
         self._pinned: Dict[int, torch.Tensor] = {}
         self.steps_run = 0
@@ -207,6 +222,48 @@ class Engine:
             self.cache.set_length(s, st + len(t))
         self.steps_run += 1
         return logits
+
+    def step_sample(self, entries: Sequence[Tuple[int, Sequence[int]]], temperature: float, seed: int,
+                    request_ids: Sequence[int], steps: Sequence[int]) -> Tuple[List[int], torch.Tensor]:
+        """``sample(step(entries), ...)`` for sequences that bring one token each, as one captured
+        graph (model and pick) where graphs are in use: the same kernels on the same inputs, so the
+        same tokens, without a launch and a copy of the logits in between.  Returns the chosen tokens
+        and the logits ``[n, vocab]``, which stay valid until the engine's next step."""
+        single = all(len(t) == 1 for _, t in entries)
+        if not (single and self.use_graph and getattr(self.model, "graph_safe", True)):
+            logits = self.step(entries)
+            return self.sample(logits, temperature, seed, request_ids, steps), logits
+        from ..sampling.sampler import row_keys
+        if temperature < 0:
+            raise ValueError("temperature must be >= 0")
+        slots = [int(s) for s, _ in entries]
+        toks = [[int(t[0])] for _, t in entries]
+        n = len(slots)
+        if len(set(slots)) != n:
+            raise ValueError("a slot appears twice in one step")
+        if len(request_ids) != n or len(steps) != n:
+            raise ValueError("one request id and one step per row")
+        V = self.spec.vocab_size
+        for s, t in zip(slots, toks):
+            if not 0 <= t[0] < V:
+                raise ValueError(f"token id {t[0]} is outside the vocabulary [0, {V})")
+        starts = [self.cache.length(s) for s in slots]
+        self.cache.reserve([(s, st + 1) for s, st in zip(slots, starts)])
+        full, _, q_lens = pack_step_host(slots, starts, toks, extra=range(n))
+        self.cache.flush()
+        keys = row_keys(seed, request_ids, steps) if temperature > 0 else None
+        key = (n, float(temperature), keys is not None)
+        g = self._graphs.get(key)
+        if g is None:
+            if len(self._graphs) >= 64:                  # (many temperatures: start over rather than grow)
+                self._graphs.clear()
+            g = self._graphs[key] = _DecodeGraph(self, n, float(temperature), keys is not None)
+        g.run(self, full, slots, q_lens, starts, keys)
+        picked = g.picked.tolist()
+        for s, st in zip(slots, starts):
+            self.cache.set_length(s, st + 1)
+        self.steps_run += 1
+        return picked, g.logits
 
     def _upload(self, host: torch.Tensor) -> torch.Tensor:
         if self.device.type != "cuda":

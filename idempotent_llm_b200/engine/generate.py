@@ -84,10 +84,14 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new: int, *, temperat
         try:
             feed = [list(prompts[r]) for r, _ in live]       # this step's tokens per live sequence
             while live:
-                logits = engine.step([(s, t) for (_, s), t in zip(live, feed)],
-                                     [[len(t) - 1] for t in feed])
-                picked = engine.sample(logits, temperature, seed, [r for r, _ in live],
-                                       [len(results[r].tokens) for r, _ in live])
+                entries = [(s, t) for (_, s), t in zip(live, feed)]
+                rows, steps = [r for r, _ in live], [len(results[r].tokens) for r, _ in live]
+                fused = getattr(engine, "step_sample", None)
+                if fused is not None and all(len(t) == 1 for t in feed):
+                    picked, logits = fused(entries, temperature, seed, rows, steps)   # one token each
+                else:
+                    logits = engine.step(entries, [[len(t) - 1] for t in feed])
+                    picked = engine.sample(logits, temperature, seed, rows, steps)
                 if on_step is not None:
                     on_step([r for r, _ in live], picked, logits)
                 nxt_live, nxt_feed = [], []

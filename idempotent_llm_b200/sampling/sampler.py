@@ -40,6 +40,11 @@ def _as_i64(x: int) -> int:
     return x - (1 << 64) if x >= (1 << 63) else x
 
 
+def row_keys(seed: int, request_ids: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
+    """The rows' keys as int64 on the host."""
+    return torch.tensor([_as_i64(row_key(seed, r, s)) for r, s in zip(request_ids, steps)], dtype=torch.int64)
+
+
 def sample_tokens(kernels, logits: torch.Tensor, temperature: float, seed: int,
                   request_ids: Sequence[int], steps: Sequence[int]) -> List[int]:
     """One token per row of ``logits`` ``[B, vocab]`` (float32, on the device)."""
@@ -50,7 +55,6 @@ def sample_tokens(kernels, logits: torch.Tensor, temperature: float, seed: int,
         raise ValueError("one request id and one step per row")
     keys = None
     if temperature > 0:
-        keys = torch.tensor([_as_i64(row_key(seed, r, s)) for r, s in zip(request_ids, steps)],
-                            dtype=torch.int64).to(logits.device)
+        keys = row_keys(seed, request_ids, steps).to(logits.device)
     out = kernels.sample(logits, float(temperature), keys)        # int32 [B] on the device
     return out.tolist()

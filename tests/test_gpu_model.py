@@ -274,3 +274,48 @@ def test_graph_and_eager_decode_give_the_same_bits(loaded):
         assert torch.equal(a, b)
         assert all(torch.equal(x, y) for x, y in zip(la, lb))
         lm.engine.use_graph = True
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("temperature", [0.0, 0.7])
+def test_step_and_pick_in_one_graph_is_step_then_pick(loaded, dtype, temperature):
+    """``step_sample`` (model and pick captured together) against ``step`` followed by ``sample``: the
+    same tokens and the same logits, step after step, also after a sequence has left the batch."""
+    lm, cfg, w = loaded("B", dtype)
+    eng = lm.engine
+    prompts = [helpers.rand_ids(n, cfg["vocab_size"], 300 + n) for n in (9, 2, 70)]
+
+    def run(fused):
+        slots = [eng.open() for _ in prompts]
+        logits = eng.step(list(zip(slots, prompts)))
+        reqs = [0, 1, 2]
+        cur = eng.sample(logits, temperature, 5, reqs, [0] * 3)
+        out = [list(cur)]
+        kept = []
+        for s in range(1, 12):
+            if s == 6:                                   # the middle sequence ends
+                eng.close(slots.pop(1)); reqs.pop(1); cur.pop(1)
+            entries = [(sl, [t]) for sl, t in zip(slots, cur)]
+            if fused:
+                cur, lg = eng.step_sample(entries, temperature, 5, reqs, [s] * len(reqs))
+            else:
+                lg = eng.step(entries)
+                cur = eng.sample(lg, temperature, 5, reqs, [s] * len(reqs))
+            kept.append(lg.clone())
+            out.append(list(cur))
+        for sl in slots:
+            eng.close(sl)
+        return out, kept
+    eng.use_graph = True
+    fused_tokens, fused_logits = run(True)
+    plain_tokens, plain_logits = run(False)
+    assert fused_tokens == plain_tokens
+    assert all(torch.equal(a, b) for a, b in zip(fused_logits, plain_logits))
+    with pytest.raises(ValueError, match="vocabulary"):
+        s = eng.open()
+        try:
+            eng.step(([(s, [1, 2])]))
+            eng.step_sample([(s, [cfg["vocab_size"]])], 0.0, 0, [0], [0])
+        finally:
+            eng.close(s)
+    _check_clean(lm)
