@@ -163,8 +163,10 @@ extern "C" int idm_add_rmsnorm(float* h, const float* delta, int n_partials, lon
 // ---------------------------------------------------------------- rotary table
 // cs[t, j] = (cos, sin)(positions[t] * inv_freq[j]), angle and functions in 64-bit,
 // rounded to 32-bit (src/detllm/ops/rope.py:25-35 builds its table the same way).
+// cs_by_dim, if given, gets the same values as [half, n_tokens]: there the tokens of one dim lie side
+// by side, which is how a kernel with one thread per token wants to read them.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
-                                  float2* __restrict__ cs, int n_tokens, int half) {
+                                  float2* __restrict__ cs, float2* __restrict__ cs_by_dim, int n_tokens, int half) {
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -173,14 +175,16 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const doubl
     double s, c;
     sincos((double)positions[t] * inv_freq[j], &s, &c);
     cs[i] = make_float2((float)c, (float)s);
+    if (cs_by_dim != nullptr) cs_by_dim[(size_t)j * n_tokens + t] = make_float2((float)c, (float)s);
 }
 
-extern "C" int idm_rope_table(const int* positions, const double* inv_freq, float* cs, int n_tokens,
-                              int half, cudaStream_t stream) {
+extern "C" int idm_rope_table(const int* positions, const double* inv_freq, float* cs, float* cs_by_dim,
+                              int n_tokens, int half, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     IDM_REQUIRE(half > 0, "rope_table: bad half=%d", half);
     const int n = n_tokens * half;
-    idm_launch(rope_table_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, positions, inv_freq, (float2*)cs, n_tokens, half);
+    idm_launch(rope_table_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, positions, inv_freq, (float2*)cs,
+               (float2*)cs_by_dim, n_tokens, half);
     IDM_LAUNCH_CHECK("rope_table");
     return 0;
 }
@@ -245,7 +249,7 @@ extern "C" int idm_qkv_finish(const float* qkv, int n_partials, long long partia
     QkvArgs a;
     a.qkv = qkv; a.n_partials = n_partials; a.partial_stride = (size_t)partial_stride;
     a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd;
-    a.gq = gq; a.gk = gk; a.eps = eps; a.inv_hd = 1.0f / (float)hd; a.cs = (const float2*)cs;
+    a.gq = gq; a.gk = gk; a.eps = eps; a.inv_hd = 1.0f / (float)hd; a.cs = (const float2*)cs; a.cs_by_dim = nullptr;
     a.q_out = (T*)q_out; a.k_new = (T*)k_new; a.v_new = (T*)v_new;
     a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
     a.write_cache = k_pool != nullptr;

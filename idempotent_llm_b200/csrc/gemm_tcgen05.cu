@@ -716,14 +716,17 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __gri
 // The same persistent scheme with the operands' roles exchanged: the MMA's M axis carries 128 tokens
 // (rows of x), its N axis 256 features (rows of w: whole heads), so an accumulator lane is a token and
 // a thread reads its token's whole head along the columns.  The per-head norm is then a sum inside the
-// thread, the rotation partner (d, d + head_dim / 2) a register of the same thread: no shuffles and no
-// turn through shared memory.  A head of a tile goes to one warp per 32 tokens; where a tile has fewer
-// heads than there are groups of epilogue warps (2 heads of 128), the dims of a head are shared out among
-// the groups left over: each adds up the head's squares for itself and finishes its part of the dims.
-// The epilogue is memory latency (a thread walks rows of its own: 32 lines per request), so it wants
-// every warp busy and the rotation table asked for before the accumulator is read.
+// thread, the rotation partner (d, d + head_dim / 2) a register of the same thread: no shuffles, no
+// turn through shared memory, no barrier between warps.  A head of a tile goes to one warp per 32
+// tokens.  The epilogue is a chain of latencies (accumulator read ~900 cycles, the rotation table from
+// L2, stores that touch 32 lines each), so it has few warps with many registers: a thread asks for its
+// whole head (up to 128 columns) at once and for the next 16 dims' (cos, sin) while it works on these.
+// With 16 warps of 112 registers, each reading 32 columns at a time and sharing heads through a
+// barrier, a tile's epilogue took 9 us against 5.8 us for its MMAs.
 #define GQ_BN 256
 #define GQ_STAGES 4
+#define GQ_EPI_WARPS 8
+#define GQ_THREADS (32 * (GQ_EPI_WARPS + 2))
 struct QkvTokensSmem {
     static constexpr int A_BYTES = GT_BM * GT_BK * 2;              // 128 tokens
     static constexpr int B_BYTES = GQ_BN * GT_BK * 2;              // 256 features
@@ -732,7 +735,88 @@ struct QkvTokensSmem {
     static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-__global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __grid_constant__ CUtensorMap map_w,
+// One head of one token: norm, rotation, stores.  col0: the head's first accumulator column (with the
+// warp's lanes); cs_row: the token's row of the rotation table; cs_dim: the same table by dim (the
+// tokens of a dim side by side: two lines per request instead of 32), or null.
+template <int HD>
+__device__ __forceinline__ void qkv_tokens_head(const QkvArgs& a, uint32_t col0, const float* gamma, bool rotate,
+                                                const float2* cs_row, const float2* cs_dim, int n_tokens,
+                                                T* dst_a, T* dst_b) {
+    constexpr int HALF = HD / 2;
+    float cs4[4][8];                                               // (cos, sin) of 16 dims
+    auto ask_cs = [&](int c) {
+        if (!rotate) return;
+        if (cs_dim != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float2 v = __ldg(cs_dim + (size_t)(c + i) * n_tokens);
+                cs4[i / 4][2 * (i % 4)] = v.x; cs4[i / 4][2 * (i % 4) + 1] = v.y;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                load8_readonly(reinterpret_cast<const float*>(cs_row + c + 4 * i), cs4[i]);
+        }
+    };
+    uint32_t cur[32];                                              // 16 dims of each half: this step's, then the next's
+    float inv = 1.f;
+    {
+        // the head's sum of squares (four chains), one half of the head at a time in registers (the whole
+        // head at once leaves no room); the first step's columns of each half are kept
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t raw[HALF];
+#pragma unroll
+            for (int c = 0; c < HALF; c += 16) tc_ld16_issue(col0 + (uint32_t)(h * HALF + c), raw + c);
+            if (h == 0) ask_cs(0);
+            tc_ld_wait();
+            if (gamma != nullptr) {
+#pragma unroll
+                for (int i = 0; i < HALF; ++i)
+                    s4[i & 3] = __fmaf_rn(__uint_as_float(raw[i]), __uint_as_float(raw[i]), s4[i & 3]);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) cur[16 * h + i] = raw[i];
+        }
+        if (gamma != nullptr) inv = head_inv_rms(a, (s4[0] + s4[1]) + (s4[2] + s4[3]));
+    }
+    // dims d and d + HALF together, 16 of each per step; the next step's columns are asked for before
+    // this step's arithmetic (the loop stays a loop: unrolled, the compiler moves all steps' loads of the
+    // norm weight to the front and runs out of registers)
+#pragma unroll 1
+    for (int c = 0; c < HALF; c += 16) {
+        float lo[16], hi[16];
+        if (c > 0) tc_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { lo[i] = __uint_as_float(cur[i]); hi[i] = __uint_as_float(cur[16 + i]); }
+        if (c + 16 < HALF) {
+            tc_ld16_issue(col0 + (uint32_t)(c + 16), cur);
+            tc_ld16_issue(col0 + (uint32_t)(HALF + c + 16), cur + 16);
+        }
+        if (gamma != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                lo[i] = __fmul_rn(__fmul_rn(lo[i], inv), __ldg(gamma + c + i));
+                hi[i] = __fmul_rn(__fmul_rn(hi[i], inv), __ldg(gamma + HALF + c + i));
+            }
+        }
+        if (rotate) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float u = lo[i], w = hi[i];
+                const float co = cs4[i / 4][2 * (i % 4)], si = cs4[i / 4][2 * (i % 4) + 1];
+                lo[i] = __fmaf_rn(u, co, -__fmul_rn(w, si));
+                hi[i] = __fmaf_rn(w, co, __fmul_rn(u, si));
+            }
+        }
+        if (c + 16 < HALF) ask_cs(c + 16);                         // before this step's stores queue up
+        if (dst_a) { store16(dst_a + c, lo); store16(dst_a + HALF + c, hi); }
+        if (dst_b) { store16(dst_b + c, lo); store16(dst_b + HALF + c, hi); }
+    }
+}
+
+__global__ void __launch_bounds__(GQ_THREADS) gemm_qkv_tokens_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                      const __grid_constant__ CUtensorMap map_x,
                                                                      const GemmEpi e, int n_tokens, int n_features,
                                                                      int kb_total, int tiles_x, int n_tiles) {
@@ -754,18 +838,18 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __gri
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), GP_EPI_WARPS); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), GQ_EPI_WARPS); }
         *abort_flag = 0;
         mbar_init_fence();
     }
-    if (warp == GP_EPI_WARPS + 1) tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+    if (warp == GQ_EPI_WARPS + 1) tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     pdl_wait();
 
-    if (warp == GP_EPI_WARPS) {
+    if (warp == GQ_EPI_WARPS) {
         if (lane == 0) {
             uint32_t cnt = 0;
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
@@ -783,7 +867,7 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __gri
                 if (!ok) break;
             }
         }
-    } else if (warp == GP_EPI_WARPS + 1) {
+    } else if (warp == GQ_EPI_WARPS + 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(GT_BM, BN);
             uint32_t cnt = 0, it = 0;
@@ -811,13 +895,13 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __gri
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const QkvArgs& a = e.q;
-        const int quarter = warp & 3, grp = warp >> 2;             // accumulator lanes 32 quarter ..; heads grp, grp + 4, ...
+        const int quarter = warp & 3, grp = warp >> 2;             // accumulator lanes 32 quarter ..; heads grp, grp + 2, ...
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const int hd = a.hd, half = hd >> 1, heads = a.n_q + 2 * a.n_kv, hpt = BN / hd;
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-            const int f0 = (tile % tiles_x) * BN, t0 = (tile / tiles_x) * GT_BM;
+            const int tx = tile % tiles_x, f0 = tx * BN, t0 = (tile / tiles_x) * GT_BM;
             const uint32_t acc = it & 1;
             const int t = t0 + quarter * 32 + lane;                // this thread's token
             const bool live = t < n_tokens;
@@ -829,15 +913,13 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __gri
                 const int page = a.cache.table[(size_t)a.slots[a.token_seq[t]] * a.cache.table_stride + r / IDM_PAGE];
                 place = (size_t)page * a.n_kv * IDM_PAGE + r % IDM_PAGE;       // row of kv-head 0; kv-head g: + g * IDM_PAGE
             }
+            const float2* cs_row = a.cs + (size_t)(live ? t : 0) * half;
+            const float2* cs_dim = a.cs_by_dim ? a.cs_by_dim + (live ? t : 0) : nullptr;
             ok = mbar_wait(tfull_bar(acc), (it >> 1) & 1, abort_flag, &g_gemm_error);
             if (!ok) break;
             tc_fence_after();
-            // groups beyond the tile's heads share a head's dims: part `part` of `n_parts`
-            const int n_parts = (hpt < GP_GROUPS && (half / (GP_GROUPS / hpt)) % 16 == 0) ? GP_GROUPS / hpt : 1;
-            const int part = n_parts > 1 ? grp / hpt : 0;
-            const int c_first = part * (half / n_parts), c_end = c_first + half / n_parts;
-            for (int hh = n_parts > 1 ? grp % hpt : grp; hh < hpt; hh += GP_GROUPS) {
-                const int head = f0 / hd + hh;
+            for (int hh = grp; hh < hpt; hh += GQ_EPI_WARPS / 4) {
+                const int head = tx * hpt + hh;
                 if (head >= heads) break;                          // the last tile may reach past the last head
                 const uint32_t col0 = tmem + acc * BN + lane_base + (uint32_t)(hh * hd);
                 const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
@@ -853,52 +935,10 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __gri
                         if (packed) dst_b = packed + ((size_t)t * a.n_kv + g) * hd;
                     }
                 }
-                float inv = 1.f;
-                if (gamma != nullptr) {                            // the head's sum of squares: a first pass over its columns
-                    float ss = 0.f;
-#pragma unroll 1
-                    for (int c = 0; c < hd; c += 16) {
-                        float v[16];
-                        tc_ld16(col0 + (uint32_t)c, v);
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) ss = __fmaf_rn(v[i], v[i], ss);
-                    }
-                    inv = head_inv_rms(a, ss);
-                }
                 const bool rotate = (is_q || is_k) && a.cs != nullptr;
-                const float2* cs = a.cs + (size_t)(live ? t : 0) * half;
-                // dims d and d + half together: norm, rotation, 16 dims of each half per step
-#pragma unroll 1
-                for (int c = c_first; c < c_end; c += 16) {
-                    float cs4[4][8];                               // (cos, sin) of the 16 dims, 32 bytes a piece
-                    if (rotate) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) load8_readonly(reinterpret_cast<const float*>(cs + c + 4 * i), cs4[i]);
-                    }
-                    float lo[16], hi[16];
-                    tc_ld16(col0 + (uint32_t)c, lo);
-                    tc_ld16(col0 + (uint32_t)(half + c), hi);
-                    if (gamma != nullptr) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            lo[i] = __fmul_rn(__fmul_rn(lo[i], inv), __ldg(gamma + c + i));
-                            hi[i] = __fmul_rn(__fmul_rn(hi[i], inv), __ldg(gamma + half + c + i));
-                        }
-                    }
-                    if (rotate) {
-#pragma unroll
-                        for (int i = 0; i < 16; i += 4) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const float u = lo[i + j], w = hi[i + j];
-                                lo[i + j] = __fmaf_rn(u, cs4[i / 4][2 * j], -__fmul_rn(w, cs4[i / 4][2 * j + 1]));
-                                hi[i + j] = __fmaf_rn(w, cs4[i / 4][2 * j], __fmul_rn(u, cs4[i / 4][2 * j + 1]));
-                            }
-                        }
-                    }
-                    if (dst_a) { store16(dst_a + c, lo); store16(dst_a + half + c, hi); }
-                    if (dst_b) { store16(dst_b + c, lo); store16(dst_b + half + c, hi); }
-                }
+                if (hd == 128) qkv_tokens_head<128>(a, col0, gamma, rotate, cs_row, cs_dim, n_tokens, dst_a, dst_b);
+                else if (hd == 64) qkv_tokens_head<64>(a, col0, gamma, rotate, cs_row, cs_dim, n_tokens, dst_a, dst_b);
+                else qkv_tokens_head<32>(a, col0, gamma, rotate, cs_row, cs_dim, n_tokens, dst_a, dst_b);
             }
             tc_fence_before();
             __syncwarp();
@@ -907,7 +947,7 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_qkv_tokens_kernel(const __gri
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == GP_EPI_WARPS + 1) tmem_dealloc(tmem, TMEM_COLS);
+    if (warp == GQ_EPI_WARPS + 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 static int launch_qkv_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
@@ -926,7 +966,7 @@ static int launch_qkv_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const
     const int tiles_x = (N + GQ_BN - 1) / GQ_BN, tiles_y = (M + GT_BM - 1) / GT_BM;
     const int n_tiles = tiles_x * tiles_y;
     const int grid = n_tiles < n_sm ? n_tiles : n_sm;
-    idm_launch(gemm_qkv_tokens_kernel, dim3(grid), dim3(GP_THREADS), S::TOTAL, stream, mw, mx, e, M, N, kb_total, tiles_x,
+    idm_launch(gemm_qkv_tokens_kernel, dim3(grid), dim3(GQ_THREADS), S::TOTAL, stream, mw, mx, e, M, N, kb_total, tiles_x,
                n_tiles);
     IDM_LAUNCH_CHECK("gemm_qkv_tokens");
     return 0;
@@ -1056,7 +1096,7 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, i
     }
     CUtensorMap mw, mx;
     auto on32 = [](const void* p) { return ((uintptr_t)p & 31) == 0; };   // (null counts: that output is not written)
-    if (EPI == EPI_QKV && splits == 1 && M > 256 && g_gemm_persistent && GQ_BN % e.q.hd == 0 && e.q.hd % 32 == 0 &&
+    if (EPI == EPI_QKV && splits == 1 && M > 256 && g_gemm_persistent && (e.q.hd == 32 || e.q.hd == 64 || e.q.hd == 128) &&
         on32(e.q.q_out) && on32(e.q.k_new) && on32(e.q.v_new) && on32(e.q.cache.k) && on32(e.q.cache.v) && on32(e.q.cs)) {
         // many tokens: tokens on the accumulator's lanes, 256 features (whole heads) per tile
         if (make_map(&mw, w, N, K, GQ_BN)) return 1;
@@ -1128,6 +1168,7 @@ extern "C" int idm_gemm_bf16_swiglu(const void* x, const void* w_tiled, void* y,
 // The fused q/k/v projection with the per-head finish (see qkv_finish.cuh); 128 % head_dim must be 0
 extern "C" int idm_gemm_bf16_qkv(const void* x, const void* w, float* workspace, int M, int K, int splits, int n_q,
                                  int n_kv, int hd, const float* gq, const float* gk, float eps, const float* cs,
+                                 const float* cs_by_dim,
                                  void* q_out, void* k_new, void* v_new, void* k_pool, void* v_pool, const int* table,
                                  int table_stride, int ring, const int* token_seq, const int* positions,
                                  const int* slots, cudaStream_t stream) {
@@ -1137,6 +1178,7 @@ extern "C" int idm_gemm_bf16_qkv(const void* x, const void* w, float* workspace,
     a.qkv = nullptr; a.n_partials = 0; a.partial_stride = 0;
     a.n_tokens = M; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd;
     a.gq = gq; a.gk = gk; a.eps = eps; a.inv_hd = 1.0f / (float)hd; a.cs = (const float2*)cs;
+    a.cs_by_dim = (const float2*)cs_by_dim;
     a.q_out = (T*)q_out; a.k_new = (T*)k_new; a.v_new = (T*)v_new;
     a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
     a.write_cache = k_pool != nullptr;

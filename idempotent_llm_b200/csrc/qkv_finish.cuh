@@ -55,6 +55,7 @@ struct QkvArgs {
     int n_tokens, n_q, n_kv, hd;
     const float* gq; const float* gk; float eps; float inv_hd;   // inv_hd = 1 / hd
     const float2* cs;
+    const float2* cs_by_dim;                                     // the same table as [hd / 2, n_tokens], or null
     T* q_out; T* k_new; T* v_new;
     KVAddr cache; int write_cache;
     const int* token_seq; const int* positions; const int* slots;

@@ -54,7 +54,7 @@ SIGNATURES = {
     "idm_set_pdl": (None, "i"),
     "idm_embed": (c_int, "pppiip"),
     "idm_add_rmsnorm": (c_int, "ppiqpfppiip"),
-    "idm_rope_table": (c_int, "pppiip"),
+    "idm_rope_table": (c_int, "ppppiip"),
     "idm_qkv_finish": (c_int, "piqiiiippfpppppppiipppp"),
     "idm_kv_write_ring": (c_int, "pppppiippppiiip"),
     "idm_swiglu": (c_int, "piqpiiip"),
@@ -81,7 +81,7 @@ SIGNATURES = {
     "idm_gemm_bf16_store": (c_int, "ppppiiiip"),
     "idm_gemm_bf16_residual": (c_int, "ppppiiiip"),
     "idm_gemm_bf16_swiglu": (c_int, "ppppiiiip"),
-    "idm_gemm_bf16_qkv": (c_int, "pppiiiiiippfpppppppiipppp"),
+    "idm_gemm_bf16_qkv": (c_int, "pppiiiiiippfppppppppiipppp"),
     "idm_gemm_status": (c_int, ""),
 }
 
@@ -200,8 +200,12 @@ class Kernels:
         self._need(inv_freq, torch.float64, "inv_freq")
         n, half = positions.numel(), inv_freq.numel()
         cs = torch.empty((n, half, 2), dtype=torch.float32, device=self.device)
-        self._check(self.lib.idm_rope_table(_p(positions), _p(inv_freq), _p(cs),
+        # for steps of many tokens also as [half, n, 2]: the q/k/v product's epilogue of such steps has
+        # a thread per token and reads the tokens of one dim side by side
+        by_dim = torch.empty((half, n, 2), dtype=torch.float32, device=self.device) if n > 256 else None
+        self._check(self.lib.idm_rope_table(_p(positions), _p(inv_freq), _p(cs), _p(by_dim),
                                             n, half, self._stream()))
+        cs.by_dim = by_dim
         return cs
 
     def qkv_finish(self, qkv, n_q, n_kv, hd, q_gamma, k_gamma, eps, cs, ctx, kv, keep_new: bool):
@@ -454,7 +458,7 @@ class Kernels:
             self._check(self.lib.idm_gemm_bf16_qkv(
                 _p(x), _p(w), _p(ws), M, Kd, P, n_q,
                 n_kv, hd, _p(q_gamma), _p(k_gamma), eps,
-                _p(cs), _p(q), _p(k_new), _p(v_new),
+                _p(cs), _p(getattr(cs, "by_dim", None)), _p(q), _p(k_new), _p(v_new),
                 (_p(kv.k) if kv is not None else None), (_p(kv.v) if kv is not None else None),
                 (_p(kv.table) if kv is not None else None),
                 (kv.table.shape[1] if kv is not None else 0), (kv.ring if kv is not None else 0),
