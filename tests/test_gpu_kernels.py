@@ -94,6 +94,11 @@ def test_rope_table(kernels):
     ang = pos.double()[:, None] * inv[None, :]
     assert (cs[..., 0].double() - torch.cos(ang)).abs().max() < 1e-7       # 32-bit rounding of an exact value
     assert (cs[..., 1].double() - torch.sin(ang)).abs().max() < 1e-7
+    # from 257 positions on the table also comes by dim, the same values
+    many = torch.arange(1000, 1300, dtype=torch.int32).cuda()
+    cs = K.rope_table(many, inv.cuda())
+    assert cs.by_dim is not None and tuple(cs.by_dim.shape) == (64, 300, 2)
+    assert torch.equal(cs.by_dim.permute(1, 0, 2), cs)
 
 
 def _cache_with(K, dtype, n_kv, hd, window, lens, seed, max_tokens=64 * 64):
@@ -443,7 +448,7 @@ def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, 
     if lens[0] == 0:
         starts, lens = [5], [M]
 
-    def run(fused):
+    def run(fused, by_dim=True):
         cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, 64 * 32, torch.bfloat16, "cuda:0", max_seqs=4)
         slots = [cache.alloc_slot() for _ in lens]
         cache.reserve([(s_, st + L) for s_, st, L in zip(slots, starts, lens)]); cache.flush()
@@ -454,6 +459,8 @@ def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, 
         gq, gk = (1 + _randn(hd, seed=82, scale=0.3)).float().cuda(), (1 + _randn(hd, seed=83, scale=0.3)).float().cuda()
         inv = 3e4 ** (-2.0 * torch.arange(0, hd // 2, dtype=torch.float64) / hd)
         cs = K.rope_table(ctx.positions, inv.cuda())
+        if not by_dim:
+            cs.by_dim = None                               # the table by token only, as another position encoding gives it
         kv = cache.view(0)
         if fused:
             q, kn, vn = K.gemm_qkv(x, w, n_q, n_kv, hd, gq, gk, 1e-5, cs, ctx, kv, keep_new=True)
@@ -468,6 +475,9 @@ def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, 
         assert helpers.rel_err(t_a, t_b) < KTOL["bfloat16"], name
         if M <= 64 and 128 % hd == 0:
             assert torch.equal(t_a, t_b), name + ": up to 64 tokens both paths finish rows the same way"
+    if M > 256:
+        for t_a, t_c, name in zip(a, run(True, by_dim=False), ("q", "k_new", "v_new", "cache k", "cache v")):
+            assert torch.equal(t_a, t_c), name + ": the table read by dim or by token gives other bits"
     assert K.gemm_status() == 0
 
 
