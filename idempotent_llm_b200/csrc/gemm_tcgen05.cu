@@ -1054,11 +1054,24 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmE
     return 0;
 }
 
-// How many partial sums a product of this shape is split into.  Up to 256 tokens the split depends
-// on the layer (N, K) only, so a token's result is the same in any batch; beyond that K is not split.
+// From how many tokens on a product runs unsplit in the persistent kernels.
+static int g_gemm_many_from = 257;
+extern "C" void idm_gemm_set_many_from(int tokens) { g_gemm_many_from = tokens < 65 ? 65 : tokens; }
+
+// How many partial sums a product of this shape is split into.  Below that border the split depends
+// on the layer (N, K) only, so a token's result is the same in any batch; from it on K is not split.
+// Between 65 tokens and the border a layer whose unsplit product is short anyway (its tiles of 128
+// tokens, counted for 256 tokens, times its k-blocks at 0.3 us: at most 16 us, about what the host
+// needs to launch one more kernel) is not split either: it then runs with its epilogue fused, and a
+// step of that size is bound by its launches, not by its kernels.
 extern "C" int idm_gemm_bf16_splits(int M, int N, int K) {
     const int kb_total = (K + GT_BK - 1) / GT_BK;
-    if (M > 256) return 1;
+    if (M >= g_gemm_many_from) return 1;
+    if (M > 64) {
+        const long long tiles256 = 2LL * ((N + GT_BM - 1) / GT_BM);
+        const long long rounds = (tiles256 + 147) / 148;
+        if (rounds * kb_total * 3 <= 160) return 1;
+    }
     const int tiles = (N + GT_BM - 1) / GT_BM;
     int want = 296 / tiles;                       // about two blocks per SM
     if (want < 1) want = 1;
@@ -1096,14 +1109,14 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, i
     }
     CUtensorMap mw, mx;
     auto on32 = [](const void* p) { return ((uintptr_t)p & 31) == 0; };   // (null counts: that output is not written)
-    if (EPI == EPI_QKV && splits == 1 && M > 256 && g_gemm_persistent && (e.q.hd == 32 || e.q.hd == 64 || e.q.hd == 128) &&
+    if (EPI == EPI_QKV && splits == 1 && M > 64 && g_gemm_persistent && (e.q.hd == 32 || e.q.hd == 64 || e.q.hd == 128) &&
         on32(e.q.q_out) && on32(e.q.k_new) && on32(e.q.v_new) && on32(e.q.cache.k) && on32(e.q.cache.v) && on32(e.q.cs)) {
         // many tokens: tokens on the accumulator's lanes, 256 features (whole heads) per tile
         if (make_map(&mw, w, N, K, GQ_BN)) return 1;
         if (make_map(&mx, x, M, K, GT_BM)) return 1;
         return launch_qkv_tokens(mw, mx, e, M, N, kb_total, stream);
     }
-    if (splits == 1 && M > 256 && g_gemm_persistent) {
+    if (splits == 1 && M > 64 && g_gemm_persistent) {
         // many tokens: the persistent kernel; 256-token tiles unless 128 fill more of the SMs
         const int tiles_x = (N + GT_BM - 1) / GT_BM;
         const bool wide = (long long)tiles_x * ((M + 255) / 256) >= 120;

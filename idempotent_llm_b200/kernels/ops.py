@@ -77,6 +77,7 @@ SIGNATURES = {
     "idm_gemm_bf16_workspace_floats": (c_longlong, "iii"),
     "idm_gemm_set_cluster": (None, "i"),
     "idm_gemm_set_persistent": (None, "i"),
+    "idm_gemm_set_many_from": (None, "i"),
     "idm_gemm_bf16": (c_int, "pppiiiip"),
     "idm_gemm_bf16_store": (c_int, "ppppiiiip"),
     "idm_gemm_bf16_residual": (c_int, "ppppiiiip"),
@@ -123,8 +124,11 @@ class Kernels:
         # Up to 64 tokens the slices of a split inner axis are added inside a thread-block cluster and
         # the epilogue is fused; above 256 tokens nothing is split and the epilogue is fused; between
         # the two the separate kernels, which add the slices with the whole GPU, are quicker than one
-        # block per tile doing it.  IDM_FUSED_MIN_TOKENS / IDM_FUSED_MAX_SMALL move the borders.
+        # block per tile doing it -- unless the layer's products are so short that the library does not
+        # split them at all (see use_fused).  IDM_FUSED_MIN_TOKENS / IDM_FUSED_MAX_SMALL move the borders.
         self.fused_min_tokens = int(os.environ.get("IDM_FUSED_MIN_TOKENS", "257"))
+        if dtype == torch.bfloat16:
+            L.idm_gemm_set_many_from(self.fused_min_tokens)
         self.fused_max_small = int(os.environ.get("IDM_FUSED_MAX_SMALL", "64"))
         # "tcgen05": prompts' attention on the tensor cores; "general": the one-warp-per-query kernel
         self.prefill_impl = os.environ.get("IDM_PREFILL", "tcgen05")
@@ -134,8 +138,22 @@ class Kernels:
         self.page = L.idm_page_tokens()
         self._gemm_plans = {}          # (M, N, K) -> (splits of the inner axis, workspace floats)
 
-    def use_fused(self, n_tokens: int) -> bool:
-        return self.fused and (n_tokens >= self.fused_min_tokens or n_tokens <= self.fused_max_small)
+    def use_fused(self, n_tokens: int, *weights) -> bool:
+        """Whether a part runs its products with fused epilogues at this many tokens: always up to
+        ``fused_max_small`` and from ``fused_min_tokens`` on; in between only if none of the part's
+        products (``weights``: their ``[N, K]`` matrices) is split over its inner axis."""
+        if not self.fused:
+            return False
+        if n_tokens >= self.fused_min_tokens or n_tokens <= self.fused_max_small:
+            return True
+        return bool(weights) and all(self._splits(n_tokens, w.shape[0], w.shape[1]) == 1 for w in weights)
+
+    def _splits(self, M: int, N: int, Kd: int) -> int:
+        plan = self._gemm_plans.get((M, N, Kd))
+        if plan is None:
+            P = self.lib.idm_gemm_bf16_splits(M, N, Kd)
+            plan = self._gemm_plans[(M, N, Kd)] = (P, self.lib.idm_gemm_bf16_workspace_floats(M, N, P))
+        return plan[0]
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -202,7 +220,7 @@ class Kernels:
         cs = torch.empty((n, half, 2), dtype=torch.float32, device=self.device)
         # for steps of many tokens also as [half, n, 2]: the q/k/v product's epilogue of such steps has
         # a thread per token and reads the tokens of one dim side by side
-        by_dim = torch.empty((half, n, 2), dtype=torch.float32, device=self.device) if n > 256 else None
+        by_dim = torch.empty((half, n, 2), dtype=torch.float32, device=self.device) if n > 64 else None
         self._check(self.lib.idm_rope_table(_p(positions), _p(inv_freq), _p(cs), _p(by_dim),
                                             n, half, self._stream()))
         cs.by_dim = by_dim
@@ -391,11 +409,8 @@ class Kernels:
             raise KernelError(f"gemm: input rows have {Kd} elements, weight rows {K2}")
         if Kd % 8:
             raise KernelError(f"gemm: the inner size {Kd} must be a multiple of 8 for the fused kernels")
-        plan = self._gemm_plans.get((M, N, Kd))
-        if plan is None:
-            P = self.lib.idm_gemm_bf16_splits(M, N, Kd)
-            plan = self._gemm_plans[(M, N, Kd)] = (P, self.lib.idm_gemm_bf16_workspace_floats(M, N, P))
-        return M, N, Kd, plan[0], self.scratch("gemm_ws", plan[1])
+        P = self._splits(M, N, Kd)
+        return M, N, Kd, P, self.scratch("gemm_ws", self._gemm_plans[(M, N, Kd)][1])
 
     def gemm_store(self, x, w) -> torch.Tensor:
         """``x . w^T`` finished in 32-bit ``[M, N]``."""

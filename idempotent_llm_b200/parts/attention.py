@@ -74,7 +74,7 @@ class GQAAttention(Mixer):
         if writes_cache == s.kv_from_other:
             raise ValueError("a mixer with its own k/v must write its cache entry; one without must not")
         cs = self.position.tables(ctx) if self.position is not None else None
-        fused = (bool(getattr(K, "fused", False)) and K.use_fused(x.shape[0]) and s.hidden % 8 == 0
+        fused = (bool(getattr(K, "fused", False)) and K.use_fused(x.shape[0], self.w_qkv, self.w_o) and s.hidden % 8 == 0
                  and (s.n_heads * s.head_dim) % 8 == 0)
         # A windowed layer's ring cannot hold a whole prompt, so a step of several tokens reads its
         # own keys from packed buffers and writes the ring afterwards.  A single token overwrites

@@ -41,7 +41,7 @@ class GatedMLP(FeedForward):
     def forward(self, x, ctx, residual=None):
         """Returns the delta ``[P, N, hidden]``, or None after adding it into ``residual`` in place."""
         K = self.rt.kernels
-        if self.fused and K.use_fused(x.shape[0]):
+        if self.fused and K.use_fused(x.shape[0], self.w_gate_up, self.w_down):
             y = K.gemm_swiglu(x, self.w_gate_up, self.spec.intermediate)
             if residual is not None:
                 K.gemm_residual(y, self.w_down, residual)
