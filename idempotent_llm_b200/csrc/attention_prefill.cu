@@ -226,11 +226,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     if (key0 + j > p_r) sr[j] = 0xff800000u;      // -inf: p becomes 0 exactly
             }
             // the maximum of the raw scores (the scale is positive), four chains side by side
+            // (the three-input maximum of sm_100: two scores per instruction)
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < AP_BN; j += 4) {
+            for (int j = 0; j < AP_BN; j += 8) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], __uint_as_float(sr[j + u]));
+                for (int u = 0; u < 4; ++u)
+                    mx[u] = max3(mx[u], __uint_as_float(sr[j + 2 * u]), __uint_as_float(sr[j + 2 * u + 1]));
             }
             const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;
             float alpha = 1.f;

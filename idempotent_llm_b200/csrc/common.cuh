@@ -114,6 +114,13 @@ __device__ __forceinline__ float ex2_hw(float x) {
     return y;
 }
 
+// max(a, b, c) in one instruction (sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // g * sigmoid(g) * u with the hardware exponential and division (relative error ~1e-6, far below the
 // bfloat16 rounding of the result).  Every kernel that applies the activation uses this one formula,
 // so fused and separate paths give the same bits.  (src/detllm/ops/di_swiglu.py:43-45)
