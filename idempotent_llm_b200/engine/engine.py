@@ -40,11 +40,23 @@ class _DecodeGraph:
         self.logits = None
         self.picked = None              # int32 [n_seqs] on the device, if the pick is part of the graph
         self.uploaded = None            # event: the last host->device copy of `host` is done
+        self.host_np = self.host.numpy()                 # the same pinned memory
+        self.last_slots, self.next_starts = None, None   # the batch of the last run and where it goes on
 
-    def run(self, engine: "Engine", packed: torch.Tensor, slots, q_lens, starts, keys=None) -> torch.Tensor:
+    def run(self, engine: "Engine", packed: Optional[torch.Tensor], slots, q_lens, starts, keys=None,
+            tokens=None) -> torch.Tensor:
+        """``packed``: the whole packed step, or None when the step is the last run's batch one token
+        further: then only ``tokens`` are new and positions and lengths move on by one in place."""
         if self.uploaded is not None:
             self.uploaded.synchronize()
-        self.host[:self.packed_size].copy_(packed)
+        if packed is not None:
+            self.host[:self.packed_size].copy_(packed)
+        else:
+            n, h = self.n, self.host_np
+            h[0:n] = tokens
+            h[2 * n:3 * n] += 1                          # positions
+            h[5 * n + 1:7 * n + 1] += 1                  # first new position and length after the step
+        self.last_slots, self.next_starts = slots, [st + 1 for st in starts]
         if self.keys:
             self.host[self.keys_at:].view(torch.int64).copy_(keys)
         self.dev.copy_(self.host, non_blocking=True)
@@ -249,7 +261,6 @@ class Engine:
                 raise ValueError(f"token id {t[0]} is outside the vocabulary [0, {V})")
         starts = [self.cache.length(s) for s in slots]
         self.cache.reserve([(s, st + 1) for s, st in zip(slots, starts)])
-        full, _, q_lens = pack_step_host(slots, starts, toks, extra=range(n))
         self.cache.flush()
         keys = row_keys(seed, request_ids, steps) if temperature > 0 else None
         key = (n, float(temperature), keys is not None)
@@ -258,7 +269,11 @@ class Engine:
             if len(self._graphs) >= 64:                  # (many temperatures: start over rather than grow)
                 self._graphs.clear()
             g = self._graphs[key] = _DecodeGraph(self, n, float(temperature), keys is not None)
-        g.run(self, full, slots, q_lens, starts, keys)
+        if g.graph is not None and g.last_slots == slots and g.next_starts == starts:
+            g.run(self, None, slots, None, starts, keys, tokens=[t[0] for t in toks])   # the same batch, one token on
+        else:
+            full, _, q_lens = pack_step_host(slots, starts, toks, extra=range(n))
+            g.run(self, full, slots, q_lens, starts, keys)
         picked = g.picked.tolist()
         for s, st in zip(slots, starts):
             self.cache.set_length(s, st + 1)
