@@ -159,7 +159,9 @@ def e2e_point(lm, batch: int, context: int, steps: int, warmup: int, seed: int):
     dt = time.perf_counter() - t0
     for s in slots:
         eng.close(s)
-    return batch * steps / dt, (8 * batch + 1) * 4, batch * 4
+    # per step: the packed step (7 ints per sequence, one more, the wanted rows; an even count) goes up,
+    # one chosen token per sequence comes back
+    return batch * steps / dt, (8 * batch + 1 + 1) // 2 * 2 * 4, batch * 4
 
 
 def prefill_point(lm, tokens: int, warmup: int, iters: int, seed: int):
