@@ -795,10 +795,15 @@ __device__ __forceinline__ void qkv_tokens_head(const QkvArgs& a, uint32_t col0,
             tc_ld16_issue(col0 + (uint32_t)(HALF + c + 16), cur + 16);
         }
         if (gamma != nullptr) {
+            // the norm weight four values a request (every lane asks for the same address)
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                lo[i] = __fmul_rn(__fmul_rn(lo[i], inv), __ldg(gamma + c + i));
-                hi[i] = __fmul_rn(__fmul_rn(hi[i], inv), __ldg(gamma + HALF + c + i));
+            for (int i = 0; i < 16; i += 4) {
+                const float4 gl = __ldg(reinterpret_cast<const float4*>(gamma + c + i));
+                const float4 gh = __ldg(reinterpret_cast<const float4*>(gamma + HALF + c + i));
+                lo[i] = __fmul_rn(__fmul_rn(lo[i], inv), gl.x); lo[i + 1] = __fmul_rn(__fmul_rn(lo[i + 1], inv), gl.y);
+                lo[i + 2] = __fmul_rn(__fmul_rn(lo[i + 2], inv), gl.z); lo[i + 3] = __fmul_rn(__fmul_rn(lo[i + 3], inv), gl.w);
+                hi[i] = __fmul_rn(__fmul_rn(hi[i], inv), gh.x); hi[i + 1] = __fmul_rn(__fmul_rn(hi[i + 1], inv), gh.y);
+                hi[i + 2] = __fmul_rn(__fmul_rn(hi[i + 2], inv), gh.z); hi[i + 3] = __fmul_rn(__fmul_rn(hi[i + 3], inv), gh.w);
             }
         }
         if (rotate) {
@@ -1110,7 +1115,8 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, float* workspace, i
     CUtensorMap mw, mx;
     auto on32 = [](const void* p) { return ((uintptr_t)p & 31) == 0; };   // (null counts: that output is not written)
     if (EPI == EPI_QKV && splits == 1 && M > 64 && g_gemm_persistent && (e.q.hd == 32 || e.q.hd == 64 || e.q.hd == 128) &&
-        on32(e.q.q_out) && on32(e.q.k_new) && on32(e.q.v_new) && on32(e.q.cache.k) && on32(e.q.cache.v) && on32(e.q.cs)) {
+        on32(e.q.q_out) && on32(e.q.k_new) && on32(e.q.v_new) && on32(e.q.cache.k) && on32(e.q.cache.v) && on32(e.q.cs) &&
+        on32(e.q.gq) && on32(e.q.gk)) {
         // many tokens: tokens on the accumulator's lanes, 256 features (whole heads) per tile
         if (make_map(&mw, w, N, K, GQ_BN)) return 1;
         if (make_map(&mx, x, M, K, GT_BM)) return 1;
