@@ -87,6 +87,15 @@ __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ void from_f32(float& dst, float v) { dst = v; }
 __device__ __forceinline__ void from_f32(__nv_bfloat16& dst, float v) { dst = __float2bfloat16_rn(v); }
+// four consecutive elements as one store (the address on an 8-byte border in bfloat16, 16-byte in 32-bit);
+// each value rounded as from_f32 rounds it
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
 
 // 16-byte vector of T: 8 bfloat16 or 4 float
 template <typename U> struct Vec16;

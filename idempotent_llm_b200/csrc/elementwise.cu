@@ -87,8 +87,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec4_kernel(float* __restrict
     if (live) {
         const float4 gm = *reinterpret_cast<const float4*>(gamma + c);
         T* xr = x + (size_t)i * hidden + c;
-        from_f32(xr[0], v.x * inv * gm.x); from_f32(xr[1], v.y * inv * gm.y);
-        from_f32(xr[2], v.z * inv * gm.z); from_f32(xr[3], v.w * inv * gm.w);
+        store4(xr, v.x * inv * gm.x, v.y * inv * gm.y, v.z * inv * gm.z, v.w * inv * gm.w);
     }
 }
 
@@ -125,8 +124,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
         const int c = (32 * w + lane) * 4;
         if (c < hidden) {
             const float4 gm = *reinterpret_cast<const float4*>(gamma + c);
-            from_f32(xr[c + 0], v[w].x * inv * gm.x); from_f32(xr[c + 1], v[w].y * inv * gm.y);
-            from_f32(xr[c + 2], v[w].z * inv * gm.z); from_f32(xr[c + 3], v[w].w * inv * gm.w);
+            store4(xr + c, v[w].x * inv * gm.x, v[w].y * inv * gm.y, v[w].z * inv * gm.z, v[w].w * inv * gm.w);
         }
     }
 }
