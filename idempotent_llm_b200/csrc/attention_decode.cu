@@ -156,8 +156,12 @@ __device__ __forceinline__ void decode_merge_head_wide(const DecodeArgs& a, int 
     }
     const float inv = 1.0f / L;
     T* orow = a.out + (size_t)warp * HD + lane * V;
+    if constexpr (V == 4) {
+        store4(orow, acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+    } else {
 #pragma unroll
-    for (int i = 0; i < V; ++i) from_f32(orow[i], acc[i] * inv);
+        for (int i = 0; i < V; ++i) from_f32(orow[i], acc[i] * inv);
+    }
 }
 
 template <int HD, int GT>
