@@ -13,15 +13,18 @@ a library, ``torch._int_mm``, src/detllm/backends.py:88-135); ``IDM_GEMM=library
 switches to the GEMM torch wraps, which is kept only to compare against.
 
 Environment switches (all default to the fast path): ``IDM_GEMM``, ``IDM_FUSED``,
-``IDM_FUSED_MIN_TOKENS``, ``IDM_FUSED_MAX_SMALL``, ``IDM_PREFILL``, ``IDM_PDL``,
-``IDM_PDL_ATTN``, ``IDM_DECODE_MMA``.
+``IDM_FUSED_MIN_TOKENS``, ``IDM_FUSED_MAX_SMALL``, ``IDM_PREFILL``, ``IDM_PREFILL_RUN``,
+``IDM_PDL``, ``IDM_PDL_ATTN``, ``IDM_DECODE_MMA``.
+
+The entry points are called through ctypes with declared argument types (``SIGNATURES``), so that a
+call passes plain integers and floats; the current stream's handle comes from torch without a stream
+object being built.
 """
 
 from __future__ import annotations
 
 import ctypes
 import os
-import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
