@@ -301,22 +301,27 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         if (ok) ok = mbar_wait(o_done, (nb - 1) & 1, abort_flag, &g_attn_prefill_error);
         T* orow = a.out + ((size_t)(tok0 + r) * a.n_q + head) * HD;
-        if (ok && n_runs > 1) {
+        ok = __all_sync(0xffffffffu, ok);                          // (one answer per warp for what follows)
+        if (n_runs > 1) {
             // This run's result goes to its place among the tile's; the block that comes last adds them
             // all, in the order of the runs whoever it is, so the sum does not depend on who came last.
-            tc_fence_after();
+            // (A warp whose wait ran out skips the work but not the two barriers and the count: the
+            // error is reported, the result is wrong, and nobody waits for anybody for ever.)
             float* part0 = a.parts + (size_t)(tile * a.n_q + head) * a.max_split * S::PART;
             float4* mine = reinterpret_cast<float4*>(part0 + (size_t)run * S::PART);
+            if (ok) {
+                tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < HD; c += 16) {
-                float o[16];
-                tc_ld16(tmem_o + lane_base + c, o);
+                for (int c = 0; c < HD; c += 16) {
+                    float o[16];
+                    tc_ld16(tmem_o + lane_base + c, o);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    mine[(c / 4 + k) * AP_BM + r] = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
+                    for (int k = 0; k < 4; ++k)
+                        mine[(c / 4 + k) * AP_BM + r] = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
+                }
+                reinterpret_cast<float2*>(mine + (HD / 4) * AP_BM)[r] = make_float2(m_ref, l);
+                __threadfence();
             }
-            reinterpret_cast<float2*>(mine + (HD / 4) * AP_BM)[r] = make_float2(m_ref, l);
-            __threadfence();
             volatile int* last_flag = (volatile int*)(gbase + S::BAR_OFF + 128);
             asm volatile("bar.sync 1, 128;" ::: "memory");         // the four softmax warps
             if (r == 0) {
@@ -326,7 +331,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 *last_flag = is_last;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (*last_flag) {
+            if (*last_flag && ok) {
                 __threadfence();
                 float f[AP_MAX_SPLIT], m_all = -INFINITY, l_all = 0.f;
 #pragma unroll
@@ -429,6 +434,7 @@ extern "C" int idm_attention_prefill_max_run(long long key_blocks, int longest, 
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;                               // (no answer from the device: the B200's count)
     const long long share = (key_blocks + 2 * sms - 1) / (2 * sms);
     const long long run = share + share / 4 + 2;
     return (int)(run < AP_MIN_RUN ? AP_MIN_RUN : run > longest ? longest : run);
