@@ -67,6 +67,17 @@ def pack_step_host(slots: List[int], starts: List[int], token_lists: List[List[i
     return torch.from_numpy(buf), n, q_lens
 
 
+def advance_packed_single(buf: np.ndarray, n_seq: int, tokens: Sequence[int]) -> None:
+    """In place: the packed step of ``n_seq`` sequences with one token each (``pack_step_host``)
+    becomes the step that follows it for the same sequences: ``tokens`` are the new tokens, positions,
+    first new positions and lengths move on by one; sequence numbers, ``cu_q``, slots and the wanted
+    rows stay."""
+    n = n_seq
+    buf[0:n] = tokens
+    buf[2 * n:3 * n] += 1                      # positions
+    buf[5 * n + 1:7 * n + 1] += 1              # q_start and kv_len
+
+
 def context_from_packed(dev_buf: torch.Tensor, n: int, slots: List[int], q_lens: List[int],
                         starts: List[int], max_kv_len=None) -> StepContext:
     n_seq = len(slots)

@@ -18,7 +18,7 @@ import torch
 
 from ..cache import CacheError, SequenceCache
 from .assembly import CausalLM, cache_needs
-from .batch import StepContext, context_from_packed, pack_step_host
+from .batch import StepContext, advance_packed_single, context_from_packed, pack_step_host
 
 
 class _DecodeGraph:
@@ -52,10 +52,7 @@ class _DecodeGraph:
         if packed is not None:
             self.host[:self.packed_size].copy_(packed)
         else:
-            n, h = self.n, self.host_np
-            h[0:n] = tokens
-            h[2 * n:3 * n] += 1                          # positions
-            h[5 * n + 1:7 * n + 1] += 1                  # first new position and length after the step
+            advance_packed_single(self.host_np, self.n, tokens)
         self.last_slots, self.next_starts = slots, [st + 1 for st in starts]
         if self.keys:
             self.host[self.keys_at:].view(torch.int64).copy_(keys)

@@ -12,7 +12,11 @@ admits.
 The loop only needs ``open() -> slot``, ``close(slot)``,
 ``step(entries, want) -> logits`` and ``sample(logits, temperature, seed,
 request_ids, steps) -> list[int]`` from the engine, so its decisions are
-testable with a stand-in.
+testable with a stand-in.  An engine that also has ``step_sample(entries,
+temperature, seed, request_ids, steps) -> (tokens, logits)`` is asked for the
+two at once when every sequence brings one token; the logits it returns (and
+``on_step`` sees) are valid until the engine's next step, so what is kept
+(``return_logits``) is copied.
 """
 
 from __future__ import annotations

@@ -115,3 +115,18 @@ def test_generator_of_the_sampler_is_the_documented_one():
         assert mix64(x) == plain._mix(x)
     assert row_key(7, 3, 11) == plain._mix(plain._mix(plain._mix(7) ^ 3) ^ 11)
     assert row_key(7, 3, 11) != row_key(7, 4, 11) != row_key(7, 3, 12)
+
+
+def test_packed_single_token_step_moved_on_in_place_is_the_next_step_packed_anew():
+    """The step function keeps the packed arrays of a batch that goes on by one token and updates them
+    in place; that must give what packing the next step from scratch gives."""
+    import numpy as np
+    from idempotent_llm_b200.engine.batch import advance_packed_single, pack_step_host
+    slots, starts = [3, 0, 7, 5], [10, 63, 64, 0]
+    first, n, _ = pack_step_host(slots, starts, [[11], [12], [13], [14]], extra=range(4))
+    buf = first.numpy().copy()
+    for step in range(1, 4):
+        tokens = [100 * step + i for i in range(4)]
+        advance_packed_single(buf, 4, tokens)
+        anew, _, _ = pack_step_host(slots, [s + step for s in starts], [[t] for t in tokens], extra=range(4))
+        assert np.array_equal(buf, anew.numpy()), f"step {step}"
