@@ -36,12 +36,28 @@ def peaks():
         try:
             with open(path) as f:
                 m = json.load(f)
-            p["hbm_gbs"] = float(m.get("hbm_gbs", p["hbm_gbs"]))
-            p["bf16_tflops"] = float(m.get("bf16_tflops", p["bf16_tflops"]))
-            p["source"] = "measured"
+            hbm, flops = _number(m.get("hbm_gbs")), _number(m.get("bf16_tflops"))
+            if hbm and flops:                      # both or neither: one source for the whole line
+                p.update(hbm_gbs=hbm, bf16_tflops=flops, source="measured")
         except (ValueError, OSError, TypeError, AttributeError):
             pass
     return p
+
+
+def _number(v):
+    """A figure of the measured-peaks file: a number, or a record or list that holds one."""
+    if isinstance(v, bool) or v is None:
+        return None
+    if isinstance(v, (int, float)):
+        return float(v) if v > 0 else None
+    if isinstance(v, dict):
+        for key in ("value", "median", "mean", "max"):
+            if key in v:
+                return _number(v[key])
+        return None
+    if isinstance(v, (list, tuple)) and v:
+        return _number(v[0])
+    return None
 
 
 class ClockSampler:
