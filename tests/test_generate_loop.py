@@ -130,3 +130,36 @@ def test_packed_single_token_step_moved_on_in_place_is_the_next_step_packed_anew
         advance_packed_single(buf, 4, tokens)
         anew, _, _ = pack_step_host(slots, [s + step for s in starts], [[t] for t in tokens], extra=range(4))
         assert np.array_equal(buf, anew.numpy()), f"step {step}"
+
+
+class FusedFakeEngine(FakeEngine):
+    """The same with the step and the pick in one call for sequences that bring one token each."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.fused_calls, self.plain_calls = 0, 0
+
+    def step(self, entries, want):
+        self.plain_calls += 1
+        return super().step(entries, want)
+
+    def step_sample(self, entries, temperature, seed, request_ids, steps):
+        assert all(len(t) == 1 for _, t in entries), "asked for more than one token per sequence"
+        self.fused_calls += 1
+        self.plain_calls -= 1
+        logits = self.step(entries, [[0]] * len(entries))
+        return self.sample(logits, temperature, seed, request_ids, steps), logits
+
+
+def test_an_engine_that_can_step_and_pick_at_once_is_asked_to_for_single_tokens():
+    prompts = [[1, 2, 3], [10], [20, 21]]
+    e = FusedFakeEngine(max_slots=4)
+    res = generate(e, prompts, 4, stop_token_ids=[12], max_tokens=64 * 8, max_seqs=4, return_logits=True)
+    _, want = run(prompts, 4, stop_token_ids=[12], return_logits=True)
+    assert [r.tokens for r in res] == [r.tokens for r in want] == [[4, 5, 6, 7], [11, 12], [22, 23, 24, 25]]
+    assert [r.finish_reason for r in res] == [r.finish_reason for r in want]
+    assert e.plain_calls == 1 and e.fused_calls == 3          # the prompts, then one token each three times
+    assert all(torch.equal(a, b) for r, w in zip(res, want) for a, b in zip(r.logits, w.logits))
+    assert not e.held
+    # request ids and step numbers of the last pick: the two sequences still alive, at their fourth token
+    assert e.last_sample == ([0, 2], [3, 3])
