@@ -184,101 +184,8 @@ def cmd_bench(args) -> int:
 
 
 def cmd_kernel_bench(args) -> int:
-    """One kernel alone at a preset's layer sizes, timed with CUDA events (L2 flushed between runs)."""
-    import math
-    from .cache import CacheNeed, SequenceCache
-    from .config.presets import preset
-    from .kernels import Kernels
-    cfg = preset(args.size)
-    K = Kernels(torch.bfloat16, "cuda:0")
-    n_q, n_kv, hd, H, I = (cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size,
-                           cfg.intermediate_size)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    g = torch.Generator().manual_seed(0)
-
-    def timed(fn, reps=args.reps):
-        for _ in range(3):
-            fn()
-        ts = []
-        for _ in range(reps):
-            flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); fn(); e1.record()
-            torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1) * 1e-3)
-        ts.sort()
-        return ts[len(ts) // 2]
-
-    if args.kernel in ("attention_decode", "attention_prefill"):
-        B = args.batch
-        cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, B * args.capacity, torch.bfloat16, "cuda:0",
-                              max_seqs=B, max_seq_len=args.capacity)
-        slots = [cache.alloc_slot() for _ in range(B)]
-        lens = [int(torch.randint(int(args.context * 0.7), args.context + 1, (1,), generator=g)) for _ in range(B)]
-        if args.kernel == "attention_prefill":
-            lens = [args.context] * B
-        cache.reserve(list(zip(slots, lens))); cache.flush()
-        kv = cache.view(0)
-        scale = 1.0 / math.sqrt(hd)
-        if args.kernel == "attention_decode":
-            q = torch.randn(B, n_q, hd, device="cuda").bfloat16()
-            sl = torch.tensor(slots, dtype=torch.int32, device="cuda")
-            kl = torch.tensor(lens, dtype=torch.int32, device="cuda")
-            t = timed(lambda: K.attention_decode(q, kv, sl, kl, args.capacity, scale, 0))
-            byt = sum(lens) * n_kv * hd * 2 * 2
-            print(f"attention_decode {args.size} batch={B} context~{args.context}: {t * 1e6:.1f} us, "
-                  f"{byt / 1e6:.1f} MB of keys and values, {byt / t / 1e9:.0f} GB/s")
-        else:
-            from .engine.batch import context_from_packed, pack_step_host
-            packed, n, q_lens = pack_step_host(slots, [0] * B, [[0] * L for L in lens])
-            ctx = context_from_packed(packed.cuda(), n, slots, q_lens, [0] * B)
-            q = torch.randn(n, n_q, hd, device="cuda").bfloat16()
-            t = timed(lambda: K.attention_prefill(q, kv, ctx, scale))
-            fl = sum(4 * hd * n_q * L * (L + 1) // 2 for L in lens)
-            print(f"attention_prefill {args.size} batch={B} tokens={args.context}: {t * 1e6:.1f} us, "
-                  f"{fl / 1e9:.1f} GFLOP (causal), {fl / t / 1e12:.0f} TFLOP/s")
-    elif args.kernel == "gemm":
-        shapes = {"qkv": ((n_q + 2 * n_kv) * hd, H), "o": (H, n_q * hd), "gate_up": (2 * I, H), "down": (H, I),
-                  "lm_head": (cfg.vocab_size, H)}
-        for name, (N, Kd) in shapes.items():
-            x = torch.randn(args.tokens, Kd, device="cuda").bfloat16()
-            w = (torch.randn(N, Kd, device="cuda") * 0.02).bfloat16()
-            t = timed(lambda: K.gemm(x, w))
-            fl, byt = 2.0 * args.tokens * N * Kd, 2.0 * N * Kd
-            print(f"gemm {name} [{args.tokens} x {Kd}] . [{N} x {Kd}]^T: {t * 1e6:.1f} us, {fl / t / 1e12:.1f} TFLOP/s, "
-                  f"weights {byt / t / 1e9:.0f} GB/s")
-    elif args.kernel == "gemm_fused":
-        # the four products of a layer with their fused epilogues, as the parts call them
-        from .engine.batch import context_from_packed, pack_step_host
-        M = args.tokens
-        cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, -(-M // 64) * 64 + 64, torch.bfloat16, "cuda:0",
-                              max_seqs=1, max_seq_len=-(-M // 64) * 64 + 64)
-        slot = cache.alloc_slot()
-        cache.reserve([(slot, M)]); cache.flush()
-        packed, n, q_lens = pack_step_host([slot], [0], [[0] * M])
-        ctx = context_from_packed(packed.cuda(), n, [slot], q_lens, [0])
-        kv = cache.view(0)
-        rnd = lambda *shape: (torch.randn(*shape, device="cuda") * 0.05).bfloat16()
-        x, xo, xi = rnd(M, H) * 20, rnd(M, n_q * hd) * 20, rnd(M, I) * 20
-        w_qkv, w_o, w_down = rnd((n_q + 2 * n_kv) * hd, H), rnd(H, n_q * hd), rnd(H, I)
-        w_gu = K.tile_gate_up(rnd(I, H), rnd(I, H))
-        gq = torch.ones(hd, device="cuda"); gk = torch.ones(hd, device="cuda")
-        inv = 1e6 ** (-2.0 * torch.arange(0, hd // 2, dtype=torch.float64) / hd)
-        cs = K.rope_table(ctx.positions, inv.cuda())
-        h = torch.zeros(M, H, device="cuda")
-        runs = {"qkv (norm, rotation, cache write)": (lambda: K.gemm_qkv(x, w_qkv, n_q, n_kv, hd, gq, gk, 1e-6, cs, ctx, kv,
-                                                                           keep_new=False), (n_q + 2 * n_kv) * hd, H),
-                "o (residual add)": (lambda: K.gemm_residual(xo, w_o, h), H, n_q * hd),
-                "gate_up (SwiGLU)": (lambda: K.gemm_swiglu(x, w_gu, I), 2 * I, H),
-                "down (residual add)": (lambda: K.gemm_residual(xi, w_down, h), H, I)}
-        for name, (fn, N, Kd) in runs.items():
-            t = timed(fn)
-            fl, byt = 2.0 * M * N * Kd, 2.0 * N * Kd
-            print(f"gemm {name} [{M} x {Kd}] . [{N} x {Kd}]^T: {t * 1e6:.1f} us, {fl / t / 1e12:.1f} TFLOP/s, "
-                  f"weights {byt / t / 1e9:.0f} GB/s")
-    else:
-        raise ValueError(f"unknown kernel {args.kernel!r}")
-    return 0
+    from .kernel_bench import run
+    return run(args)
 
 
 def _ids(text: str) -> List[int]:
@@ -351,7 +258,7 @@ def main(argv=None) -> int:
     r.set_defaults(fn=cmd_random)
 
     k = sub.add_parser("kernel-bench", help="one kernel alone at a preset's layer sizes")
-    k.add_argument("--kernel", required=True, choices=["attention_decode", "attention_prefill", "gemm", "gemm_fused"])
+    k.add_argument("--kernel", required=True, choices=["attention_single", "attention_single_mma", "attention_prompt", "gemm", "gemm_fused"])
     k.add_argument("--size", default="qwen3-0.6b")
     k.add_argument("--batch", type=int, default=8)
     k.add_argument("--context", type=int, default=3000)

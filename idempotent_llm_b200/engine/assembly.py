@@ -68,10 +68,7 @@ class CausalLM:
             h, pending = self.blocks[e.layer].forward(h, pending, ctx, cache.view(e.cache),
                                                       cache.state_of(e.cache), e.writes_cache)
         x = self.final_norm.forward(h, pending, ctx, rows=want_rows)
-        if getattr(K, "fused", False) and K.use_fused(x.shape[0], self.head) and self.spec.hidden % 8 == 0:
-            return K.gemm_store(x, self.head)
-        logits = K.gemm(x, self.head)
-        return logits[0] if logits.shape[0] == 1 else logits.sum(0)
+        return K.gemm_store(x, self.head)
 
     def weight_bytes(self) -> int:
         seen, n = set(), 0

@@ -9,12 +9,12 @@ library's message when a launch is refused.  There is no CPU path: constructing
 Matrix products: the 32-bit library has its own FMA kernel (no tensor cores, no
 reduced-precision mode).  In bfloat16 they run on the hand-written tcgen05
 kernels of ``csrc/gemm_tcgen05.cu`` (the reference sends every matrix product to
-a library, ``torch._int_mm``, src/detllm/backends.py:88-135); ``IDM_GEMM=library``
-switches to the GEMM torch wraps, which is kept only to compare against.
+a library, ``torch._int_mm``, src/detllm/backends.py:88-135).  No product is sent
+to a library here, and none is split over its inner axis: an element is one chain
+of additions whatever the step's size.
 
-Environment switches (all default to the fast path): ``IDM_GEMM``, ``IDM_FUSED``,
-``IDM_FUSED_MIN_TOKENS``, ``IDM_FUSED_MAX_SMALL``, ``IDM_PREFILL``, ``IDM_PREFILL_RUN``,
-``IDM_PDL``, ``IDM_PDL_ATTN``, ``IDM_DECODE_MMA``.
+Environment switches (all default to the fast path): ``IDM_FUSED``, ``IDM_PREFILL``,
+``IDM_PDL``.
 
 The entry points are called through ctypes with declared argument types (``SIGNATURES``), so that a
 call passes plain integers and floats; the current stream's handle comes from torch without a stream
@@ -70,22 +70,18 @@ SIGNATURES = {
     "idm_attention_decode_scratch_floats": (c_longlong, "iiii"),
     "idm_attention_decode": (c_int, "pppppiipppiiiiifip"),
     "idm_attention_decode_static": (c_int, "pppppiippiiiiifip"),
-    "idm_attention_prefill_supports": (c_int, "i"),
-    "idm_attention_prefill_max_run": (c_int, "qiii"),
-    "idm_attention_prefill_scratch_floats": (c_longlong, "iiii"),
-    "idm_attention_prefill": (c_int, "ppppipippippppiiiifiipp"),
-    "idm_attention_prefill_status": (c_int, ""),
+    "idm_attention_tc_supports": (c_int, "i"),
+    "idm_attention_tc_heads_per_tile": (c_int, "ii"),
+    "idm_attention_tc_scratch_floats": (c_longlong, "iiiiii"),
+    "idm_attention_tc": (c_int, "ppppipippippppiiiifiiipp"),
+    "idm_attention_tc_status": (c_int, ""),
     "idm_gemm_f32": (c_int, "pppiiip"),
-    "idm_gemm_bf16_splits": (c_int, "iii"),
-    "idm_gemm_bf16_workspace_floats": (c_longlong, "iii"),
-    "idm_gemm_set_cluster": (None, "i"),
-    "idm_gemm_set_persistent": (None, "i"),
-    "idm_gemm_set_many_from": (None, "i"),
-    "idm_gemm_bf16": (c_int, "pppiiiip"),
-    "idm_gemm_bf16_store": (c_int, "ppppiiiip"),
-    "idm_gemm_bf16_residual": (c_int, "ppppiiiip"),
-    "idm_gemm_bf16_swiglu": (c_int, "ppppiiiip"),
-    "idm_gemm_bf16_qkv": (c_int, "pppiiiiiippfppppppppiipppp"),
+    "idm_gemm_set_small": (None, "ii"),
+    "idm_gemm_set_small_max": (None, "i"),
+    "idm_gemm_bf16": (c_int, "pppiiip"),
+    "idm_gemm_bf16_residual": (c_int, "pppiiip"),
+    "idm_gemm_bf16_swiglu": (c_int, "pppiiip"),
+    "idm_gemm_bf16_qkv": (c_int, "ppiiiiippfppppppppiipppp"),
     "idm_gemm_status": (c_int, ""),
 }
 
@@ -105,6 +101,7 @@ class Kernels:
         self.lib = builder.load(_DT[dtype])
         self.launches = 0                     # kernels of this library launched so far
         self._scratch = {}
+        self._single_tiles = {}
         self._device_index = device.index if device.index is not None else 0
         self._retired = []
         L = self.lib
@@ -117,46 +114,18 @@ class Kernels:
                 continue                      # an entry point of the other precision's library
             fn.restype = result
             fn.argtypes = [kinds[a] for a in args]
-        # "tcgen05": the hand-written tensor-core kernel; "library": the GEMM torch wraps (kept to
-        # compare against)
-        self.gemm_impl = os.environ.get("IDM_GEMM", "tcgen05")
         # fused epilogues of the tensor-core product (residual add, SwiGLU, q/k/v finish): parts use
-        # them when this is True and fall back to separate kernels otherwise
-        self.fused = (dtype == torch.bfloat16 and self.gemm_impl == "tcgen05"
-                      and os.environ.get("IDM_FUSED", "1") != "0")
-        # Up to 64 tokens the slices of a split inner axis are added inside a thread-block cluster and
-        # the epilogue is fused; above 256 tokens nothing is split and the epilogue is fused; between
-        # the two the separate kernels, which add the slices with the whole GPU, are quicker than one
-        # block per tile doing it -- unless the layer's products are so short that the library does not
-        # split them at all (see use_fused).  IDM_FUSED_MIN_TOKENS / IDM_FUSED_MAX_SMALL move the borders.
-        self.fused_min_tokens = int(os.environ.get("IDM_FUSED_MIN_TOKENS", "257"))
-        if dtype == torch.bfloat16:
-            L.idm_gemm_set_many_from(self.fused_min_tokens)
-        self.fused_max_small = int(os.environ.get("IDM_FUSED_MAX_SMALL", "64"))
-        # "tcgen05": prompts' attention on the tensor cores; "general": the one-warp-per-query kernel
-        self.prefill_impl = os.environ.get("IDM_PREFILL", "tcgen05")
-        # the most key blocks (of 64) one block of that kernel works through before a tile is cut into
-        # runs for several blocks; 0: by the step's size
-        self.prefill_run = int(os.environ.get("IDM_PREFILL_RUN", "0"))
+        # them when this is True and run separate kernels otherwise (IDM_FUSED=0, and the 32-bit library).
+        # Which of the two runs never depends on how many tokens a step brings.
+        self.fused = dtype == torch.bfloat16 and os.environ.get("IDM_FUSED", "1") != "0"
+        # "tcgen05": attention on the tensor cores wherever that kernel has the head size (64, 128) and the
+        # layer has no window; "general": the one-warp-per-query kernel everywhere.  Which kernel runs never
+        # depends on the step's shape, so prompts and single tokens give the same bits.
+        self.attention_impl = os.environ.get("IDM_ATTENTION", "tcgen05")
+        # key blocks (of 64) of a run of the tensor-core kernel: each run starts its sums from nothing and
+        # the runs are folded in ascending order, so this number is part of the arithmetic's definition
+        self.attention_run_blocks = 8
         self.page = L.idm_page_tokens()
-        self._gemm_plans = {}          # (M, N, K) -> (splits of the inner axis, workspace floats)
-
-    def use_fused(self, n_tokens: int, *weights) -> bool:
-        """Whether a part runs its products with fused epilogues at this many tokens: always up to
-        ``fused_max_small`` and from ``fused_min_tokens`` on; in between only if none of the part's
-        products (``weights``: their ``[N, K]`` matrices) is split over its inner axis."""
-        if not self.fused:
-            return False
-        if n_tokens >= self.fused_min_tokens or n_tokens <= self.fused_max_small:
-            return True
-        return bool(weights) and all(self._splits(n_tokens, w.shape[0], w.shape[1]) == 1 for w in weights)
-
-    def _splits(self, M: int, N: int, Kd: int) -> int:
-        plan = self._gemm_plans.get((M, N, Kd))
-        if plan is None:
-            P = self.lib.idm_gemm_bf16_splits(M, N, Kd)
-            plan = self._gemm_plans[(M, N, Kd)] = (P, self.lib.idm_gemm_bf16_workspace_floats(M, N, P))
-        return plan[0]
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -273,67 +242,78 @@ class Kernels:
             n_kv, hd, self._stream()))
 
     def attention(self, q, kv, ctx, k_new, v_new, scale: float, window) -> torch.Tensor:
-        """Causal attention of the step's queries over the cache entry; returns [N, n_q * hd]."""
+        """Causal attention of the step's queries over the cache entry; returns [N, n_q * hd].
+
+        One kernel per (dtype, head size, window or not) whatever the step looks like: the 32-bit
+        library and windowed layers take the general kernel, bfloat16 with head sizes 64 and 128 the
+        tensor-core kernel, for prompts and for single tokens alike."""
         self._need(q, self.dtype, "q")
         n, n_q, hd = q.shape
         self._check_kv(kv, kv.n_kv_heads, hd)
-        out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
         w = int(window) if window else 0
-        # 32-bit keeps ONE kernel for prompts and single tokens, so its logits are the same bits
-        # however a sequence is cut into steps; bfloat16 takes the bandwidth-bound decode kernel
-        if (self.dtype != torch.float32 and ctx.single_token and k_new is None
-                and self.lib.idm_attention_decode_supports(hd)):
-            return self.attention_decode(q, kv, ctx.slots, ctx.kv_len, ctx.max_kv_len, scale, w, out)
-        if (self.dtype == torch.bfloat16 and self.prefill_impl == "tcgen05" and not ctx.single_token
-                and k_new is None and not w and kv.ring == 0 and self.lib.idm_attention_prefill_supports(hd)):
-            return self.attention_prefill(q, kv, ctx, scale, out)
-        self._check(self.lib.idm_attention_generic(
-            _p(q), _p(out), _p(kv.k), _p(kv.v), _p(kv.table),
-            kv.table.shape[1], kv.ring, _p(k_new), _p(v_new),
-            _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots),
-            _p(ctx.q_start), _p(ctx.cu_q), n, n_q, kv.n_kv_heads,
-            hd, scale, w, self._stream()))
-        return out
+        if (self.dtype == torch.bfloat16 and self.attention_impl == "tcgen05" and k_new is None and not w
+                and kv.ring == 0 and self.lib.idm_attention_tc_supports(hd)):
+            return self.attention_tc(q, kv, ctx, scale)
+        return self.attention_generic(q, kv, ctx, k_new, v_new, scale, window)
 
-    def attention_prefill(self, q, kv, ctx, scale: float, out=None) -> torch.Tensor:
-        """Causal attention of prompts on the tensor cores (tiles of 128 query tokens x q-heads)."""
+    def attention_tc(self, q, kv, ctx, scale: float, out=None, through_scratch=None) -> torch.Tensor:
+        """Causal attention on the tensor cores: tiles of (128 / gp tokens) x (gp q-heads of one kv-head).
+
+        Steps with few tokens per sequence (at most 32 rows a tile: single tokens above all) give every
+        run of key blocks a block of its own, and the runs meet in scratch; other steps let one block
+        walk a tile's runs.  ``through_scratch`` forces one or the other (tests: the bits are the same)."""
         n, n_q, hd = q.shape
+        n_kv = kv.n_kv_heads
         if out is None:
             out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
-        tiles = ctx.memo.get("prefill_tiles")
+        gp = self.lib.idm_attention_tc_heads_per_tile(n_q, n_kv)
+        tok = 128 // gp
+        R = self.attention_run_blocks
+        tiles = ctx.memo.get(("attention_tc_tiles", gp))
+        if tiles is None and ctx.single_token:
+            # one tile per sequence: the same list for every step of that many sequences (kept, so that a
+            # step being captured into a graph copies nothing from the host)
+            tiles = self._single_tiles.get((ctx.n_seqs, gp))
+            if tiles is None:
+                dev = torch.stack([torch.arange(ctx.n_seqs, dtype=torch.int32),
+                                   torch.zeros(ctx.n_seqs, dtype=torch.int32)]).to(self.device)
+                tiles = self._single_tiles[(ctx.n_seqs, gp)] = (dev, dev[0].data_ptr(), dev[1].data_ptr(), ctx.n_seqs, gp)
         if tiles is None:
             # (sequence, first token of the tile); tiles with the most keys first, so that the longest
             # blocks start first
             items = []
             for i, L in enumerate(ctx.host_q_lens):
-                for st in range(0, L, 128):
-                    items.append((ctx.host_starts[i] + min(st + 127, L - 1), i, st))
+                for st in range(0, L, tok):
+                    items.append((ctx.host_starts[i] + min(st + tok - 1, L - 1), i, st))
             items.sort(key=lambda t: -t[0])
             host = torch.tensor([[i for _, i, _ in items], [st for _, _, st in items]], dtype=torch.int32)
-            blocks = [last // 64 + 1 for last, _, _ in items]        # key blocks of each tile
             dev = host.to(self.device)
-            tiles = ctx.memo["prefill_tiles"] = (dev, dev[0].data_ptr(), dev[1].data_ptr(), len(items), sum(blocks),
-                                                 blocks[0])
-        _, tile_seq, tile_start, n_tiles, key_blocks, longest = tiles
-        plan = ctx.memo.get(("prefill_runs", n_q, hd, self.prefill_run))
-        if plan is None:
-            max_run = self.prefill_run or self.lib.idm_attention_prefill_max_run(
-                key_blocks * n_q, longest, n_tiles, n_q)
-            split = min(4, -(-longest // max_run))
-            need = self.lib.idm_attention_prefill_scratch_floats(n_tiles, n_q, hd, split)
-            plan = ctx.memo[("prefill_runs", n_q, hd, self.prefill_run)] = (max_run, split, need)
-        max_run, split, need = plan
-        scratch = self.scratch("attention_prefill", need) if need else None
-        self._check(self.lib.idm_attention_prefill(
+            rows_cap = min(tok, max(ctx.host_q_lens)) * gp
+            tiles = ctx.memo[("attention_tc_tiles", gp)] = (dev, dev[0].data_ptr(), dev[1].data_ptr(), len(items), rows_cap)
+        _, tile_seq, tile_start, n_tiles, rows_cap = tiles
+        # an upper bound of the key blocks any tile has (a captured step is replayed at growing lengths)
+        longest = -(-ctx.max_kv_len // self.page)
+        max_runs = -(-longest // R)
+        if through_scratch is None:
+            through_scratch = rows_cap <= 32
+        if through_scratch:
+            if rows_cap > 128:
+                raise KernelError("attention_tc: runs through scratch hold at most 128 rows a tile")
+            need = self.lib.idm_attention_tc_scratch_floats(n_tiles, n_q, n_kv, hd, max_runs, rows_cap)
+        else:
+            need = self.lib.idm_attention_tc_scratch_floats(n_tiles, n_q, n_kv, hd, 0, 0) if max_runs > 1 else 0
+            max_runs = 0
+        scratch = self.scratch("attention_tc", need) if need else None
+        self._check(self.lib.idm_attention_tc(
             _p(q), _p(out), _p(kv.k), _p(kv.v), kv.k.shape[0],
             _p(kv.table), kv.table.shape[1], tile_seq, tile_start, n_tiles, _p(ctx.cu_q), _p(ctx.q_start),
-            _p(ctx.kv_len), _p(ctx.slots), n, n_q, kv.n_kv_heads,
-            hd, scale, split, max_run, _p(scratch),
+            _p(ctx.kv_len), _p(ctx.slots), n, n_q, n_kv,
+            hd, scale, R, max_runs, rows_cap, _p(scratch),
             self._stream()))
         return out
 
-    def attention_prefill_status(self) -> int:
-        return 0 if self.dtype == torch.float32 else self.lib.idm_attention_prefill_status()
+    def attention_tc_status(self) -> int:
+        return 0 if self.dtype == torch.float32 else self.lib.idm_attention_tc_status()
 
     def attention_generic(self, q, kv, ctx, k_new, v_new, scale: float, window) -> torch.Tensor:
         """The general kernel, whatever the step's shape (tests compare the special kernels with it)."""
@@ -382,27 +362,10 @@ class Kernels:
         return y
 
     def gemm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        """``x [M, K] . w [N, K]^T`` -> 32-bit partial sums ``[P, M, N]`` (their sum over P is the product)."""
-        self._need(x, self.dtype, "gemm input")
-        self._need(w, self.dtype, "gemm weight")
-        M, Kd = x.shape
-        N, K2 = w.shape
-        if Kd != K2:
-            raise KernelError(f"gemm: input rows have {Kd} elements, weight rows {K2}")
-        if self.dtype == torch.float32:
-            out = torch.empty((1, M, N), dtype=torch.float32, device=self.device)
-            self._check(self.lib.idm_gemm_f32(_p(x), _p(w), _p(out), M,
-                                              N, Kd, self._stream()))
-            return out
-        if self.gemm_impl == "library" or Kd % 8 or M == 0:
-            return self._gemm_library(x, w)
-        P = self.lib.idm_gemm_bf16_splits(M, N, Kd)
-        out = torch.empty((P, M, N), dtype=torch.float32, device=self.device)
-        self._check(self.lib.idm_gemm_bf16(_p(x), _p(w), _p(out), M, N,
-                                           Kd, P, self._stream()))
-        return out
+        """``x [M, K] . w [N, K]^T`` in 32-bit as ``[1, M, N]`` (the leading axis is the one a part's
+        delta carries: partial sums that the consumer adds; these kernels never split a sum)."""
+        return self.gemm_store(x, w).unsqueeze(0)
 
-    # ---- fused epilogues (bfloat16 only) ------------------------------------------------------------
     def _gemm_shape(self, x, w):
         self._need(x, self.dtype, "gemm input")
         self._need(w, self.dtype, "gemm weight")
@@ -410,31 +373,30 @@ class Kernels:
         N, K2 = w.shape
         if Kd != K2:
             raise KernelError(f"gemm: input rows have {Kd} elements, weight rows {K2}")
-        if Kd % 8:
-            raise KernelError(f"gemm: the inner size {Kd} must be a multiple of 8 for the fused kernels")
-        P = self._splits(M, N, Kd)
-        return M, N, Kd, P, self.scratch("gemm_ws", self._gemm_plans[(M, N, Kd)][1])
+        if self.dtype == torch.bfloat16 and Kd % 8:
+            raise KernelError(f"gemm: the inner size {Kd} must be a multiple of 8 in bfloat16 (rows on 16-byte borders)")
+        return M, N, Kd
 
     def gemm_store(self, x, w) -> torch.Tensor:
-        """``x . w^T`` finished in 32-bit ``[M, N]``."""
-        M, N, Kd, P, ws = self._gemm_shape(x, w)
+        """``x . w^T`` in 32-bit ``[M, N]``."""
+        M, N, Kd = self._gemm_shape(x, w)
         out = torch.empty((M, N), dtype=torch.float32, device=self.device)
         if M:
-            self._check(self.lib.idm_gemm_bf16_store(_p(x), _p(w), _p(out),
-                                                     _p(ws), M, N, Kd, P,
-                                                     self._stream()))
+            if self.dtype == torch.float32:
+                self._check(self.lib.idm_gemm_f32(_p(x), _p(w), _p(out), M, N, Kd, self._stream()))
+            else:
+                self._check(self.lib.idm_gemm_bf16(_p(x), _p(w), _p(out), M, N, Kd, self._stream()))
         return out
 
+    # ---- fused epilogues (bfloat16 only) ------------------------------------------------------------
     def gemm_residual(self, x, w, h) -> None:
         """``h += x . w^T`` in 32-bit, in place."""
-        M, N, Kd, P, ws = self._gemm_shape(x, w)
+        M, N, Kd = self._gemm_shape(x, w)
         self._need(h, torch.float32, "residual stream")
         if tuple(h.shape) != (M, N):
             raise KernelError(f"residual stream {tuple(h.shape)} does not match the product {(M, N)}")
         if M:
-            self._check(self.lib.idm_gemm_bf16_residual(_p(x), _p(w), _p(h),
-                                                        _p(ws), M, N, Kd, P,
-                                                        self._stream()))
+            self._check(self.lib.idm_gemm_bf16_residual(_p(x), _p(w), _p(h), M, N, Kd, self._stream()))
 
     def tile_gate_up(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
         """Rows of gate and up alternating (gate row of a feature, then its up row), padded with zero
@@ -448,20 +410,21 @@ class Kernels:
 
     def gemm_swiglu(self, x, w_tiled, inter: int) -> torch.Tensor:
         """``silu(x . gate^T) * (x . up^T)`` in the storage dtype ``[M, inter]``."""
-        M, N, Kd, P, ws = self._gemm_shape(x, w_tiled)
+        M, N, Kd = self._gemm_shape(x, w_tiled)
         if N != -(-inter // 64) * 128:
             raise KernelError(f"tiled gate/up weight has {N} rows, expected {-(-inter // 64) * 128}")
         y = torch.empty((M, inter), dtype=self.dtype, device=self.device)
         if M:
-            self._check(self.lib.idm_gemm_bf16_swiglu(_p(x), _p(w_tiled), _p(y),
-                                                      _p(ws), M, inter, Kd, P,
-                                                      self._stream()))
+            self._check(self.lib.idm_gemm_bf16_swiglu(_p(x), _p(w_tiled), _p(y), M, inter, Kd, self._stream()))
         return y
 
+    QKV_FUSED_HEAD_DIMS = (32, 64, 128)
+
     def gemm_qkv(self, x, w, n_q, n_kv, hd, q_gamma, k_gamma, eps, cs, ctx, kv, keep_new: bool):
-        """The fused q/k/v projection with ``qkv_finish`` as its epilogue (128 % hd == 0)."""
-        M, N, Kd, P, ws = self._gemm_shape(x, w)
-        if N != (n_q + 2 * n_kv) * hd or 128 % hd:
+        """The fused q/k/v projection with norm, rotation and cache write as its epilogue
+        (head_dim in ``QKV_FUSED_HEAD_DIMS``)."""
+        M, N, Kd = self._gemm_shape(x, w)
+        if N != (n_q + 2 * n_kv) * hd or hd not in self.QKV_FUSED_HEAD_DIMS:
             raise KernelError(f"gemm_qkv: weight rows {N}, heads {(n_q, n_kv)}, head_dim {hd}")
         if cs is not None and tuple(cs.shape) != (M, hd // 2, 2):
             raise KernelError(f"rotary table {tuple(cs.shape)} does not match {(M, hd // 2, 2)}")
@@ -474,7 +437,7 @@ class Kernels:
             self._check_kv(kv, n_kv, hd)
         if M:
             self._check(self.lib.idm_gemm_bf16_qkv(
-                _p(x), _p(w), _p(ws), M, Kd, P, n_q,
+                _p(x), _p(w), M, Kd, n_q,
                 n_kv, hd, _p(q_gamma), _p(k_gamma), eps,
                 _p(cs), _p(getattr(cs, "by_dim", None)), _p(q), _p(k_new), _p(v_new),
                 (_p(kv.k) if kv is not None else None), (_p(kv.v) if kv is not None else None),
@@ -486,15 +449,6 @@ class Kernels:
     def gemm_status(self) -> int:
         """0, or 1 if a bounded wait inside the tensor-core GEMM ran out since the last call (synchronises)."""
         return 0 if self.dtype == torch.float32 else self.lib.idm_gemm_status()
-
-    def _gemm_library(self, x, w):
-        if M_is_zero(x):
-            return torch.empty((1, 0, w.shape[0]), dtype=torch.float32, device=self.device)
-        try:
-            out = torch.mm(x, w.t(), out_dtype=torch.float32)
-        except (TypeError, RuntimeError):
-            out = torch.mm(x, w.t()).to(torch.float32)
-        return out.unsqueeze(0)
 
     def sample(self, logits: torch.Tensor, temperature: float, keys: Optional[torch.Tensor]) -> torch.Tensor:
         self._need(logits, torch.float32, "logits")
@@ -517,7 +471,3 @@ class Kernels:
             _p(tokens), _p(positions), _p(q_start), _p(kv_len),
             _p(sampled), _p(history), _p(step_counter), n,
             history.shape[0], self._stream()))
-
-
-def M_is_zero(x) -> bool:
-    return x.shape[0] == 0

@@ -48,6 +48,9 @@ class GQAAttention(Mixer):
     def __init__(self, spec, weights, prefix, rt):
         if spec.n_heads % spec.n_kv_heads:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if rt.dtype == torch.bfloat16 and (spec.hidden % 8 or (spec.n_heads * spec.head_dim) % 8):
+            raise ValueError(f"in bfloat16 the widths of an attention layer must be multiples of 8 (matrix rows start "
+                             f"on 16-byte borders); got hidden {spec.hidden}, heads x head_dim {spec.n_heads * spec.head_dim}")
         self.spec = spec
         self.rt = rt
         p = prefix + "self_attn."
@@ -74,19 +77,18 @@ class GQAAttention(Mixer):
         if writes_cache == s.kv_from_other:
             raise ValueError("a mixer with its own k/v must write its cache entry; one without must not")
         cs = self.position.tables(ctx) if self.position is not None else None
-        fused = (bool(getattr(K, "fused", False)) and K.use_fused(x.shape[0], self.w_qkv, self.w_o) and s.hidden % 8 == 0
-                 and (s.n_heads * s.head_dim) % 8 == 0)
+        fused = bool(getattr(K, "fused", False))
         # A windowed layer's ring cannot hold a whole prompt, so a step of several tokens reads its
         # own keys from packed buffers and writes the ring afterwards.  A single token overwrites
         # position p - ring only, which lies outside its window, so it is written first like any key.
         windowed = kv.ring > 0 and not ctx.single_token
         finish = (s.n_heads, 0 if s.kv_from_other else s.n_kv_heads, s.head_dim, self.q_gamma, self.k_gamma,
                   s.qk_norm_eps, cs, ctx, kv if (writes_cache and not windowed) else None)
-        if fused and 128 % s.head_dim == 0:
+        if fused and s.head_dim in K.QKV_FUSED_HEAD_DIMS:
             # norm, rotation and the cache write are the epilogue of the projection
             q, k_new, v_new = K.gemm_qkv(x, self.w_qkv, *finish, keep_new=writes_cache and windowed)
         else:
-            qkv = K.gemm_store(x, self.w_qkv)[None] if fused else K.gemm(x, self.w_qkv)   # [P, N, (n_q [+ 2 n_kv]) * hd]
+            qkv = K.gemm(x, self.w_qkv)                                   # [1, N, (n_q [+ 2 n_kv]) * hd]
             q, k_new, v_new = K.qkv_finish(qkv, *finish, keep_new=writes_cache and windowed)
         o = K.attention(q, kv, ctx, k_new, v_new, s.softmax_scale, s.window)  # [N, n_q * hd]
         if writes_cache and windowed:

@@ -31,7 +31,10 @@ class GatedMLP(FeedForward):
         gate, up = weights[p + "gate_proj.weight"].to(rt.dtype), weights[p + "up_proj.weight"].to(rt.dtype)
         # with the fused kernels the activation is the epilogue of the gate/up product, which wants
         # gate and up rows interleaved in tiles; otherwise the rows are simply concatenated
-        self.fused = bool(getattr(rt.kernels, "fused", False)) and spec.hidden % 8 == 0 and spec.intermediate % 8 == 0
+        if rt.dtype == torch.bfloat16 and (spec.hidden % 8 or spec.intermediate % 8):
+            raise ValueError(f"in bfloat16 the widths of a feed-forward must be multiples of 8 (matrix rows start on "
+                             f"16-byte borders); got hidden {spec.hidden}, intermediate {spec.intermediate}")
+        self.fused = bool(getattr(rt.kernels, "fused", False))
         if self.fused:
             self.w_gate_up = rt.kernels.tile_gate_up(gate, up)
         else:
@@ -41,12 +44,12 @@ class GatedMLP(FeedForward):
     def forward(self, x, ctx, residual=None):
         """Returns the delta ``[P, N, hidden]``, or None after adding it into ``residual`` in place."""
         K = self.rt.kernels
-        if self.fused and K.use_fused(x.shape[0], self.w_gate_up, self.w_down):
+        if self.fused:
             y = K.gemm_swiglu(x, self.w_gate_up, self.spec.intermediate)
             if residual is not None:
                 K.gemm_residual(y, self.w_down, residual)
                 return None
             return K.gemm(y, self.w_down)
-        gu = K.gemm(x, self.w_gate_up)          # [P, N, 2 * intermediate] (tiled rows when self.fused)
-        y = K.swiglu(gu, tiled_inter=self.spec.intermediate if self.fused else None)   # [N, intermediate]
+        gu = K.gemm(x, self.w_gate_up)          # [P, N, 2 * intermediate]
+        y = K.swiglu(gu)                        # [N, intermediate]
         return K.gemm(y, self.w_down)           # [P, N, hidden]

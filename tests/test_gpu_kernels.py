@@ -202,11 +202,11 @@ def test_attention_general_kernel_prompts_with_history_and_new_keys(kernels, dty
         off += m
 
 
-@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (4, 4, 64), (6, 1, 128)])
-def test_attention_prefill_tensor_core_kernel(kernels, n_q, n_kv, hd):
-    """Tiles of 128 queries against pages of 64 keys: lengths straddle both borders, one sequence
-    continues from cached history, unused page tails and free pages hold NaN, one query looks at a
-    single far key."""
+@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (4, 4, 64), (6, 1, 128), (16, 8, 128), (32, 2, 64)])
+def test_attention_tensor_core_kernel(kernels, n_q, n_kv, hd):
+    """Tiles of 128 rows (the q-heads of a kv-head x tokens) against pages of 64 keys: lengths straddle
+    both borders, one sequence continues from cached history, unused page tails and free pages hold NaN,
+    one query looks at a single far key."""
     K = kernels("bfloat16")
     hist, new = [0, 0, 70, 0, 300], [1, 128, 200, 129, 333]
     lens = [h + n for h, n in zip(hist, new)]
@@ -219,9 +219,9 @@ def test_attention_prefill_tensor_core_kernel(kernels, n_q, n_kv, hd):
     qd = torch.cat(q).to(torch.bfloat16).cuda()
     packed, n, q_lens = pack_step_host(slots, hist, [[0] * m for m in new])
     ctx = context_from_packed(packed.cuda(), n, slots, q_lens, hist)
-    out = K.attention_prefill(qd, kv, ctx, scale).view(-1, n_q, hd)
+    out = K.attention_tc(qd, kv, ctx, scale).view(-1, n_q, hd)
     torch.cuda.synchronize()
-    assert K.attention_prefill_status() == 0, "a bounded wait inside the kernel ran out"
+    assert K.attention_tc_status() == 0, "a bounded wait inside the kernel ran out"
     gen = K.attention_generic(qd, kv, ctx, None, None, scale, None).view(-1, n_q, hd)
     assert torch.isfinite(out).all(), "stale page contents leaked into the result"
     off = 0
@@ -236,13 +236,14 @@ def test_attention_prefill_tensor_core_kernel(kernels, n_q, n_kv, hd):
     assert (got - vs[4][5, 0]).abs().max() < 0.05, "the far key did not dominate"
 
 
-@pytest.mark.parametrize("max_run", [1000, 11, 4, 0])
-@pytest.mark.parametrize("n_q,n_kv,hd", [(2, 1, 128), (3, 3, 64)])
-def test_attention_prefill_with_a_tile_s_keys_cut_into_runs(kernels, max_run, n_q, n_kv, hd):
-    """Long tiles of a short step are worked by several blocks, each a run of the tile's key blocks, and
-    the last to end adds the runs up.  Queries of the last tiles look at one key in the first run, at one
-    in a middle run and at the last key before the diagonal; a second launch gives the same bits, and
-    the arrival counters are back at zero (a third launch, of other sequences, is right too)."""
+@pytest.mark.parametrize("run_blocks", [8, 3, 2, 1])
+@pytest.mark.parametrize("n_q,n_kv,hd", [(2, 1, 128), (3, 3, 64), (8, 2, 128)])
+def test_attention_tensor_core_runs_and_cuts(kernels, run_blocks, n_q, n_kv, hd):
+    """A row's keys are worked in runs of key blocks that are folded in ascending order.  The bits of a row
+    must not depend on who works the runs (one block walking them, or a block per run meeting in
+    scratch), on what else the step holds, or on whether the row came with its prompt or alone as a single
+    token.  Queries of the last tiles look at one key in the first run, at one in a middle run and at the last
+    key before the diagonal; a second launch gives the same bits (the arrival counters are back at zero)."""
     K = kernels("bfloat16")
     hist, new = [0, 450, 0], [1300, 900, 130]
     lens = [h + n for h, n in zip(hist, new)]
@@ -256,14 +257,18 @@ def test_attention_prefill_with_a_tile_s_keys_cut_into_runs(kernels, max_run, n_
     qd = torch.cat(q).to(torch.bfloat16).cuda()
     packed, n, q_lens = pack_step_host(slots, hist, [[0] * m for m in new])
     ctx = context_from_packed(packed.cuda(), n, slots, q_lens, hist)
-    old = K.prefill_run
-    K.prefill_run = max_run
+    old = K.attention_run_blocks
+    K.attention_run_blocks = run_blocks
     try:
-        out = K.attention_prefill(qd, kv, ctx, scale).view(-1, n_q, hd)
-        again = K.attention_prefill(qd, kv, ctx, scale).view(-1, n_q, hd)
+        out = K.attention_tc(qd, kv, ctx, scale, through_scratch=False).view(-1, n_q, hd)
+        again = K.attention_tc(qd, kv, ctx, scale, through_scratch=False).view(-1, n_q, hd)
+        met = K.attention_tc(qd, kv, ctx, scale, through_scratch=True).view(-1, n_q, hd)
+        met2 = K.attention_tc(qd, kv, ctx, scale, through_scratch=True).view(-1, n_q, hd)
         torch.cuda.synchronize()
-        assert K.attention_prefill_status() == 0, "a bounded wait inside the kernel ran out"
-        assert torch.equal(out, again), "the sum of the runs depends on which block came last"
+        assert K.attention_tc_status() == 0, "a bounded wait inside the kernel ran out"
+        assert torch.equal(out, again)
+        assert torch.equal(met, met2), "the fold of the runs depends on which block came last"
+        assert torch.equal(out, met), "one block walking the runs and a block per run give other bits"
         gen = K.attention_generic(qd, kv, ctx, None, None, scale, None).view(-1, n_q, hd)
         assert torch.isfinite(out).all()
         assert helpers.rel_err(out, gen) < 2 * KTOL["bfloat16"]
@@ -280,12 +285,25 @@ def test_attention_prefill_with_a_tile_s_keys_cut_into_runs(kernels, max_run, n_
         # other sequences, other counters in use: only the last two
         packed, n2, q_lens2 = pack_step_host(slots[1:], hist[1:], [[0] * m for m in new[1:]])
         ctx2 = context_from_packed(packed.cuda(), n2, slots[1:], q_lens2, hist[1:])
-        out2 = K.attention_prefill(qd[new[0]:].contiguous(), kv, ctx2, scale).view(-1, n_q, hd)
-        torch.cuda.synchronize()
-        assert K.attention_prefill_status() == 0
+        out2 = K.attention_tc(qd[new[0]:].contiguous(), kv, ctx2, scale).view(-1, n_q, hd)
         assert torch.equal(out2, out[new[0]:]), "a tile's result depends on what else the step holds"
+        # the same queries as single tokens (and as a few tokens that straddle a run's border): the same bits
+        picks = [(0, 0), (0, 63), (0, 64), (0, 511), (0, 512), (0, 1299), (1, 0), (1, 61), (1, 62), (1, 899), (2, 129)]
+        for i, t in picks:
+            packed, n1, ql = pack_step_host([slots[i]], [hist[i] + t], [[0]])
+            ctx1 = context_from_packed(packed.cuda(), n1, [slots[i]], ql, [hist[i] + t], max_kv_len=2048)
+            one = K.attention_tc(qd[off[i] + t:off[i] + t + 1].contiguous(), kv, ctx1, scale).view(1, n_q, hd)
+            assert torch.equal(one[0], out[off[i] + t]), f"sequence {i} token {t} alone (position {hist[i] + t})"
+        for i, t, m in [(0, 500, 20), (1, 55, 12), (0, 1290, 10)]:
+            packed, nm, ql = pack_step_host([slots[i]], [hist[i] + t], [[0] * m])
+            ctxm = context_from_packed(packed.cuda(), nm, [slots[i]], ql, [hist[i] + t])
+            for ts in (None, True, False):
+                few = K.attention_tc(qd[off[i] + t:off[i] + t + m].contiguous(), kv, ctxm, scale, through_scratch=ts)
+                assert torch.equal(few.view(m, n_q, hd), out[off[i] + t:off[i] + t + m]), f"sequence {i} tokens {t}..{t + m}"
+        torch.cuda.synchronize()
+        assert K.attention_tc_status() == 0
     finally:
-        K.prefill_run = old
+        K.attention_run_blocks = old
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -375,49 +393,77 @@ def test_gemm_32_bit_is_true_32_bit_and_row_independent(kernels, M, N, K_):
     assert torch.equal(one[0, 0], out[0, M // 2]), "a row's result must not depend on the other rows"
 
 
-@pytest.mark.parametrize("impl", ["tcgen05", "library"])
+# Token counts on both sides of every border between kernels and tile shapes (16, 32, 64, 128 tokens on
+# the lanes of one kernel; 128- and 256-token tiles of another above that).
+CUTS = (1, 2, 16, 17, 32, 33, 64, 65, 128, 129, 200, 256, 257, 300)
+
+
 @pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (8, 1000, 160), (200, 512, 1024), (17, 130, 72), (64, 1024, 3072),
-                                    (33, 257, 2048), (300, 384, 136), (1, 151936, 64), (2048, 1024, 1024)])
-def test_gemm_bfloat16(kernels, impl, M, N, K_):
+                                    (33, 257, 2048), (300, 384, 136), (1, 151936, 64), (2048, 1024, 1024),
+                                    (130, 4096, 4096), (200, 1024, 12288), (256, 5120, 5120), (96, 40, 8)])
+def test_gemm_bfloat16(kernels, M, N, K_):
     K = kernels("bfloat16")
     x, w = _randn(M, K_, seed=72).bfloat16(), _randn(N, K_, seed=73).bfloat16()
-    old, K.gemm_impl = K.gemm_impl, impl
-    try:
-        out = K.gemm(x.cuda(), w.cuda())
-        torch.cuda.synchronize()
-        assert K.gemm_status() == 0, "a bounded wait inside the kernel ran out"
-        assert out.dtype == torch.float32 and out.shape[1:] == (M, N)
-        ref = x.double() @ w.double().T
-        # products of bfloat16 values are exact in 32-bit; only the accumulation rounds
-        assert helpers.rel_err(out.sum(0), ref) < 2e-5
-        if impl == "tcgen05" and M > 1:
-            # a token's partial sums do not depend on what else is in the batch (same split of K)
-            one = K.gemm(x[M // 2:M // 2 + 1].contiguous().cuda(), w.cuda())
-            if one.shape[0] == out.shape[0]:
-                assert torch.equal(one[:, 0], out[:, M // 2])
-    finally:
-        K.gemm_impl = old
+    xd, wd = x.cuda(), w.cuda()
+    out = K.gemm(xd, wd)
+    torch.cuda.synchronize()
+    assert K.gemm_status() == 0, "a bounded wait inside the kernel ran out"
+    assert out.dtype == torch.float32 and out.shape == (1, M, N)
+    ref = x.double() @ w.double().T
+    # products of bfloat16 values are exact in 32-bit; only the accumulation rounds
+    assert helpers.rel_err(out[0], ref) < 2e-5
+    # a token's product is the same bits whatever else is in the step and however many tokens it has
+    for m in CUTS:
+        if m < M:
+            assert torch.equal(K.gemm_store(xd[:m].contiguous(), wd), out[0, :m]), f"the first {m} of {M} tokens alone"
+    mid = K.gemm_store(xd[M // 2:M // 2 + 1].contiguous(), wd)
+    assert torch.equal(mid[0], out[0, M // 2]), "a row alone"
+
+
+def test_a_product_element_is_one_chain_whatever_the_instruction(kernels):
+    """What the kernels rest on, asked of the hardware: an element of a tcgen05 product has the same
+    bits for every shape of the instruction, whatever its neighbours hold, and whichever operand
+    carries the tokens; a sum of partial chains does not have them."""
+    K = kernels("bfloat16")
+    Kd = 3072
+    x = (_randn(600, Kd, seed=170)).bfloat16().cuda()
+    w = (_randn(520, Kd, seed=171, scale=0.05)).bfloat16().cuda()
+    full = K.gemm_store(x, w)                                  # 600 tokens: 128 features on the lanes, 128/256 tokens a tile
+    # neighbours: other rows of the operand replaced
+    x2 = x[:16].clone()
+    x2[4:] = 7.0
+    assert torch.equal(K.gemm_store(x2, w)[3], full[3])
+    # roles exchanged: (w . x^T)^T
+    for a, b in ((x[:512], w[:512]), (x[:8], w[:512]), (x[:300], w[:40])):
+        a, b = a.contiguous(), b.contiguous()
+        assert torch.equal(K.gemm_store(a, b), K.gemm_store(b, a).T.contiguous())
+    # two half chains added differ from the one chain somewhere (else splitting the inner axis would be free)
+    halves = K.gemm_store(x[:64, :Kd // 2].contiguous(), w[:, :Kd // 2].contiguous()) + \
+        K.gemm_store(x[:64, Kd // 2:].contiguous(), w[:, Kd // 2:].contiguous())
+    assert not torch.equal(halves, full[:64]) and helpers.rel_err(halves, full[:64]) < 1e-5
+    assert K.gemm_status() == 0
 
 
 @pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (8, 1024, 2048), (64, 1024, 3072), (200, 512, 1024), (300, 384, 136),
-                                    (2048, 1024, 1024), (5, 151936, 64), (1030, 4096, 192), (700, 16000, 72)])
+                                    (2048, 1024, 1024), (5, 151936, 64), (1030, 4096, 192), (700, 16000, 72),
+                                    (130, 4096, 4096), (8, 131, 80)])
 def test_gemm_fused_store_and_residual(kernels, M, N, K_):
     K = kernels("bfloat16")
     x, w = _randn(M, K_, seed=74).bfloat16(), _randn(N, K_, seed=75).bfloat16()
     ref = x.double() @ w.double().T
-    for _ in range(2):                                    # twice: the tile counters must be back at zero
+    for _ in range(2):
         out = K.gemm_store(x.cuda(), w.cuda())
         assert out.shape == (M, N) and helpers.rel_err(out, ref) < 2e-5
     h0 = _randn(M, N, seed=76, scale=3.0).float()
     h = h0.clone().cuda()
     K.gemm_residual(x.cuda(), w.cuda(), h)
     assert helpers.rel_err(h, h0.double() + ref) < 2e-5
-    # the fused result is the partial sums added in ascending order: the same bits
-    parts = K.gemm(x.cuda(), w.cuda())
-    acc = torch.zeros_like(out)
-    for p_ in parts:
-        acc += p_
-    assert torch.equal(acc, out)
+    assert torch.equal(h, h0.cuda() + out), "the residual epilogue adds the product's bits to the stream once"
+    for m in CUTS:
+        if m < M:
+            hm = h0[:m].clone().cuda()
+            K.gemm_residual(x[:m].contiguous().cuda(), w.cuda(), hm)
+            assert torch.equal(hm, h[:m]), f"the first {m} of {M} tokens alone"
     torch.cuda.synchronize()
     assert K.gemm_status() == 0
 
@@ -435,48 +481,63 @@ def test_gemm_fused_swiglu(kernels, M, inter, K_):
         g, u = x.double() @ gate.double().T, x.double() @ up.double().T
         assert y.shape == (M, inter) and helpers.rel_err(y, g * torch.sigmoid(g) * u) < KTOL["bfloat16"]
     unfused = K.swiglu(K.gemm(x.cuda(), torch.cat([gate, up]).cuda()))
-    assert torch.equal(unfused, y), "fused and separate kernels add the same partial sums in the same order"
+    assert torch.equal(unfused, y), "fused and separate kernels apply one formula to the same products"
+    for m in CUTS:
+        if m < M:
+            assert torch.equal(K.gemm_swiglu(x[:m].contiguous().cuda(), tiled, inter), y[:m]), f"the first {m} of {M} tokens alone"
     assert torch.equal(K.swiglu(K.gemm(x.cuda(), tiled), tiled_inter=inter), y), "the tiled layout read by the separate kernel"
 
 
-@pytest.mark.parametrize("M,n_q,n_kv,hd,hidden", [(3, 6, 2, 32, 96), (70, 4, 2, 16, 64), (9, 16, 8, 128, 1024),
+@pytest.mark.parametrize("M,n_q,n_kv,hd,hidden", [(3, 6, 2, 32, 96), (9, 16, 8, 128, 1024),
                                                   (300, 8, 2, 128, 160), (64, 2, 1, 64, 72), (1030, 24, 4, 128, 192),
-                                                  (520, 40, 12, 64, 136), (300, 6, 2, 32, 96), (260, 3, 1, 16, 64)])
+                                                  (520, 40, 12, 64, 136), (300, 6, 2, 32, 96), (130, 32, 8, 128, 4096)])
 def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, hidden):
     K = kernels("bfloat16")
-    starts, lens = [5, 64], [M // 2, M - M // 2]
-    if lens[0] == 0:
-        starts, lens = [5], [M]
+    x_all = _randn(M, hidden, seed=80).bfloat16().cuda()
+    w = _randn((n_q + 2 * n_kv) * hd, hidden, seed=81, scale=0.2).bfloat16().cuda()
+    gq, gk = (1 + _randn(hd, seed=82, scale=0.3)).float().cuda(), (1 + _randn(hd, seed=83, scale=0.3)).float().cuda()
+    inv = 3e4 ** (-2.0 * torch.arange(0, hd // 2, dtype=torch.float64) / hd)
 
-    def run(fused, by_dim=True):
-        cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, 64 * 32, torch.bfloat16, "cuda:0", max_seqs=4)
+    def run(fused, m=M, by_dim=True, split=True):
+        """The first ``m`` tokens, as two sequences (``split``) or one, starting at positions 5 and 64."""
+        starts, lens = ([5, 64], [m // 2, m - m // 2]) if split and m >= 2 else ([5], [m])
+        cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, 64 * 40, torch.bfloat16, "cuda:0", max_seqs=4)
         slots = [cache.alloc_slot() for _ in lens]
         cache.reserve([(s_, st + L) for s_, st, L in zip(slots, starts, lens)]); cache.flush()
         packed, n, q_lens = pack_step_host(slots, starts, [[0] * L for L in lens])
         ctx = context_from_packed(packed.cuda(), n, slots, q_lens, starts)
-        x = _randn(M, hidden, seed=80).bfloat16().cuda()
-        w = _randn((n_q + 2 * n_kv) * hd, hidden, seed=81, scale=0.2).bfloat16().cuda()
-        gq, gk = (1 + _randn(hd, seed=82, scale=0.3)).float().cuda(), (1 + _randn(hd, seed=83, scale=0.3)).float().cuda()
-        inv = 3e4 ** (-2.0 * torch.arange(0, hd // 2, dtype=torch.float64) / hd)
         cs = K.rope_table(ctx.positions, inv.cuda())
         if not by_dim:
             cs.by_dim = None                               # the table by token only, as another position encoding gives it
         kv = cache.view(0)
+        x = x_all[:m].contiguous()
         if fused:
             q, kn, vn = K.gemm_qkv(x, w, n_q, n_kv, hd, gq, gk, 1e-5, cs, ctx, kv, keep_new=True)
         else:
             q, kn, vn = K.qkv_finish(K.gemm(x, w), n_q, n_kv, hd, gq, gk, 1e-5, cs, ctx, kv, keep_new=True)
         torch.cuda.synchronize()
-        return q, kn, vn, kv.k.clone(), kv.v.clone()
+        # the cache rows of the tokens, gathered in token order
+        rows_k, rows_v = [], []
+        for s_, st, L in zip(slots, starts, lens):
+            for pos in range(st, st + L):
+                page = int(kv.table[s_, pos // 64])
+                rows_k.append(kv.k[page, :, pos % 64]); rows_v.append(kv.v[page, :, pos % 64])
+        return q, kn, vn, torch.stack(rows_k), torch.stack(rows_v)
     a, b = run(True), run(False)
-    for t_a, t_b, name in zip(a, b, ("q", "k_new", "v_new", "cache k", "cache v")):
-        # the same numbers; a row's sum of squares may be added in another order (four elements per
-        # lane in the separate kernel and in the cluster path, strided pairs in the tile epilogues)
+    names = ("q", "k_new", "v_new", "cache k", "cache v")
+    for t_a, t_b, name in zip(a, b, names):
+        # the same numbers; a head's sum of squares is added in another order by the separate kernel
         assert helpers.rel_err(t_a, t_b) < KTOL["bfloat16"], name
-        if M <= 64 and 128 % hd == 0:
-            assert torch.equal(t_a, t_b), name + ": up to 64 tokens both paths finish rows the same way"
-    if M > 256:
-        for t_a, t_c, name in zip(a, run(True, by_dim=False), ("q", "k_new", "v_new", "cache k", "cache v")):
+    assert torch.equal(a[1], a[3]) and torch.equal(a[2], a[4]), "what goes to the cache is what goes to the packed buffers"
+    # one sequence of the same tokens at positions 5 ..: the bits of a token do not depend on how many tokens the step has
+    whole = run(True, split=False)
+    for m in CUTS:
+        if m < M:
+            part = run(True, m=m, split=False)
+            for t_w, t_p, name in zip(whole, part, names):
+                assert torch.equal(t_w[:m], t_p), f"{name}: the first {m} of {M} tokens alone"
+    if M > 128:
+        for t_a, t_c, name in zip(a, run(True, by_dim=False), names):
             assert torch.equal(t_a, t_c), name + ": the table read by dim or by token gives other bits"
     assert K.gemm_status() == 0
 
@@ -514,3 +575,8 @@ def test_sizes_the_kernels_cannot_take_are_refused(kernels):
         K.swiglu(torch.zeros(1, 4, 8, device="cuda", dtype=torch.bfloat16))
     with pytest.raises(KernelError, match="rows"):
         K.gemm(torch.zeros(2, 8, device="cuda", dtype=torch.bfloat16), torch.zeros(4, 16, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(KernelError, match="multiple of 8"):
+        K.gemm(torch.zeros(2, 12, device="cuda", dtype=torch.bfloat16), torch.zeros(4, 12, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(KernelError, match="head_dim"):
+        K.gemm_qkv(torch.zeros(1, 64, device="cuda", dtype=torch.bfloat16), torch.zeros(48, 64, device="cuda", dtype=torch.bfloat16),
+                   1, 1, 16, None, None, 1e-6, None, None, None, False)

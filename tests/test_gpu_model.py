@@ -116,9 +116,9 @@ def test_unequal_batches_one_after_another_reusing_slots(loaded, name, dtype):
     _check_clean(lm)
 
 
-@pytest.mark.parametrize("dtype", ["float32"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
-def test_32_bit_logits_are_the_same_bits_however_the_tokens_are_cut(loaded, name, dtype):
+def test_logits_are_the_same_bits_however_the_tokens_are_cut(loaded, name, dtype):
     lm, cfg, w = loaded(name, dtype)
     eng = lm.engine
     lens = [70, 9, 131, 33]
