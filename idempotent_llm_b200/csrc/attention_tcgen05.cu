@@ -45,6 +45,19 @@
 
 __device__ int g_attn_tc_error = 0;
 
+// -DIDM_TRACE: block (0, 0) leaves nanosecond stamps of its stages (a measuring aid, compiled out otherwise)
+#if defined(IDM_TRACE)
+__device__ unsigned long long g_attn_trace[64];
+__device__ __forceinline__ void attn_stamp(int i) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && i < 64) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); g_attn_trace[i] = t; }
+}
+extern "C" int idm_attention_tc_trace_read(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(unsigned long long) * 64);
+}
+#else
+__device__ __forceinline__ void attn_stamp(int) {}
+#endif
+
 struct AttnTcArgs {
     T* out;
     const int* tile_seq; const int* tile_start;
@@ -55,7 +68,7 @@ struct AttnTcArgs {
     float scale_log2;
     int run_blocks;                                    // key blocks of a run
     int max_runs;                                      // > 0: every run has a block of its own (grid.x = head groups x max_runs); 0: one block walks a tile's runs
-    int rows_cap;                                      // runs through scratch: rows of a tile the scratch holds
+    int rows_cap;                                      // the most rows any tile of the step has: what is fetched of q, and what the scratch holds of a run
     int* counters;                                     // [n_tiles * head groups] arrivals, zero between launches
     float* parts;                                      // runs through scratch: [n_tiles * head groups, max_runs] of rows_cap * (HD + 2) floats;
                                                        // one block per tile: [n_tiles * head groups] of 128 * HD floats (the context so far)
@@ -128,6 +141,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
+    if (threadIdx.x == 0) attn_stamp(0);                         // block started
 
     // blocks start in this order: all head groups (and runs) of the longest tile first.  What is read
     // here was written before the step began, not by the kernel before this one.
@@ -170,29 +184,44 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_o = tmem + 128;                          // S buffers at columns 0 and 64, O from 128
     pdl_wait();                                                  // set-up done; now the previous kernel's results
+    if (threadIdx.x == 0) attn_stamp(1);                         // set-up done, the kernel before too
 
     // from here on b counts this block's own key blocks (buffers and barrier phases go by it); the block's
     // place among the sequence's keys is b_first + b, and a run starts wherever that is a multiple of R
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
+        // (the whole warp walks the loop: its lanes fetch the page numbers of 32 key blocks at a time, so that
+        // no request waits for a look-up of its own; lane 0 issues the requests)
         if (lane == 0) {
-            mbar_expect_tx(q_full, S::Q_BYTES);
+            // (only the rows that some tile of the step has are fetched; the rest of the tile is whatever was there,
+            // makes rows of scores nobody reads, and gets p = 0)
+            mbar_expect_tx(q_full, (uint32_t)(HT * a.rows_cap * 128));
             for (int h = 0; h < HT; ++h)
                 tma_load_3d(base + S::Q_OFF + h * AP_BM * 128, &map_q, h * 64, head0, tok0, q_full);
-            const int slot = a.slots[seq];
-            for (int b = 0; b < nb; ++b) {
-                const int page = a.table[(size_t)slot * a.table_stride + b_first + b];
-                const int row = (page * a.n_kv + g) * IDM_PAGE;
-                const int vb = b & 1;                            // this block's key and value buffers
-                if (b >= 2 && !mbar_wait(k_empty(vb), ((b >> 1) - 1) & 1, abort_flag, &g_attn_tc_error)) break;
-                mbar_expect_tx(k_full(vb), S::K_BYTES);
-                for (int h = 0; h < HT; ++h)
-                    tma_load_2d(base + S::K_OFF + vb * S::K_BYTES + h * AP_BN * 128, &map_k, h * 64, row, k_full(vb));
-                if (b >= 2 && !mbar_wait(v_empty(vb), ((b >> 1) - 1) & 1, abort_flag, &g_attn_tc_error)) break;
-                mbar_expect_tx(v_full(vb), S::V_BYTES);
-                for (int h = 0; h < HT; ++h)
-                    tma_load_2d(base + S::V_OFF + vb * S::V_BYTES + h * AP_BN * 128, &map_v, h * 64, row, v_full(vb));
+        }
+        const int* pages = a.table + (size_t)a.slots[seq] * a.table_stride + b_first;
+        int my_page = 0;
+        for (int b = 0; b < nb; ++b) {
+            if ((b & 31) == 0) my_page = b + lane < nb ? pages[b + lane] : 0;
+            const int page = __shfl_sync(0xffffffffu, my_page, b & 31);
+            const int row = (page * a.n_kv + g) * IDM_PAGE;
+            const int vb = b & 1;                                // this block's key and value buffers
+            bool ok = true;
+            if (lane == 0) {
+                ok = b < 2 || mbar_wait(k_empty(vb), ((b >> 1) - 1) & 1, abort_flag, &g_attn_tc_error);
+                if (ok) {
+                    mbar_expect_tx(k_full(vb), S::K_BYTES);
+                    for (int h = 0; h < HT; ++h)
+                        tma_load_2d(base + S::K_OFF + vb * S::K_BYTES + h * AP_BN * 128, &map_k, h * 64, row, k_full(vb));
+                    ok = b < 2 || mbar_wait(v_empty(vb), ((b >> 1) - 1) & 1, abort_flag, &g_attn_tc_error);
+                }
+                if (ok) {
+                    mbar_expect_tx(v_full(vb), S::V_BYTES);
+                    for (int h = 0; h < HT; ++h)
+                        tma_load_2d(base + S::V_OFF + vb * S::V_BYTES + h * AP_BN * 128, &map_v, h * 64, row, v_full(vb));
+                }
             }
+            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
         }
     } else if (warp == 5) {
         // -------------------------------------------------------------------- MMA issuer
@@ -259,6 +288,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int b = 0; b < nb && ok; ++b) {
             ok = mbar_wait(s_full(b & 1), (b >> 1) & 1, abort_flag, &g_attn_tc_error);
             if (!ok) break;
+            if (threadIdx.x == 0) attn_stamp(2 + 2 * b);         // scores of block b are there
             tc_fence_after();
             const bool run_start = b > 0 && (b_first + b) % R == 0;
             float m_prev = 0.f, l_prev = 0.f;
@@ -327,18 +357,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         fold_coeffs(M_tot, L_tot, m_prev, l_prev, a_, b_);
                         float4* mine = reinterpret_cast<float4*>(tot);
 #pragma unroll 1
-                        for (int c = 0; c < HD; c += 16) {
-                            float o[16];
-                            tc_ld16(tmem_o + lane_base + c, o);
+                        for (int c = 0; c < HD; c += 32) {           // 32 columns and their old values are asked for together
+                            uint32_t o[32];
+                            float4 t[8];
+                            tc_ld16_issue(tmem_o + lane_base + c, o);
+                            tc_ld16_issue(tmem_o + lane_base + c + 16, o + 16);
+#pragma unroll
+                            for (int k = 0; k < 8; ++k)
+                                t[k] = (row_live && !first) ? mine[(c / 4 + k) * AP_BM + r] : make_float4(0.f, 0.f, 0.f, 0.f);
+                            tc_ld_wait();
                             if (row_live) {
 #pragma unroll
-                                for (int k = 0; k < 4; ++k) {
-                                    float4* dst = mine + (c / 4 + k) * AP_BM + r;
-                                    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-                                    if (!first) t = *dst;
-                                    t.x = fold_value(t.x, a_, o[4 * k], b_); t.y = fold_value(t.y, a_, o[4 * k + 1], b_);
-                                    t.z = fold_value(t.z, a_, o[4 * k + 2], b_); t.w = fold_value(t.w, a_, o[4 * k + 3], b_);
-                                    *dst = t;
+                                for (int k = 0; k < 8; ++k) {
+                                    t[k].x = fold_value(t[k].x, a_, __uint_as_float(o[4 * k]), b_);
+                                    t[k].y = fold_value(t[k].y, a_, __uint_as_float(o[4 * k + 1]), b_);
+                                    t[k].z = fold_value(t[k].z, a_, __uint_as_float(o[4 * k + 2]), b_);
+                                    t[k].w = fold_value(t[k].w, a_, __uint_as_float(o[4 * k + 3]), b_);
+                                    mine[(c / 4 + k) * AP_BM + r] = t[k];
                                 }
                             }
                         }
@@ -381,9 +416,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
+            if (threadIdx.x == 0) attn_stamp(3 + 2 * b);         // p of block b handed over
         }
         if (ok) ok = mbar_wait(o_done, (nb - 1) & 1, abort_flag, &g_attn_tc_error);
         ok = __all_sync(0xffffffffu, ok);                          // (one answer per warp for what follows)
+        if (threadIdx.x == 0) attn_stamp(40);                    // the last context is complete
         T* orow = a.out + ((size_t)(tok0 + (r >> gs)) * a.n_q + head0 + (r & (gp - 1))) * HD;
         if (through_scratch && n_runs > 1) {
             // This run's result goes to its place among the tile's; the block that comes last folds them
@@ -396,14 +433,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (ok && warp_live) {
                 tc_fence_after();
                 float4* mine = reinterpret_cast<float4*>(part0 + (size_t)run * part_floats);
+                // (64 columns are asked for before the first is waited for)
 #pragma unroll 1
-                for (int c = 0; c < HD; c += 16) {
-                    float o[16];
-                    tc_ld16(tmem_o + lane_base + c, o);
+                for (int c = 0; c < HD; c += 64) {
+                    uint32_t o[64];
+#pragma unroll
+                    for (int u = 0; u < 64; u += 16) tc_ld16_issue(tmem_o + lane_base + c + u, o + u);
+                    tc_ld_wait();
                     if (r < cap) {
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            mine[(c / 4 + k) * cap + r] = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
+                        for (int k = 0; k < 16; ++k)
+                            mine[(c / 4 + k) * cap + r] = make_float4(__uint_as_float(o[4 * k]), __uint_as_float(o[4 * k + 1]),
+                                                                      __uint_as_float(o[4 * k + 2]), __uint_as_float(o[4 * k + 3]));
                     }
                 }
                 if (r < cap) reinterpret_cast<float2*>(mine + (HD / 4) * cap)[r] = make_float2(m_ref, l);
@@ -418,6 +459,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 *last_flag = is_last;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 0) attn_stamp(41);                // this run's result is in scratch and counted
             if (*last_flag && ok) {
                 __threadfence();
                 // the block's 128 threads share the tile's (row, four dims) pieces; each folds its piece over the runs
@@ -426,14 +468,26 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     if (row >= rows_valid) continue;
                     float M = -INFINITY, L = 0.f;
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int i = 0; i < n_runs; ++i) {
-                        const float* pi = part0 + (size_t)i * part_floats;
-                        const float2 ml = __ldcg(reinterpret_cast<const float2*>(pi + (size_t)HD * cap) + row);
-                        const float4 o = __ldcg(reinterpret_cast<const float4*>(pi) + w);
-                        float a_, b_;
-                        fold_coeffs(M, L, ml.x, ml.y, a_, b_);
-                        acc.x = fold_value(acc.x, a_, o.x, b_); acc.y = fold_value(acc.y, a_, o.y, b_);
-                        acc.z = fold_value(acc.z, a_, o.z, b_); acc.w = fold_value(acc.w, a_, o.w, b_);
+                    for (int i0 = 0; i0 < n_runs; i0 += 8) {       // eight runs' loads are in flight together; the fold is a chain
+                        float2 ml[8];
+                        float4 o[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            if (i0 + u < n_runs) {
+                                const float* pi = part0 + (size_t)(i0 + u) * part_floats;
+                                ml[u] = __ldcg(reinterpret_cast<const float2*>(pi + (size_t)HD * cap) + row);
+                                o[u] = __ldcg(reinterpret_cast<const float4*>(pi) + w);
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            if (i0 + u < n_runs) {
+                                float a_, b_;
+                                fold_coeffs(M, L, ml[u].x, ml[u].y, a_, b_);
+                                acc.x = fold_value(acc.x, a_, o[u].x, b_); acc.y = fold_value(acc.y, a_, o[u].y, b_);
+                                acc.z = fold_value(acc.z, a_, o[u].z, b_); acc.w = fold_value(acc.w, a_, o[u].w, b_);
+                            }
+                        }
                     }
                     const float inv = __fdiv_rn(1.0f, L);
                     T* dst = a.out + ((size_t)(tok0 + (row >> gs)) * a.n_q + head0 + (row & (gp - 1))) * HD + c4 * 4;
@@ -468,6 +522,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
         }
     }
+    if (threadIdx.x == 0) attn_stamp(42);                        // done
     tc_fence_before();
     __syncthreads();
     if (warp == 5) tmem_dealloc(tmem, AP_TMEM_COLS);
@@ -514,8 +569,8 @@ extern "C" long long idm_attention_tc_scratch_floats(int n_tiles, int n_q, int n
 
 // q [n_tokens, n_q, hd]; out [n_tokens, n_q * hd]; the cache entry's pools [n_pages, n_kv, 64, hd];
 // tiles: (sequence, first token of the tile within the sequence's tokens of this step), a tile being
-// 128 / heads_per_tile tokens, longest first.  max_runs > 0: every run of `run_blocks` key blocks is a
-// block of its own and results meet in scratch (few rows per tile: at most rows_cap <= 32); max_runs == 0:
+// 128 / heads_per_tile tokens, longest first; rows_cap: the most rows (tokens x heads_per_tile) any tile has.  max_runs > 0: every run of `run_blocks` key blocks is a
+// block of its own and results meet in scratch; max_runs == 0:
 // one block per tile and head group (`scratch` may be null if no tile has more than run_blocks key blocks).
 extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, const void* v_pool, int n_pages,
                                 const int* table, int table_stride, const int* tile_seq, const int* tile_start,
@@ -531,14 +586,15 @@ extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, co
     int gs = 0;
     while ((1 << gs) < gp) ++gs;
     const long long groups = (long long)n_tiles * (n_q / gp);
-    IDM_REQUIRE(max_runs == 0 || (scratch != nullptr && rows_cap >= 1 && rows_cap <= AP_BM && groups <= AP_COUNTERS),
-                "attention_tc: runs through scratch need scratch, 1 <= rows_cap <= %d (got %d) and at most %d tiles x head "
-                "groups (got %lld)", AP_BM, rows_cap, AP_COUNTERS, groups);
+    IDM_REQUIRE(rows_cap >= gp && rows_cap <= AP_BM && rows_cap % gp == 0,
+                "attention_tc: rows_cap=%d must be a multiple of %d (the q-heads of a tile) up to %d", rows_cap, gp, AP_BM);
+    IDM_REQUIRE(max_runs == 0 || (scratch != nullptr && groups <= AP_COUNTERS),
+                "attention_tc: runs through scratch need scratch and at most %d tiles x head groups (got %lld)", AP_COUNTERS, groups);
     CUtensorMap mq, mk, mv;
     {
         cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)n_q, (cuuint64_t)n_tokens};
         cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)n_q * hd * 2};
-        cuuint32_t box[3] = {64, (cuuint32_t)gp, (cuuint32_t)(AP_BM / gp)};
+        cuuint32_t box[3] = {64, (cuuint32_t)gp, (cuuint32_t)(rows_cap / gp)};
         const int r = tc_make_map_bf16(&mq, q, 3, dims, strides, box);
         IDM_REQUIRE(r == 0, "attention_tc: tensor map for q failed (%d)", r);
     }

@@ -15,6 +15,8 @@
 // why nothing is split.)
 //
 // Three kernels.
+//   up to 128 tokens,   gemm_wide_kernel: 128 features on the lanes, the tokens along the columns, a block per 128
+//   >= 16384 features   features (the lm_head).
 //   up to 128 tokens    gemm_small_kernel: the MMA's M axis carries the step's tokens (an accumulator
 //                       lane is a token), its N axis a narrow slice of 16 to 128 output features, so
 //                       that even a matrix of 1024 rows is spread over 64 blocks; each block streams
@@ -44,6 +46,20 @@
 #define GT_UMMA_K 16
 
 __device__ int g_gemm_error = 0;
+
+// -DIDM_TRACE: block 0 of the kernel for few tokens leaves nanosecond stamps of its stages (a measuring aid,
+// compiled out otherwise)
+#if defined(IDM_TRACE)
+__device__ unsigned long long g_gemm_trace[64];
+__device__ __forceinline__ void trace_stamp(int i) {
+    if (blockIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); g_gemm_trace[i] = t; }
+}
+extern "C" int idm_gemm_trace_read(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned long long) * 64);
+}
+#else
+__device__ __forceinline__ void trace_stamp(int) {}
+#endif
 
 enum { EPI_STORE = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
 
@@ -539,17 +555,19 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const
 // `tbox` are fetched; what the other rows of the operand hold is whatever lies behind the slot in
 // shared memory, and goes into accumulator lanes nobody reads), `bf` output features along its
 // columns.  A block owns features [bf * blockIdx.x, + bf) and walks the whole inner axis: one chain
-// per element.  Warp 4 issues the TMA loads -- the weight slices of the first `stages` k-blocks before
-// the wait on the kernel before (no kernel writes weights), the activations after it; warp 5 issues
-// the MMAs; warps 0-3 read the accumulator (thread = token) and run the epilogue.
+// per element.  Warp 4 issues the TMA loads, `gk` k-blocks per request and barrier (a three-dimensional
+// view of the matrices: k within a block, row, k-block) -- the weight slices of the first `stages`
+// groups before the wait on the kernel before (no kernel writes weights), the activations after it;
+// warp 5 issues the MMAs (a chain of K / 16 instructions of ~46 cycles each, whatever their width: the
+// floor of this kernel); warps 0-3 read the accumulator (thread = token) and run the epilogue.
 #define GS_THREADS 192
-#define GS_MAX_STAGES 48
+#define GS_MAX_STAGES 16
 #define GS_BAR_BYTES 1024
 
-__host__ __device__ inline uint32_t gs_data_bytes(int tbox, int bf, int stages) {
+__host__ __device__ inline uint32_t gs_data_bytes(int tbox, int bf, int gk, int stages) {
     const uint32_t a_slot = (uint32_t)tbox * 128u, b_slot = (uint32_t)bf * 128u;
-    uint32_t data = (uint32_t)stages * (a_slot + b_slot);
-    const uint32_t reach = (uint32_t)(stages - 1) * a_slot + GT_BM * 128u;      // the MMA reads 128 rows from every A slot
+    uint32_t data = (uint32_t)(stages * gk) * (a_slot + b_slot);
+    const uint32_t reach = (uint32_t)(stages * gk - 1) * a_slot + GT_BM * 128u;   // the MMA reads 128 rows from every A slot
     if (reach > data) data = reach;
     return (data + 1023u) & ~1023u;
 }
@@ -558,15 +576,15 @@ template <int EPI>
 __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 const GemmEpi e, int n_tokens, int n_features,
-                                                                int kb_total, int bf, int tbox, int stages,
-                                                                int tmem_cols) {
+                                                                int kb_total, int bf, int tbox, int gk, int grouped,
+                                                                int stages, int tmem_cols) {
     pdl_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t a_slot = (uint32_t)tbox * 128u, b_slot = (uint32_t)bf * 128u;
-    const uint32_t a_base = base, b_base = base + (uint32_t)stages * a_slot;
-    const uint32_t bar_off = gs_data_bytes(tbox, bf, stages);
+    const uint32_t a_slot = (uint32_t)tbox * 128u, b_slot = (uint32_t)bf * 128u;      // one k-block of each operand
+    const uint32_t a_base = base, b_base = base + (uint32_t)(stages * gk) * a_slot;
+    const uint32_t bar_off = gs_data_bytes(tbox, bf, gk, stages);
     const uint32_t bars = base + bar_off;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (GS_MAX_STAGES + s); };
@@ -576,6 +594,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int f0 = blockIdx.x * bf;
+    const int n_groups = (kb_total + gk - 1) / gk;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -588,42 +607,74 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = *tmem_slot;
+    if (threadIdx.x == 0) trace_stamp(0);                        // set-up done
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            const int early = min(kb_total, stages);
-            for (int i = 0; i < early; ++i) {
-                mbar_expect_tx(full_bar(i), a_slot + b_slot);
-                tma_load_2d(b_base + i * b_slot, &map_w, i * GT_BK, f0, full_bar(i));
+            // a group's loads: one request per operand (grouped: the maps are three-dimensional), or one per k-block
+            auto load_w = [&](int gi, int s) {
+                const uint32_t dst = b_base + (uint32_t)(s * gk) * b_slot;
+                if (grouped) { tma_load_3d(dst, &map_w, 0, f0, gi * gk, full_bar(s)); return; }
+                for (int k = 0; k < gk && gi * gk + k < kb_total; ++k)
+                    tma_load_2d(dst + k * b_slot, &map_w, (gi * gk + k) * GT_BK, f0, full_bar(s));
+            };
+            auto load_x = [&](int gi, int s) {
+                const uint32_t dst = a_base + (uint32_t)(s * gk) * a_slot;
+                if (grouped) { tma_load_3d(dst, &map_x, 0, 0, gi * gk, full_bar(s)); return; }
+                for (int k = 0; k < gk && gi * gk + k < kb_total; ++k)
+                    tma_load_2d(dst + k * a_slot, &map_x, (gi * gk + k) * GT_BK, 0, full_bar(s));
+            };
+            // (a grouped request always brings gk k-blocks: those past the end come as zeros)
+            auto group_bytes = [&](int gi) { return (uint32_t)(grouped ? gk : min(gk, kb_total - gi * gk)) * (a_slot + b_slot); };
+            const int early = min(n_groups, stages);
+            for (int gi = 0; gi < early; ++gi) {
+                mbar_expect_tx(full_bar(gi), group_bytes(gi));
+                load_w(gi, gi);
             }
+            trace_stamp(1);                                      // early weight loads issued
             pdl_wait();
-            for (int i = 0; i < early; ++i) tma_load_2d(a_base + i * a_slot, &map_x, i * GT_BK, 0, full_bar(i));
-            for (int i = early; i < kb_total; ++i) {
-                const int s = i % stages;
-                if (!mbar_wait(empty_bar(s), ((i / stages) & 1) ^ 1, abort_flag, &g_gemm_error)) break;
-                mbar_expect_tx(full_bar(s), a_slot + b_slot);
-                tma_load_2d(b_base + s * b_slot, &map_w, i * GT_BK, f0, full_bar(s));
-                tma_load_2d(a_base + s * a_slot, &map_x, i * GT_BK, 0, full_bar(s));
+            trace_stamp(2);                                      // the kernel before is done
+            for (int gi = 0; gi < early; ++gi) load_x(gi, gi);
+            trace_stamp(3);                                      // early activation loads issued
+            int s = 0; uint32_t phase = 0;                       // the ring goes round: stage and the parity of its use
+            for (int gi = early; gi < n_groups; ++gi) {
+                if (!mbar_wait(empty_bar(s), phase, abort_flag, &g_gemm_error)) break;
+                mbar_expect_tx(full_bar(s), group_bytes(gi));
+                load_w(gi, s);
+                load_x(gi, s);
+                if (++s == stages) { s = 0; phase ^= 1; }
             }
+            trace_stamp(4);                                      // all loads issued
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(GT_BM, bf);
+            const uint64_t a_desc0 = umma_desc_kmajor(a_base), b_desc0 = umma_desc_kmajor(b_base);
+            const uint32_t a_step = a_slot >> 4, b_step = b_slot >> 4;     // descriptors count in 16 bytes
             bool ok = true;
-            for (int i = 0; i < kb_total && ok; ++i) {
-                const int s = i % stages;
-                ok = mbar_wait(full_bar(s), (i / stages) & 1, abort_flag, &g_gemm_error);
+            int s = 0; uint32_t phase = 0, acc = 0;
+            uint64_t a_desc = a_desc0, b_desc = b_desc0;
+            for (int gi = 0; gi < n_groups && ok; ++gi) {
+                ok = mbar_wait(full_bar(s), phase, abort_flag, &g_gemm_error);
                 if (!ok) break;
+                if (gi == 0) trace_stamp(5);                     // first operands landed
                 tc_fence_after();
-                const uint64_t a_desc = umma_desc_kmajor(a_base + s * a_slot), b_desc = umma_desc_kmajor(b_base + s * b_slot);
-#pragma unroll
-                for (int k = 0; k < GT_BK / GT_UMMA_K; ++k)
-                    tc_mma_bf16(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                tc_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+                const int nk = min(gk, kb_total - gi * gk);
+                uint64_t ad = a_desc, bd = b_desc;
+#pragma unroll 4
+                for (int k = 0; k < nk; ++k) {
+                    tc_mma_bf16_kblock(tmem_d, ad, bd, idesc, acc);
+                    acc = 1u;
+                    ad += a_step; bd += b_step;
+                }
+                if (gi + stages < n_groups) tc_commit(empty_bar(s));      // the stage is free once these MMAs have read it
+                a_desc += (uint64_t)gk * a_step; b_desc += (uint64_t)gk * b_step;
+                if (++s == stages) { s = 0; phase ^= 1; a_desc = a_desc0; b_desc = b_desc0; }
             }
             if (ok) tc_commit(accum_bar);         // the accumulator is complete once all MMAs are done
+            trace_stamp(6);                       // all MMAs issued
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 0-3): thread = token
@@ -643,6 +694,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
                 }
             }
             if (mbar_wait(accum_bar, 0, abort_flag, &g_gemm_error)) {
+                if (threadIdx.x == 0) trace_stamp(7);            // accumulator complete
                 tc_fence_after();
                 if (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
                     const bool vec = (n_features & 3) == 0;
@@ -723,10 +775,122 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
             }
         }
     }
+    if (threadIdx.x == 0) trace_stamp(8);                        // epilogue done
     tc_fence_before();
     __syncthreads();
     if (warp == 5) tmem_dealloc(tmem_d, (uint32_t)tmem_cols);
 }
+
+// ------------------------------------------------------- few tokens, very many features (the lm_head)
+// 128 output features on the accumulator's lanes, BN tokens along its columns, one block per 128 features,
+// the whole inner axis in one chain.  With some thousand feature tiles there is no lack of blocks, and
+// for one token the 32 lanes of a warp store 32 consecutive features: every thread of the four epilogue
+// warps has work, where the kernel above would leave all of it to the few threads that own a token.
+#define GW_THREADS 192
+template <int BN, int STAGES>
+struct WideSmem {
+    static constexpr int A_BYTES = GT_BM * GT_BK * 2;
+    static constexpr int B_BYTES = BN * GT_BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 256 + 1024;   // barriers; slack to align to 1024
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GW_THREADS) gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                               const __grid_constant__ CUtensorMap map_x,
+                                                               float* out, int n_tokens, int n_features, int kb_total) {
+    using S = WideSmem<BN, STAGES>;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    pdl_launch_dependents();
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + STAGES * S::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + STAGES * S::STAGE_BYTES + 8 * (2 * STAGES + 1));
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f0 = blockIdx.x * GT_BM, t0 = blockIdx.y * BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 5) tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *tmem_slot;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            // weights are written by no kernel: the first stages' tiles are fetched before the wait on the kernel before
+            const int early = min(kb_total, STAGES);
+            for (int i = 0; i < early; ++i) {
+                mbar_expect_tx(full_bar(i), S::STAGE_BYTES);
+                tma_load_2d(base + i * S::STAGE_BYTES, &map_w, i * GT_BK, f0, full_bar(i));
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(base + i * S::STAGE_BYTES + S::A_BYTES, &map_x, i * GT_BK, t0, full_bar(i));
+            int s = 0; uint32_t phase = 0;
+            for (int i = early; i < kb_total; ++i) {
+                if (!mbar_wait(empty_bar(s), phase, abort_flag, &g_gemm_error)) break;
+                mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+                const uint32_t a_dst = base + s * S::STAGE_BYTES;
+                tma_load_2d(a_dst, &map_w, i * GT_BK, f0, full_bar(s));
+                tma_load_2d(a_dst + S::A_BYTES, &map_x, i * GT_BK, t0, full_bar(s));
+                if (++s == STAGES) { s = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(GT_BM, BN);
+            bool ok = true;
+            int s = 0; uint32_t phase = 0;
+            for (int i = 0; i < kb_total && ok; ++i) {
+                ok = mbar_wait(full_bar(s), phase, abort_flag, &g_gemm_error);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = base + s * S::STAGE_BYTES;
+                tc_mma_bf16_kblock(tmem_d, umma_desc_kmajor(a_addr), umma_desc_kmajor(a_addr + S::A_BYTES), idesc, i > 0 ? 1u : 0u);
+                tc_commit(empty_bar(s));
+                if (++s == STAGES) { s = 0; phase ^= 1; }
+            }
+            if (ok) tc_commit(accum_bar);
+        }
+    } else {
+        pdl_wait();
+        if (mbar_wait(accum_bar, 0, abort_flag, &g_gemm_error)) {
+            tc_fence_after();
+            const int f = f0 + warp * 32 + lane;                   // feature = accumulator lane
+            const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (t0 + c0 >= n_tokens) break;                    // warp-uniform
+                float v[16];
+                tc_ld16(tmem_d + lane_base + (uint32_t)c0, v);
+                if (f < n_features) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c0 + j;
+                        if (t < n_tokens) out[(size_t)t * n_features + f] = v[j];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem_d, TMEM_COLS);
+}
+
+template <int BN, int STAGES>
+static int launch_wide(const void* x, const void* w, float* out, int M, int N, int K, cudaStream_t stream);
 
 // ------------------------------------------------------------------------------ host
 // a [rows, k] bfloat16 row-major matrix, tiles of [box_rows, 64], 128-byte swizzle, zero fill outside
@@ -736,6 +900,24 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int k, int box_
     cuuint32_t box[2] = {GT_BK, (cuuint32_t)box_rows};
     const int r = tc_make_map_bf16(map, ptr, 2, dims, strides, box);
     IDM_REQUIRE(r == 0, "gemm: cuTensorMapEncodeTiled failed with %d (rows=%d k=%d box=%d)", r, rows, k, box_rows);
+    return 0;
+}
+
+template <int BN, int STAGES>
+static int launch_wide(const void* x, const void* w, float* out, int M, int N, int K, cudaStream_t stream) {
+    using S = WideSmem<BN, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_wide_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        IDM_REQUIRE(err == cudaSuccess, "gemm: cannot get %d bytes of shared memory: %s", S::TOTAL, cudaGetErrorString(err));
+        configured = true;
+    }
+    CUtensorMap mw, mx;
+    if (make_map(&mw, w, N, K, GT_BM)) return 1;
+    if (make_map(&mx, x, M, K, BN)) return 1;
+    dim3 grid((N + GT_BM - 1) / GT_BM, (M + BN - 1) / BN);
+    idm_launch(gemm_wide_kernel<BN, STAGES>, grid, dim3(GW_THREADS), S::TOTAL, stream, mw, mx, out, M, N, (K + GT_BK - 1) / GT_BK);
+    IDM_LAUNCH_CHECK("gemm_wide");
     return 0;
 }
 
@@ -766,11 +948,25 @@ static int small_slice(int N, int tbox, int unit) {
     return best ? best : unit;
 }
 
-static int g_small_bf = 0, g_small_budget = 96 * 1024;
-// (for measurements: fix the slice width / the bytes of shared memory a block's ring may take)
-extern "C" void idm_gemm_set_small(int bf, int ring_bytes) {
+// The same matrix as [k within a k-block (64), row, k-block]: a box of [64, box_rows, box_kb] brings
+// box_kb k-blocks of box_rows rows with one request, each k-block's rows together in shared memory.
+// Only for inner sizes that are whole k-blocks (a row's last, partial block would run into the next row).
+static int make_map_grouped(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows, int box_kb) {
+    cuuint64_t dims[3] = {GT_BK, (cuuint64_t)rows, (cuuint64_t)(k / GT_BK)};
+    cuuint64_t strides[2] = {(cuuint64_t)k * 2, GT_BK * 2};
+    cuuint32_t box[3] = {GT_BK, (cuuint32_t)box_rows, (cuuint32_t)box_kb};
+    const int r = tc_make_map_bf16(map, ptr, 3, dims, strides, box);
+    IDM_REQUIRE(r == 0, "gemm: cuTensorMapEncodeTiled failed with %d (rows=%d k=%d box=%d x %d k-blocks)", r, rows, k, box_rows,
+                box_kb);
+    return 0;
+}
+
+static int g_small_bf = 0, g_small_budget = 200 * 1024, g_small_gk = 0;
+// (for measurements: fix the slice width / the bytes of shared memory a block's ring may take / k-blocks per request)
+extern "C" void idm_gemm_set_small(int bf, int ring_bytes, int gk) {
     g_small_bf = bf;
     if (ring_bytes > 0) g_small_budget = ring_bytes;
+    g_small_gk = gk;
 }
 
 template <int EPI>
@@ -781,14 +977,23 @@ static int launch_small(const void* x, const void* w, const GemmEpi& e, int M, i
     if (EPI == EPI_QKV) unit = e.q.hd < 16 ? 16 : e.q.hd;
     int bf = g_small_bf && g_small_bf % unit == 0 ? g_small_bf : small_slice(N, tbox, unit);
     if (EPI == EPI_QKV && bf < e.q.hd) bf = e.q.hd;
-    const int stage_bytes = (tbox + bf) * 128;
-    int stages = g_small_budget / stage_bytes;
-    if (stages < 4) stages = 4;
-    if (stages > kb_total) stages = kb_total;
+    const int kb_bytes = (tbox + bf) * 128;                       // one k-block of both operands
+    // k-blocks per request: about 32 KB, at most 8, and no more than a quarter of the inner axis
+    int gk = g_small_gk ? g_small_gk : 32 * 1024 / kb_bytes;
+    if (gk > 8) gk = 8;
+    if (gk > kb_total / 4) gk = kb_total / 4;
+    if (gk < 1) gk = 1;
+    const int grouped = (K % GT_BK == 0 && gk > 1) ? 1 : 0;
+    if (!grouped && K % GT_BK) gk = 1;
+    const int n_groups = (kb_total + gk - 1) / gk;
+    int stages = g_small_budget / (gk * kb_bytes);
+    if (stages < 2) stages = 2;
+    if (stages > n_groups) stages = n_groups;
     if (stages > GS_MAX_STAGES) stages = GS_MAX_STAGES;
     int tmem_cols = 32;
     while (tmem_cols < bf) tmem_cols *= 2;
-    const int smem = (int)gs_data_bytes(tbox, bf, stages) + GS_BAR_BYTES + 1024;      // + slack to align to 1024
+    const int smem = (int)gs_data_bytes(tbox, bf, gk, stages) + GS_BAR_BYTES + 1024;      // + slack to align to 1024
+    IDM_REQUIRE(smem <= 227 * 1024, "gemm: %d bytes of shared memory for %d tokens x %d features a block", smem, tbox, bf);
     static int configured = 0;
     if (smem > configured) {
         cudaError_t err = cudaFuncSetAttribute(gemm_small_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -796,10 +1001,15 @@ static int launch_small(const void* x, const void* w, const GemmEpi& e, int M, i
         configured = smem;
     }
     CUtensorMap mw, mx;
-    if (make_map(&mw, w, N, K, bf)) return 1;
-    if (make_map(&mx, x, M, K, tbox)) return 1;
+    if (grouped) {
+        if (make_map_grouped(&mw, w, N, K, bf, gk)) return 1;
+        if (make_map_grouped(&mx, x, M, K, tbox, gk)) return 1;
+    } else {
+        if (make_map(&mw, w, N, K, bf)) return 1;
+        if (make_map(&mx, x, M, K, tbox)) return 1;
+    }
     idm_launch(gemm_small_kernel<EPI>, dim3((N + bf - 1) / bf), dim3(GS_THREADS), (size_t)smem, stream, mw, mx, e, M, N,
-               kb_total, bf, tbox, stages, tmem_cols);
+               kb_total, bf, tbox, gk, grouped, stages, tmem_cols);
     IDM_LAUNCH_CHECK("gemm_small");
     return 0;
 }
@@ -807,6 +1017,9 @@ static int launch_small(const void* x, const void* w, const GemmEpi& e, int M, i
 // Up to how many tokens the kernel with the tokens on the lanes runs (at most 128: the lanes of the accumulator).
 static int g_gemm_small_max = 128;
 extern "C" void idm_gemm_set_small_max(int tokens) { g_gemm_small_max = tokens < 0 ? 0 : tokens > 128 ? 128 : tokens; }
+// From how many output features on a plain product of few tokens runs with the features on the lanes.
+static int g_gemm_wide_from = 16384;
+extern "C" void idm_gemm_set_wide_from(int features) { g_gemm_wide_from = features; }
 
 template <int EPI>
 static int gemm_any(const void* x, const void* w, GemmEpi e, int M, int N, int K, cudaStream_t stream) {
@@ -822,7 +1035,16 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, int M, int N, int K
         IDM_REQUIRE(on32(e.q.q_out) && on32(e.q.k_new) && on32(e.q.v_new) && on32(e.q.cache.k) && on32(e.q.cache.v) &&
                     on32(e.q.cs) && on32(e.q.gq) && on32(e.q.gk), "gemm_qkv: outputs, tables and norm weights must lie on 32-byte borders");
     }
-    if (M <= g_gemm_small_max) return launch_small<EPI>(x, w, e, M, N, K, stream);
+    if (M <= g_gemm_small_max) {
+        if (EPI == EPI_STORE && N >= g_gemm_wide_from) {
+            // some hundred feature tiles: features on the lanes, every epilogue thread at work
+            if (M <= 16) return launch_wide<16, 6>(x, w, e.out, M, N, K, stream);
+            if (M <= 32) return launch_wide<32, 6>(x, w, e.out, M, N, K, stream);
+            if (M <= 64) return launch_wide<64, 4>(x, w, e.out, M, N, K, stream);
+            return launch_wide<128, 3>(x, w, e.out, M, N, K, stream);
+        }
+        return launch_small<EPI>(x, w, e, M, N, K, stream);
+    }
     CUtensorMap mw, mx;
     if (EPI == EPI_QKV) {
         // many tokens: tokens on the accumulator's lanes, 256 features (whole heads) per tile

@@ -115,6 +115,23 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, ui
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// Four MMAs over one k-block of 64 (four steps of 16 k = 32 bytes = 2 descriptor units along the swizzled row),
+// in ascending k, as one piece of code: the issuing thread spends no instructions between them.
+__device__ __forceinline__ void tc_mma_bf16_kblock(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t accumulate_first) {
+    asm volatile("{\n\t.reg .pred p, q;\n\t.reg .b64 a, b;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "setp.eq.b32 q, 0, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+                 "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n\t"
+                 "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n\t"
+                 "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first) : "memory");
+}
+
 #define TC_REGS16(r) "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), \
                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
 // 16 / 32 consecutive 32-bit columns of this warp's 32 lanes (issue only; tc_ld_wait before use)

@@ -76,8 +76,9 @@ SIGNATURES = {
     "idm_attention_tc": (c_int, "ppppipippippppiiiifiiipp"),
     "idm_attention_tc_status": (c_int, ""),
     "idm_gemm_f32": (c_int, "pppiiip"),
-    "idm_gemm_set_small": (None, "ii"),
+    "idm_gemm_set_small": (None, "iii"),
     "idm_gemm_set_small_max": (None, "i"),
+    "idm_gemm_set_wide_from": (None, "i"),
     "idm_gemm_bf16": (c_int, "pppiiip"),
     "idm_gemm_bf16_residual": (c_int, "pppiiip"),
     "idm_gemm_bf16_swiglu": (c_int, "pppiiip"),
@@ -295,10 +296,11 @@ class Kernels:
         longest = -(-ctx.max_kv_len // self.page)
         max_runs = -(-longest // R)
         if through_scratch is None:
+            # every run a block of its own where a tile has few rows (single tokens above all): the runs'
+            # results are small then.  For whole tiles of a prompt the way through scratch was measured
+            # slower (2048 tokens: 88 us against 45 us), although it spreads a long tile over several blocks.
             through_scratch = rows_cap <= 32
         if through_scratch:
-            if rows_cap > 128:
-                raise KernelError("attention_tc: runs through scratch hold at most 128 rows a tile")
             need = self.lib.idm_attention_tc_scratch_floats(n_tiles, n_q, n_kv, hd, max_runs, rows_cap)
         else:
             need = self.lib.idm_attention_tc_scratch_floats(n_tiles, n_q, n_kv, hd, 0, 0) if max_runs > 1 else 0

@@ -400,7 +400,7 @@ CUTS = (1, 2, 16, 17, 32, 33, 64, 65, 128, 129, 200, 256, 257, 300)
 
 @pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (8, 1000, 160), (200, 512, 1024), (17, 130, 72), (64, 1024, 3072),
                                     (33, 257, 2048), (300, 384, 136), (1, 151936, 64), (2048, 1024, 1024),
-                                    (130, 4096, 4096), (200, 1024, 12288), (256, 5120, 5120), (96, 40, 8)])
+                                    (130, 4096, 4096), (200, 1024, 12288), (256, 5120, 5120), (96, 40, 8), (100, 20000, 128)])
 def test_gemm_bfloat16(kernels, M, N, K_):
     K = kernels("bfloat16")
     x, w = _randn(M, K_, seed=72).bfloat16(), _randn(N, K_, seed=73).bfloat16()
