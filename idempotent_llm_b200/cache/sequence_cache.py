@@ -224,6 +224,20 @@ class SequenceCache:
     def state_of(self, cache_id: int) -> Optional[torch.Tensor]:
         return self.state.get(cache_id)
 
+    def snapshot_state(self, slots) -> Dict[int, torch.Tensor]:
+        """Copies of the per-sequence state of ``slots`` (empty if no entry keeps state)."""
+        if not self.state:
+            return {}
+        idx = torch.as_tensor(list(slots), dtype=torch.long, device=self.device)
+        return {cid: st.index_select(0, idx) for cid, st in self.state.items()}
+
+    def restore_state(self, slots, snapshot: Dict[int, torch.Tensor]) -> None:
+        if not snapshot:
+            return
+        idx = torch.as_tensor(list(slots), dtype=torch.long, device=self.device)
+        for cid, saved in snapshot.items():
+            self.state[cid].index_copy_(0, idx, saved)
+
     # accounting (tests) -----------------------------------------------------
     def pages_held(self) -> int:
         return sum(g.pool.n_held for g in self.groups if g.pool is not None)

@@ -1,16 +1,20 @@
 """Command line, in the manner of the reference's scripts.
 
 ``demo``  scripts/demo.py: one fixed prompt, several ways of running it (alone, with 7
-          junk co-prompts, prompt fed as prefill + single tokens), a chain hash over the
+          junk co-prompts, prompt fed as prefill + single tokens), a chained digest over the
           logits of every generated step and over the token ids; options ``--config``,
-          ``--steps``, ``--artifact``, ``--checkpoint-every`` as there (demo.py:266-278).
+          ``--steps``, ``--artifact``, ``--checkpoint-every`` as there (demo.py:266-278).  Exit 1 if
+          any two ways differ in a bit, in either precision.  The reference's fourth way, the same
+          model on the CPU as a witness from another device (demo.py:101-164), has no counterpart here
+          (there is no CPU path); ``--save-chains`` / ``--against`` compare runs, days and machines
+          instead, and the CPU witness of the arithmetic is the plain implementation under ``tests/``.
 ``bench`` scripts/bench.py: ``--model``, ``--batch``, ``--prompt-len``, ``--decode-steps``,
           ``--prefill-len`` as there (bench.py:92-100); decode tok/s = batch * steps / time in
           steady state, prefill tok/s = batch * prefill_len / time of one step call.
 ``generate``  token ids in, token ids out.
 ``random``    write a model folder with seeded random weights.
 ``replay``    the trace replay program (also ``bin/trace_run``).
-``kernel-bench``  one kernel alone at a preset's layer sizes (the commands under profiles/ use it).
+``kernel-bench``  one kernel alone at a preset's layer sizes (``kernel_bench.py``).
 
 The reference's tokenizer is a library black box (demo.py:82-87); this command line
 takes and prints token ids.
@@ -27,21 +31,36 @@ from typing import List
 import torch
 
 
-class HashChain:
-    """h_i = sha256(h_{i-1} || bytes_i), as scripts/demo.py:58-71."""
+class ChainedDigest:
+    """A running SHA-256 over a sequence of records: the state after record i is
+    ``sha256(state before || record i)``, starting from a fixed tag.  Two runs agree on their first i
+    records exactly if their i-th states agree, so the first state that differs names the first step
+    that diverged.  (The reference's demo chains its logits and token ids this way,
+    scripts/demo.py:58-71.)"""
 
-    def __init__(self, every: int = 0, marks=(64, 128, 256, 512)):
-        self.h = hashlib.sha256(b"detllm-demo-v1").digest()
-        self.steps: List[str] = []
-        self.at = {}
-        self.every, self.marks = every, marks
+    TAG = b"idempotent_llm_b200 chained digest, version 1"
 
-    def update(self, data: bytes):
-        self.h = hashlib.sha256(self.h + data).digest()
-        self.steps.append(self.h.hex()[:16])
-        n = len(self.steps)
-        if (self.every and n % self.every == 0) or (not self.every and n in self.marks):
-            self.at[n] = self.h.hex()[:16]
+    def __init__(self):
+        self._state = hashlib.sha256(self.TAG).digest()
+        self.prefixes: List[str] = []          # the first 16 hex digits of every state, in order
+
+    def add(self, record: bytes) -> None:
+        self._state = hashlib.sha256(self._state + record).digest()
+        self.prefixes.append(self._state.hex()[:16])
+
+    def checkpoints(self, every: int = 0, marks=(64, 128, 256, 512)) -> dict:
+        """record count -> state, at every ``every``-th record (or at ``marks``) and at the end."""
+        n = len(self.prefixes)
+        at = [k for k in range(1, n + 1) if (every and k % every == 0) or (not every and k in marks)]
+        return {k: self.prefixes[k - 1] for k in sorted(set(at + ([n] if n else [])))}
+
+    @staticmethod
+    def first_difference(a: List[str], b: List[str]):
+        """Index of the first record at which two chains differ (a shorter chain differs where it ends), or None."""
+        for i, (x, y) in enumerate(zip(a, b)):
+            if x != y:
+                return i
+        return None if len(a) == len(b) else min(len(a), len(b))
 
 
 def _demo_prompt(vocab: int, n: int = 64) -> List[int]:
@@ -50,19 +69,18 @@ def _demo_prompt(vocab: int, n: int = 64) -> List[int]:
 
 
 def _co_prompts(n: int, vocab: int) -> List[List[int]]:
-    """Seeded junk co-prompts, lengths 5-39, ids 100-49 999 (scripts/demo.py:90-94)."""
+    """Junk prompts that share the batch with the demo's prompt: seeded, 5 to 39 tokens long, ids from
+    100 up to 49 999 (the numbers of scripts/demo.py:90-94)."""
     g = torch.Generator().manual_seed(1234)
-    out = []
-    for _ in range(n):
-        L = int(torch.randint(5, 40, (1,), generator=g))
-        out.append(torch.randint(min(100, vocab - 1), min(50000, vocab), (L,), generator=g).tolist())
-    return out
+    lo, hi = min(100, vocab - 1), min(50000, vocab)
+    lengths = [int(torch.randint(5, 40, (1,), generator=g)) for _ in range(n)]
+    return [torch.randint(lo, hi, (L,), generator=g).tolist() for L in lengths]
 
 
-def _run_demo_config(lm, name: str, steps: int, every: int):
+def _run_demo_config(lm, name: str, steps: int):
+    """(token chain, logits chain, [(token, logits)] per generated step) of one way of running the prompt."""
     eng = lm.engine
     prompt = _demo_prompt(lm.spec.vocab_size)
-    tok_chain, logit_chain = HashChain(every), HashChain(every)
     rows = []
 
     def on_step(reqs, picked, logits):
@@ -89,15 +107,15 @@ def _run_demo_config(lm, name: str, steps: int, every: int):
         eng.close(slot)
     else:
         raise ValueError(f"unknown demo config {name!r}; b1, b8, split")
+    tokens, logits = ChainedDigest(), ChainedDigest()
     for tok, lg in rows:
-        tok_chain.update(int(tok).to_bytes(8, "little"))
-        logit_chain.update(lg.numpy().astype("<f4").tobytes())
-    for c in (tok_chain, logit_chain):
-        c.at.setdefault(len(c.steps), c.h.hex()[:16])
-    return tok_chain, logit_chain, rows
+        tokens.add(int(tok).to_bytes(8, "little"))
+        logits.add(lg.numpy().astype("<f4").tobytes())
+    return tokens, logits, rows
 
 
 def cmd_demo(args) -> int:
+    import json
     from . import api
     with open(f"{args.artifact}/model.safetensors", "rb") as f:
         sha = hashlib.sha256(f.read()).hexdigest()
@@ -108,24 +126,45 @@ def cmd_demo(args) -> int:
     results = {}
     for n in names:
         t0 = time.perf_counter()
-        results[n] = _run_demo_config(lm, n, args.steps, args.checkpoint_every or 0)
+        results[n] = _run_demo_config(lm, n, args.steps)
         tc, lc, _ = results[n]
         print(f"{n:<6} ({args.steps} tokens, {time.perf_counter() - t0:.1f}s)")
-        for k in sorted(lc.at):
-            print(f"  @{k:<4} tokens {tc.at[k]}   logits {lc.at[k]}")
+        t_at, l_at = tc.checkpoints(args.checkpoint_every or 0), lc.checkpoints(args.checkpoint_every or 0)
+        for k in sorted(l_at):
+            print(f"  @{k:<4} tokens {t_at[k]}   logits {l_at[k]}")
     ok = True
     base = names[0]
     for n in names[1:]:
         ta, la, ra = results[base]
         tb, lb, rb = results[n]
-        tdiv = next((i for i, (x, y) in enumerate(zip(ta.steps, tb.steps)) if x != y), None)
-        ldiv = next((i for i, (x, y) in enumerate(zip(la.steps, lb.steps)) if x != y), None)
+        tdiv = ChainedDigest.first_difference(ta.prefixes, tb.prefixes)
+        ldiv = ChainedDigest.first_difference(la.prefixes, lb.prefixes)
         worst = max(float((a[1] - b[1]).abs().max()) for a, b in zip(ra, rb))
         print(f"{n} vs {base}: tokens {'identical' if tdiv is None else f'diverge @ {tdiv}'}; logits "
               f"{'bit-identical' if ldiv is None else f'differ from step {ldiv}'} (max |diff| {worst:.3g})")
-        if args.dtype == "float32" and ldiv is not None:
-            ok = False                      # the 32-bit path promises identical bits across these cuts
-    print("\nVERDICT:", "consistent" if ok else "32-BIT DIVERGENCE — this is a bug")
+        if ldiv is not None or tdiv is not None:
+            ok = False                      # both precisions promise identical bits across these cuts
+    record = {"artifact_sha256": sha, "dtype": args.dtype, "steps": args.steps,
+              "chains": {n: {"tokens": results[n][0].prefixes, "logits": results[n][1].prefixes} for n in names}}
+    if args.against:
+        # the chains of another run -- another process, another day, another machine of the same kind
+        with open(args.against) as f:
+            other = json.load(f)
+        if other.get("artifact_sha256") != sha or other.get("dtype") != args.dtype:
+            print(f"{args.against}: made from another artifact or dtype; nothing to compare")
+            ok = False
+        for n in names:
+            theirs = other.get("chains", {}).get(n)
+            if theirs is None:
+                continue
+            ldiv = ChainedDigest.first_difference(record["chains"][n]["logits"][:len(theirs["logits"])],
+                                                  theirs["logits"][:len(record["chains"][n]["logits"])])
+            print(f"{n} vs {args.against}: logits {'bit-identical' if ldiv is None else f'differ from step {ldiv}'}")
+            ok = ok and ldiv is None
+    if args.save_chains:
+        with open(args.save_chains, "w") as f:
+            json.dump(record, f)
+    print("\nVERDICT:", "consistent" if ok else "DIVERGENCE — this is a bug")
     return 0 if ok else 1
 
 
@@ -225,6 +264,8 @@ def main(argv=None) -> int:
     d.add_argument("--artifact", required=True, help="model folder")
     d.add_argument("--checkpoint-every", type=int, metavar="N")
     d.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    d.add_argument("--save-chains", metavar="FILE", help="write the chains of this run as JSON")
+    d.add_argument("--against", metavar="FILE", help="compare with the chains another run wrote (--save-chains)")
     d.set_defaults(fn=cmd_demo)
 
     b = sub.add_parser("bench", help="decode and prefill throughput with random weights")

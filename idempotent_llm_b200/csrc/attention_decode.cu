@@ -46,11 +46,17 @@ struct DecodeArgs {
     int early_trigger;        // 1: let the next kernel's blocks be scheduled as soon as this one's have started
 };
 
+// A sequence's length as this launch sees it: never beyond the chunks the grid has.  (A caller that passes a
+// max_kv_len below some kv_len gets that sequence cut short, which is its own error; but every chunk that is
+// counted on then arrives, so the arrival counters in scratch are back at zero when the launch ends -- they
+// outlive the launch, and in the entry point without allocation they outlive every call of the process.)
+__device__ __forceinline__ int decode_len(const DecodeArgs& a, int s) { return min(a.kv_len[s], a.n_chunks * AD_CHUNK); }
+
 // out[s, head, :] = sum_c 2^(m_c - M) o_c / sum_c 2^(m_c - M) l_c over the sequence's chunks, ascending.
 // One warp per (sequence, q-head).  Partials were written by other blocks: read around L1.
 __device__ __forceinline__ void decode_merge_head(const DecodeArgs& a, int s, int head, int hd, int lane) {
     const int warp = s * a.n_q + head;
-    const int len = a.kv_len[s];
+    const int len = decode_len(a, s);
     const int lo = a.window > 0 ? max(0, len - a.window) : 0;
     const int c0 = lo / AD_CHUNK, c1 = (len - 1) / AD_CHUNK;
     const size_t row0 = (size_t)warp * a.n_chunks;
@@ -109,7 +115,7 @@ template <int HD>
 __device__ __forceinline__ void decode_merge_head_wide(const DecodeArgs& a, int s, int head, int lane) {
     constexpr int V = HD / 32;                               // consecutive dims per lane
     const int warp = s * a.n_q + head;
-    const int len = a.kv_len[s];
+    const int len = decode_len(a, s);
     const int lo = a.window > 0 ? max(0, len - a.window) : 0;
     const int c0 = lo / AD_CHUNK, c1 = (len - 1) / AD_CHUNK;
     const size_t row0 = (size_t)warp * a.n_chunks;
@@ -178,7 +184,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_kernel(DecodeA
     __shared__ float sm_o[AD_WARPS][GT][HD];
 
     const int chunk = blockIdx.x, g = blockIdx.y, s = blockIdx.z;
-    const int len = a.kv_len[s];
+    const int len = decode_len(a, s);
     const int lo = a.window > 0 ? max(0, len - a.window) : 0;
     if (chunk * AD_CHUNK >= len || (chunk + 1) * AD_CHUNK <= lo) return;      // nothing to see here
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -367,7 +373,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attention_decode_mma_kernel(Dec
     __shared__ int is_last;
 
     const int chunk = blockIdx.x, g = blockIdx.y, s = blockIdx.z;
-    const int len = a.kv_len[s];
+    const int len = decode_len(a, s);
     const int lo = a.window > 0 ? max(0, len - a.window) : 0;
     if (chunk * AD_CHUNK >= len || (chunk + 1) * AD_CHUNK <= lo) return;
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -1104,6 +1104,46 @@ extern "C" int idm_gemm_bf16_qkv(const void* x, const void* w, int M, int K, int
     return gemm_any<EPI_QKV>(x, w, e, M, (n_q + 2 * n_kv) * hd, K, stream);
 }
 
+// ------------------------------------------------------------------- the bounded wait, by itself
+// The wait every kernel here uses, made to run out: one block's roles wait on a barrier that nothing
+// arrives at, with a limit of `limit_cycles` instead of the two seconds of real kernels.  The first role
+// whose wait runs out sets the block's abort flag and the error word; the others see the flag and leave
+// too; tensor memory is freed and the kernel ends normally (no trap, nothing left hanging).  out[0]: 1 if
+// the wait was reported as run out, out[1]: cycles waited, out[2]: 1 if the second role left by the flag.
+__global__ void __launch_bounds__(64) wait_probe_kernel(long long limit_cycles, int arrive, int* out) {
+    __shared__ __align__(8) unsigned long long bar_mem;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const uint32_t bar = smem_u32(&bar_mem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) { mbar_init(bar, 1); abort_flag = 0; mbar_init_fence(); }
+    if (warp == 0) tmem_alloc(smem_u32(&tmem_slot), 32);          // held while waiting, as a real kernel holds it
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (arrive && threadIdx.x == 33) mbar_arrive(bar);            // (the same kernel with the arrival: the wait returns true)
+    if (lane == 0) {
+        const long long t0 = clock64();
+        // warp 1's limit is far away: it leaves because warp 0 gave up, not because its own time ran out
+        const bool ok = mbar_wait_limit(bar, 0, (volatile int*)&abort_flag, &g_gemm_error, warp == 0 ? limit_cycles : TC_WAIT_CYCLES);
+        if (warp == 0) { out[0] = ok ? 0 : 1; out[1] = (int)min((long long)0x7fffffff, clock64() - t0); }
+        else out[2] = ok ? 0 : 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_slot, 32);
+}
+
+// Launches the probe; out: three words on the device (see above).  The library's error word is set when
+// the wait runs out (idm_gemm_status reports and clears it).
+extern "C" int idm_wait_probe(long long limit_cycles, int arrive, int* out, cudaStream_t stream) {
+    IDM_REQUIRE(limit_cycles > 0 && limit_cycles <= 2000000000ll, "wait_probe: limit of %lld cycles (1 .. 2e9)", limit_cycles);
+    IDM_REQUIRE(out != nullptr, "wait_probe: no place for the result");
+    wait_probe_kernel<<<1, 64, 0, stream>>>(limit_cycles, arrive, out);
+    IDM_LAUNCH_CHECK("wait_probe");
+    return 0;
+}
+
 // 0, or 1 if any block's bounded wait ran out since the last call (reads the flag: synchronises)
 extern "C" int idm_gemm_status() {
     int v = 0, zero = 0;

@@ -24,8 +24,11 @@
 //  * All calls share the one array, which keeps what the last call left in it.  The partial results
 //    need no clearing (each call writes every one it later reads); the small arrival counters
 //    behind them must be zero when a call starts, which holds because the array starts as zeros
-//    and every call sets its counters back before it ends.  Two calls that overlap on the GPU, on
-//    different streams, race on the array: keep them on one stream or order them with events.
+//    and every call sets its counters back before it ends -- also a call whose max_kv_len is smaller
+//    than one of its kv_len: that sequence is then read only up to max_kv_len (rounded up to 256), a
+//    wrong answer for a wrong call, but no chunk is waited for that the grid does not have.  Two calls
+//    that overlap on the GPU, on different streams, race on the array: keep them on one stream or
+//    order them with events.
 //
 // Arguments are those of idm_attention_decode without `scratch`:
 //   q [n_seqs, n_q, hd] and out [n_seqs, n_q * hd] in the library's storage type; the cache entry's

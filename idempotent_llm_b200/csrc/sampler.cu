@@ -41,7 +41,9 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restr
         if (s != s) s = -INFINITY;                      // a NaN never wins
         if (temperature > 0.f) {
             const unsigned long long bits = mix64(key ^ ((unsigned long long)v * 0xD1342543DE82EF95ull));
-            const float u = ((float)(bits >> 40) + 0.5f) * (1.0f / 16777216.0f);
+            // 23 bits: x + 0.5 is exact in 32-bit for x < 2^23, so u lies in [2^-24, 1 - 2^-24] and both
+            // logarithms are finite (with 24 bits the largest x rounds up to u = 1 and the score to +inf)
+            const float u = ((float)(bits >> 41) + 0.5f) * (1.0f / 8388608.0f);
             s = s * inv_t - logf(-logf(u));
         }
         better(bs, bi, s, v);

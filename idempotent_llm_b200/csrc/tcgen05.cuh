@@ -32,18 +32,22 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: false if it ran out (then *abort_flag and *error_word are set) or if another role of
 // the block already gave up.  Callers leave their loops on false and fall through to the teardown.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word,
+                                                long long limit_cycles) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
         if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > TC_WAIT_CYCLES) {
+        if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1;
             atomicExch(error_word, 1);
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word) {
+    return mbar_wait_limit(bar, parity, abort_flag, error_word, TC_WAIT_CYCLES);
 }
 
 // The same for a barrier that blocks of other SMs of the cluster arrive at (acquire at cluster scope).

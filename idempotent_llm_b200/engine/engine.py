@@ -72,9 +72,14 @@ class _DecodeGraph:
                 self.logits = engine.model.forward(ctx, engine.cache, rows)
                 if self.temperature is not None:
                     self.picked = K.sample(self.logits, self.temperature, dev_keys)
-            for _ in range(2):                       # warm-up outside capture (lazy library state)
+            # warm-up outside capture (lazy library state).  Keys and values are written once per position,
+            # so running the step again changes nothing there; per-sequence state is read, then written:
+            # it is put back, or the replay below would be the step's third run on it
+            keep = engine.cache.snapshot_state(slots)
+            for _ in range(2):
                 body()
             torch.cuda.synchronize()
+            engine.cache.restore_state(slots, keep)
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, pool=engine._graph_pool):
                 body()
@@ -108,12 +113,13 @@ class DecodeSession:
         self.rows = self.dev[7 * B + 1:]
         self.steps_done = 0
         self.launches_per_step = 0
-        backup = self.dev.clone()
+        backup, keep = self.dev.clone(), cache.snapshot_state(self.slots)
         K = engine.rt.kernels
         for _ in range(2):
             self._one_step()
         torch.cuda.synchronize()
-        self.dev.copy_(backup)                    # warm-up moved the positions on; start again
+        self.dev.copy_(backup)                    # warm-up moved the positions (and any per-sequence state) on; start again
+        cache.restore_state(self.slots, keep)
         self.counter.zero_()
         g = torch.cuda.CUDAGraph()
         before = K.launches

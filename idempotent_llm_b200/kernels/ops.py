@@ -84,6 +84,10 @@ SIGNATURES = {
     "idm_gemm_bf16_swiglu": (c_int, "pppiiip"),
     "idm_gemm_bf16_qkv": (c_int, "ppiiiiippfppppppppiipppp"),
     "idm_gemm_status": (c_int, ""),
+    "idm_wait_probe": (c_int, "qipp"),
+    # only in a library compiled with -DIDM_TRACE (time stamps from inside two kernels: a measuring aid)
+    "idm_gemm_trace_read": (c_int, "p"),
+    "idm_attention_tc_trace_read": (c_int, "p"),
 }
 
 
@@ -447,6 +451,17 @@ class Kernels:
                 (kv.table.shape[1] if kv is not None else 0), (kv.ring if kv is not None else 0),
                 _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots), self._stream()))
         return q, k_new, v_new
+
+    def wait_probe(self, limit_cycles: int, arrive: bool = False):
+        """The kernels' bounded wait on a barrier nobody arrives at (or, with ``arrive``, one somebody does):
+        returns (ran out, cycles waited, the second role left by the abort flag).  The kernel ends normally
+        either way; a wait that ran out shows in ``gemm_status()``."""
+        if self.dtype != torch.bfloat16:
+            raise KernelError("the wait probe lives in the bfloat16 library")
+        out = torch.full((3,), -1, dtype=torch.int32, device=self.device)
+        self._check(self.lib.idm_wait_probe(int(limit_cycles), 1 if arrive else 0, _p(out), self._stream()), 1)
+        ran_out, cycles, other = out.tolist()
+        return bool(ran_out), int(cycles), bool(other)
 
     def gemm_status(self) -> int:
         """0, or 1 if a bounded wait inside the tensor-core GEMM ran out since the last call (synchronises)."""

@@ -13,7 +13,8 @@ Generator (all arithmetic modulo 2**64):
             x = (x ^ x>>27) * 0x94D049BB133111EB; return x ^ x>>31
     row_key = mix(mix(mix(seed) ^ request) ^ step)
     bits_v  = mix(row_key ^ (v * 0xD1342543DE82EF95))
-    u_v     = ((bits_v >> 40) + 0.5) / 2**24         (in (0, 1), exact in 32-bit)
+    u_v     = ((bits_v >> 41) + 0.5) / 2**23         (in [2**-24, 1 - 2**-24]: x + 0.5 is exact in
+              32-bit only for x < 2**23; with 24 bits the largest x would round up to u = 1)
 """
 
 from __future__ import annotations
@@ -34,6 +35,12 @@ def mix64(x: int) -> int:
 
 def row_key(seed: int, request: int, step: int) -> int:
     return mix64(mix64(mix64(seed & _M) ^ (request & _M)) ^ (step & _M))
+
+
+def uniform_from_bits(bits: int) -> float:
+    """The uniform number the kernel makes of 64 generator bits, with its 32-bit roundings."""
+    import numpy as np
+    return float((np.float32(bits >> 41) + np.float32(0.5)) * np.float32(1.0 / 8388608.0))
 
 
 def _as_i64(x: int) -> int:

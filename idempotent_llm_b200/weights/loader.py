@@ -7,10 +7,11 @@ wrong shape) is reported in ONE error.  The reference asserts dtype per tensor
 while loading its artifact (src/detllm/model.py:116-119) and names the
 checkpoint's tensors in src/detllm/prepare.py:323-384.
 
-Storage policy: 16-bit floats are kept as bfloat16, a tensor stored in 32-bit
-floating point stays 32-bit, integer tables become int32.  The parts decide
-afterwards what the compute path needs (matrices in the compute dtype, norm
-weights in 32-bit).
+Storage policy: bfloat16 stays bfloat16, a tensor stored in 32-bit floating point
+stays 32-bit, float16 is widened to 32-bit (exact; narrowing it to bfloat16 here
+would drop three bits even on the 32-bit path), integer tables become int32.  The
+parts decide afterwards what the compute path needs (matrices in the compute
+dtype, norm weights in 32-bit).
 """
 
 from __future__ import annotations
@@ -55,9 +56,9 @@ class WeightError(ValueError):
 
 
 def storage_dtype(dt: torch.dtype) -> torch.dtype:
-    if dt in (torch.bfloat16, torch.float16):
+    if dt == torch.bfloat16:
         return torch.bfloat16
-    if dt in (torch.float32, torch.float64):
+    if dt in (torch.float16, torch.float32, torch.float64):
         return torch.float32
     return torch.int32
 
@@ -72,7 +73,7 @@ def check_declared(where: str, decls: Sequence[TensorDecl], have: Dict[str, Tupl
             dt, shape = have[n]
             if tuple(shape) != tuple(d.shape):
                 wrong_shape.append((n, tuple(shape), tuple(d.shape)))
-            if not dt.is_floating_point:
+            if not isinstance(dt, torch.dtype) or not dt.is_floating_point:
                 wrong_dtype.append((n, dt))
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise WeightError(where, missing, unexpected, wrong_shape, wrong_dtype)
@@ -83,9 +84,14 @@ def load_weights(model_dir: str, decls: Sequence[TensorDecl], device) -> Dict[st
     src = SafetensorsDir(model_dir)
     have = {n: src.info(n) for n in src.names()}
     check_declared(model_dir, decls, have)
+    for d in decls:
+        if d.optional and d.name in have:
+            import warnings
+            warnings.warn(f"{model_dir}: {d.name} is in the file but the model does not use it "
+                          f"(tied embeddings): ignored", stacklevel=2)
     out = {}
     for d in decls:
-        if d.name not in have:
+        if d.name not in have or d.optional:
             continue
         t = src.get(d.name)
         out[d.name] = t.to(device=device, dtype=storage_dtype(t.dtype), copy=True)

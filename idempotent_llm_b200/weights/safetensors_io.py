@@ -49,14 +49,16 @@ class SafetensorsFile:
         self._base = 8 + hlen
         self._entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...], int, int]] = {}
         for name, e in header.items():
-            if e["dtype"] not in _DTYPES:
-                raise SafetensorsError(f"{path}: tensor {name!r} has unsupported dtype {e['dtype']}")
             b, en = e["data_offsets"]
-            dt = _DTYPES[e["dtype"]]
+            # a dtype this reader does not know (an 8-bit float, say) is kept by its name: only asking for
+            # such a tensor is an error, so a file may carry tensors the model never declares
+            dt = _DTYPES.get(e["dtype"], str(e["dtype"]))
             n = 1
             for s in e["shape"]:
                 n *= s
-            if en - b != n * torch.empty((), dtype=dt).element_size() or self._base + en > size:
+            if not 0 <= b <= en or self._base + en > size:
+                raise SafetensorsError(f"{path}: tensor {name!r} has offsets {b}..{en} outside the file's data")
+            if isinstance(dt, torch.dtype) and en - b != n * torch.empty((), dtype=dt).element_size():
                 raise SafetensorsError(f"{path}: tensor {name!r} has inconsistent offsets")
             self._entries[name] = (dt, tuple(e["shape"]), b, en)
         self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if size > self._base else None
@@ -65,12 +67,15 @@ class SafetensorsFile:
         return list(self._entries)
 
     def info(self, name: str) -> Tuple[torch.dtype, Tuple[int, ...]]:
+        """(dtype, shape); the dtype is its name as a string if this reader does not know it."""
         dt, shape, _, _ = self._entries[name]
         return dt, shape
 
     def get(self, name: str) -> torch.Tensor:
         """A read-only view into the mapping; copy (``.to`` / ``.clone``) before the file closes."""
         dt, shape, b, e = self._entries[name]
+        if not isinstance(dt, torch.dtype):
+            raise SafetensorsError(f"{self.path}: tensor {name!r} has unsupported dtype {dt}")
         if e == b:
             return torch.empty(shape, dtype=dt)
         buf = memoryview(self._mm)[self._base + b:self._base + e]

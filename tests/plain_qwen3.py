@@ -137,9 +137,10 @@ def head(x, w, cfg):
 
 # ------------------------------------------------------------------------------- model
 def forward(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int],
-            schedule: Optional[List[Tuple[int, int, bool]]] = None, dtype=F64) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence.  ``schedule``: (layer, cache id, writes) per
-    stop; default every layer once (pre-norm residual order of src/detllm/model.py:288-428)."""
+            schedule: Optional[List[Tuple[int, int, bool]]] = None, dtype=F64, rows=None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence (or of its positions ``rows`` only: the head of a large
+    vocabulary is most of the work).  ``schedule``: (layer, cache id, writes) per stop; default every layer
+    once (pre-norm residual order of src/detllm/model.py:288-428)."""
     w = {k: v.to(dtype) for k, v in w.items()}
     ids = torch.as_tensor(list(ids), dtype=torch.long)
     T = ids.numel()
@@ -159,7 +160,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int],
         h = h + a
         x = rmsnorm(h, w[p + "post_attention_layernorm.weight"], eps)
         h = h + mlp_block(x, w, p)
-    return head(h, w, cfg)
+    return head(h if rows is None else h[list(rows)], w, cfg)
 
 
 # ---------------------------------------------------------------------------- sampling
@@ -180,7 +181,7 @@ def gumbel_scores(logits: torch.Tensor, temperature: float, seed: int, request: 
     u = torch.empty(V, dtype=F64)
     for v in range(V):
         bits = _mix(key ^ ((v * 0xD1342543DE82EF95) & _M))
-        u[v] = ((bits >> 40) + 0.5) / 16777216.0
+        u[v] = ((bits >> 41) + 0.5) / 8388608.0
     return logits.to(F64) / temperature - torch.log(-torch.log(u))
 
 

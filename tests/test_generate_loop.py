@@ -117,6 +117,22 @@ def test_generator_of_the_sampler_is_the_documented_one():
     assert row_key(7, 3, 11) != row_key(7, 4, 11) != row_key(7, 3, 12)
 
 
+def test_the_sampler_s_uniform_number_stays_inside_the_open_interval_in_32_bit():
+    """u = ((bits >> 41) + 0.5) / 2**23 with every operation rounded to 32-bit: never 0 and never 1, so
+    -log(-log(u)) is finite.  (With 24 bits, x = 2**24 - 1 plus 0.5 rounds up to 2**24: u = 1, the score +inf.)"""
+    import math
+    import numpy as np
+    from idempotent_llm_b200.sampling.sampler import uniform_from_bits
+    for k in range(1, 65):
+        for bits in ((1 << k) - 1, ((1 << k) - 1) << (64 - k), (1 << 64) - 1, 0):
+            u = uniform_from_bits(bits & ((1 << 64) - 1))
+            assert 0.0 < u < 1.0, (k, bits, u)
+            assert math.isfinite(-math.log(-math.log(u)))
+    assert uniform_from_bits((1 << 64) - 1) == 1.0 - 2.0 ** -24 and uniform_from_bits(0) == 2.0 ** -24
+    # the 24-bit form the kernel once had does reach 1
+    assert float((np.float32((1 << 24) - 1) + np.float32(0.5)) * np.float32(1.0 / 16777216.0)) == 1.0
+
+
 def test_packed_single_token_step_moved_on_in_place_is_the_next_step_packed_anew():
     """The step function keeps the packed arrays of a batch that goes on by one token and updates them
     in place; that must give what packing the next step from scratch gives."""

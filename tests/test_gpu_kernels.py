@@ -563,6 +563,22 @@ def test_sampler_argmax_ties_and_gumbel(kernels):
         K.sample(small.cuda(), 0.7, None)
 
 
+def test_sampler_never_draws_an_infinite_score_over_a_whole_vocabulary(kernels):
+    """One logit far above the rest, the real vocabulary, many rows and keys: the peak is chosen every
+    time.  (A uniform number of exactly 1 gave its token the score +inf: about one draw in 110 at this
+    vocabulary was a random id.)"""
+    from idempotent_llm_b200.sampling.sampler import _as_i64, row_key
+    K = kernels("float32")
+    V, rows = 151936, 512
+    lg = torch.zeros(rows, V)
+    peak = torch.randint(0, V, (rows,), generator=torch.Generator().manual_seed(5))
+    lg[torch.arange(rows), peak] = 200.0
+    for seed in (0, 1, 2, 3):
+        keys = torch.tensor([_as_i64(row_key(seed, r, 17 + seed)) for r in range(rows)], dtype=torch.int64)
+        got = K.sample(lg.cuda(), 1.0, keys.cuda()).cpu()
+        assert torch.equal(got.long(), peak), f"seed {seed}: rows {(got.long() != peak).nonzero().flatten().tolist()[:5]}"
+
+
 def test_sizes_the_kernels_cannot_take_are_refused(kernels):
     from idempotent_llm_b200.kernels import KernelError
     K = kernels("bfloat16")
@@ -580,3 +596,23 @@ def test_sizes_the_kernels_cannot_take_are_refused(kernels):
     with pytest.raises(KernelError, match="head_dim"):
         K.gemm_qkv(torch.zeros(1, 64, device="cuda", dtype=torch.bfloat16), torch.zeros(48, 64, device="cuda", dtype=torch.bfloat16),
                    1, 1, 16, None, None, 1e-6, None, None, None, False)
+
+
+def test_a_bounded_wait_that_runs_out_reports_and_the_kernel_ends_normally(kernels):
+    """The wait every tensor-core kernel uses, on a barrier nothing arrives at, with a limit of a few
+    thousand cycles: it gives up, the block's other role leaves through the abort flag, tensor memory is
+    freed, the kernel returns, the status word says so once, and the device goes on working.  With an
+    arrival the same kernel reports nothing."""
+    K = kernels("bfloat16")
+    assert K.gemm_status() == 0
+    ran_out, cycles, other_left = K.wait_probe(5000)
+    assert ran_out and other_left and 5000 <= cycles < 5_000_000
+    assert K.gemm_status() == 1, "the run-out wait is not reported"
+    assert K.gemm_status() == 0, "the report is not cleared by reading it"
+    ran_out, cycles, other_left = K.wait_probe(5000, arrive=True)
+    assert not ran_out and not other_left and K.gemm_status() == 0
+    # the context is as usable as before
+    x, w = _randn(8, 128, seed=1).bfloat16().cuda(), _randn(32, 128, seed=2).bfloat16().cuda()
+    assert helpers.rel_err(K.gemm_store(x, w), x.double().cpu() @ w.double().cpu().T) < 2e-5
+    with pytest.raises(Exception, match="limit"):
+        K.wait_probe(0)

@@ -187,6 +187,21 @@ class ToyDecayMixer(Mixer):
         return out.unsqueeze(0)
 
 
+class ToyDecayMixerOnDevice(ToyDecayMixer):
+    """The same mixer with its single-token step written without a look at the host, so that the engine may
+    capture such steps in a graph.  Its state is read, then written: a step that runs twice shows."""
+
+    graph_safe = True
+
+    def forward(self, x, ctx, kv, state, writes_cache):
+        if not ctx.single_token:
+            return super().forward(x, ctx, kv, state, writes_cache)
+        idx = ctx.slots.long()
+        s = self.spec.decay * state.index_select(0, idx) + x.float()
+        state.index_copy_(0, idx, s)
+        return (s @ self.w.T).unsqueeze(0)
+
+
 @dataclass(frozen=True)
 class ToyConfig:
     vocab_size: int = 97
@@ -270,6 +285,60 @@ def test_toy_mixer_with_its_own_state_is_registered_built_and_stepped(tmp_path, 
             eng.close(s)
     toks, _ = lm.generate(reqs, 4)
     assert toks.shape == (3, 4) and int(toks.min()) >= 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_steps_advance_a_mixer_s_state_once(tmp_path, dtype):
+    """Single-token steps of a model whose mixer keeps per-sequence state, captured in graphs (the first such
+    step of a batch size also warms up and captures) and launched one by one: the same bits, and both right.
+    Also through the device-side decode loop."""
+    import json
+    import idempotent_llm_b200 as idm
+    from idempotent_llm_b200.weights import write_safetensors
+    MIXERS.register("toy_decay", ToyDecayMixerOnDevice)
+    try:
+        idm.register_architecture("ToyForCausalLM", ToyConfig)
+        cfg = ToyConfig()
+        w = random_weights(declare_weights(cfg.to_model_spec()), 7, 0.2, dtype=torch.bfloat16)
+        (tmp_path / "config.json").write_text(json.dumps({"architectures": ["ToyForCausalLM"], "vocab_size": 97,
+                                                          "hidden_size": 48, "decay": 0.75}))
+        write_safetensors(str(tmp_path / "model.safetensors"), list(w.items()))
+        reqs = [helpers.rand_ids(n, 97, 40 + n) for n in (9, 30, 7)]
+        refs = [_toy_plain(_w64(w), r, cfg) for r in reqs]
+        outs = {}
+        for graph in (True, False):
+            lm = idm.load(str(tmp_path), dtype=dtype, max_tokens=64 * 6, max_seqs=3, use_graph=graph)
+            eng = lm.engine
+            assert lm.model.graph_safe
+            slots = [eng.open() for _ in reqs]
+            cut = [len(r) - 5 for r in reqs]
+            eng.step([(s_, r[:c]) for s_, r, c in zip(slots, reqs, cut)])
+            got = []
+            for k in range(5):
+                got.append(eng.step([(s_, [r[c + k]]) for s_, r, c in zip(slots, reqs, cut)]).clone())
+                ref = torch.stack([ref_[c + k] for ref_, c in zip(refs, cut)])
+                assert helpers.rel_err(got[-1], ref) < helpers.TOL[dtype], f"graph={graph}: single-token step {k}"
+            outs[graph] = torch.stack(got)
+            # the device-side loop from here: its first step also warms up and captures
+            first = [int(t) for t in got[-1].argmax(-1)]
+            state_before = {cid: st.clone() for cid, st in eng.cache.state.items()}
+            sess = eng.decode_session(slots, first, 3)
+            for cid, st in eng.cache.state.items():
+                assert torch.equal(st, state_before[cid]), "opening the session moved the state on"
+            sess.run(3)
+            chosen = sess.tokens()
+            sess.finish()
+            for i, r in enumerate(reqs):
+                seq = list(r)
+                for k in range(3):
+                    seq.append(first[i] if k == 0 else int(chosen[k - 1, i]))
+                    lgt = _toy_plain(_w64(w), seq, cfg)[-1]
+                    assert float(lgt.max() - lgt[int(chosen[k, i])]) <= helpers.TOL[dtype] * float(lgt.abs().max())
+            for s_ in slots:
+                eng.close(s_)
+        assert torch.equal(outs[True], outs[False]), "captured and plain single-token steps differ"
+    finally:
+        MIXERS.register("toy_decay", ToyDecayMixer)
 
 
 # ------------------------------------- a toy feed-forward with routing and a toy position encoding

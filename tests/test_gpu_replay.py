@@ -63,6 +63,13 @@ def test_replay_whole_split_and_batched(model_dirs, tmp_path, name, dtype):
     got = helpers.run_trace(d, dtype, steps, str(tmp_path / "out"), max_tokens=most)
     refs = [plain.forward(cfg, w, ids) for ids in reqs]
     scale = [float(r.abs().max()) for r in refs]
+    # the three ways of cutting the same requests give the same bits at every (request, position), in both precisions
+    seen = {}
+    for s, rows in zip(steps, expect):
+        for i, (r, p) in enumerate(rows):
+            first = seen.setdefault((r, p), (s["step"], got[s["step"]][i]))
+            assert torch.equal(first[1], got[s["step"]][i]), (
+                f"request {r} position {p}: step {s['step']} ({[e['id'] for e in s['entries']]}) and step {first[0]} differ in bits")
     for s, rows in zip(steps, expect):
         if not rows:
             assert s["step"] not in got

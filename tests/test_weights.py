@@ -68,7 +68,9 @@ def test_32_bit_storage_stays_32_bit_and_integers_become_int32(tmp_path):
     cfg = Qwen3Config.from_dict(helpers.TINY["A"])
     w = load_weights(d, declare_weights(cfg.to_model_spec()), "cpu")
     assert all(t.dtype == torch.float32 for t in w.values())
-    assert storage_dtype(torch.float16) == torch.bfloat16 and storage_dtype(torch.int64) == torch.int32
+    # float16 is widened, not narrowed to bfloat16: the 32-bit path must see the stored values exactly
+    assert storage_dtype(torch.float16) == torch.float32 and storage_dtype(torch.bfloat16) == torch.bfloat16
+    assert storage_dtype(torch.int64) == torch.int32
     assert storage_dtype(torch.uint8) == torch.int32 and storage_dtype(torch.float32) == torch.float32
 
 
@@ -98,7 +100,9 @@ def test_tied_model_tolerates_an_lm_head_and_untied_requires_it(tmp_path):
     d = _folder(tmp_path / "a", "A")
     _rewrite(d, lambda t: t.__setitem__("lm_head.weight", t["model.embed_tokens.weight"].clone()))
     cfg = Qwen3Config.from_dict(helpers.TINY["A"])
-    load_weights(d, declare_weights(cfg.to_model_spec()), "cpu")
+    with pytest.warns(UserWarning, match="lm_head.weight is in the file but the model does not use it"):
+        w = load_weights(d, declare_weights(cfg.to_model_spec()), "cpu")
+    assert "lm_head.weight" not in w
     d = _folder(tmp_path / "b", "B")
     _rewrite(d, lambda t: t.pop("lm_head.weight"))
     with pytest.raises(WeightError, match="lm_head.weight"):
@@ -110,6 +114,47 @@ def test_integer_tensor_under_a_weight_name_is_refused(tmp_path):
     _rewrite(d, lambda t: t.__setitem__("model.norm.weight", torch.ones(64, dtype=torch.int32)))
     with pytest.raises(WeightError, match="wrong dtype"):
         load_weights(d, declare_weights(Qwen3Config.from_dict(helpers.TINY["A"]).to_model_spec()), "cpu")
+
+
+def test_float16_is_kept_exactly_and_unknown_dtypes_matter_only_where_declared(tmp_path):
+    import struct
+    d = _folder(tmp_path, dtype=torch.float32)
+    cfg = Qwen3Config.from_dict(helpers.TINY["A"])
+    half = {}
+    _rewrite(d, lambda t: [half.__setitem__(n, t[n].to(torch.float16)) or t.__setitem__(n, t[n].to(torch.float16)) for n in list(t)])
+    w = load_weights(d, declare_weights(cfg.to_model_spec()), "cpu")
+    assert all(t.dtype == torch.float32 for t in w.values())
+    assert all(torch.equal(w[n], half[n].float()) for n in w)
+    # a tensor of a dtype this reader does not know: harmless while nobody declares it ...
+    path = os.path.join(d, "model.safetensors")
+    raw = open(path, "rb").read()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + hlen])
+    end = max(e["data_offsets"][1] for k, e in header.items() if k != "__metadata__")
+    header["extra.scale"] = {"dtype": "F8_E4M3", "shape": [4], "data_offsets": [end, end + 4]}
+    hb = json.dumps(header).encode()
+    open(path, "wb").write(struct.pack("<Q", len(hb)) + hb + raw[8 + hlen:] + b"\0\0\0\0")
+    f = SafetensorsFile(path)
+    assert f.info("extra.scale") == ("F8_E4M3", (4,))
+    with pytest.raises(SafetensorsError, match="unsupported dtype F8_E4M3"):
+        f.get("extra.scale")
+    del f
+    with pytest.raises(WeightError, match="unexpected \\(1\\): extra.scale"):
+        load_weights(d, declare_weights(cfg.to_model_spec()), "cpu")
+    # ... and a wrong dtype, named, where a declared tensor has it
+    header["model.norm.weight"]["dtype"] = "F8_E4M3"
+    del header["extra.scale"]
+    hb = json.dumps(header).encode()
+    open(path, "wb").write(struct.pack("<Q", len(hb)) + hb + raw[8 + hlen:])
+    with pytest.raises(WeightError, match="wrong dtype \\(1\\): model.norm.weight is F8_E4M3"):
+        load_weights(d, declare_weights(cfg.to_model_spec()), "cpu")
+    # offsets that run backwards or start before the data
+    header["model.norm.weight"]["dtype"] = "F16"
+    header["model.norm.weight"]["data_offsets"] = [-128, 0]
+    hb = json.dumps(header).encode()
+    open(path, "wb").write(struct.pack("<Q", len(hb)) + hb + raw[8 + hlen:])
+    with pytest.raises(SafetensorsError, match="outside the file"):
+        SafetensorsFile(path)
 
 
 def test_broken_files(tmp_path):

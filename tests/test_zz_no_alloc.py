@@ -15,11 +15,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _setup(dtype, n_q, n_kv, hd, lens, seed):
+def _setup(dtype, n_q, n_kv, hd, lens, seed, window=None):
     from idempotent_llm_b200.cache import CacheNeed, SequenceCache
     from idempotent_llm_b200.kernels import Kernels
     K = Kernels(dtype, "cuda:0")
-    cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, 64 * 64, dtype, "cuda:0", max_seqs=len(lens))
+    need = CacheNeed("window", n_kv, hd, window=window) if window else CacheNeed("full", n_kv, hd)
+    cache = SequenceCache({0: need}, 64 * 64, dtype, "cuda:0", max_seqs=len(lens))
     g = torch.Generator(device="cuda").manual_seed(seed)
     for grp in cache.groups:
         grp.k.copy_(torch.randn(grp.k.shape, generator=g, device="cuda").to(dtype))
@@ -32,10 +33,11 @@ def _setup(dtype, n_q, n_kv, hd, lens, seed):
         torch.tensor(lens, dtype=torch.int32, device="cuda"), q
 
 
+@pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_static_scratch_entry_point_matches_the_usual_one_twice(dtype):
+def test_static_scratch_entry_point_matches_the_usual_one_twice(dtype, window):
     n_q, n_kv, hd, lens = 8, 2, 64, [700, 64, 1, 300, 257]
-    K, kv, slots, kv_len, q = _setup(dtype, n_q, n_kv, hd, lens, seed=3)
+    K, kv, slots, kv_len, q = _setup(dtype, n_q, n_kv, hd, lens, seed=3, window=window)
     scale, max_len = 1.0 / math.sqrt(hd), 1024
     fn = K.lib.idm_attention_decode_static
     fn.restype = c_int
@@ -44,15 +46,23 @@ def test_static_scratch_entry_point_matches_the_usual_one_twice(dtype):
     def static_call(qq):
         out = torch.empty((len(lens), n_q * hd), dtype=dtype, device="cuda")
         rc = fn(c_void_p(qq.data_ptr()), c_void_p(out.data_ptr()), c_void_p(kv.k.data_ptr()),
-                c_void_p(kv.v.data_ptr()), c_void_p(kv.table.data_ptr()), c_int(kv.table.shape[1]), c_int(0),
+                c_void_p(kv.v.data_ptr()), c_void_p(kv.table.data_ptr()), c_int(kv.table.shape[1]), c_int(kv.ring),
                 c_void_p(slots.data_ptr()), c_void_p(kv_len.data_ptr()), c_int(len(lens)), c_int(n_q),
-                c_int(n_kv), c_int(hd), c_int(max_len), c_float(scale), c_int(0), stream)
+                c_int(n_kv), c_int(hd), c_int(max_len_now[0]), c_float(scale), c_int(window or 0), stream)
         assert rc == 0, K.lib.idm_last_error().decode()
         return out
 
-    for call in range(2):
+    max_len_now = [max_len]
+    for call in range(3):
         qq = q if call == 0 else (q * 1.5 + 0.25).to(dtype)      # other inputs: stale partials would show
-        want = K.attention_decode(qq, kv, slots, kv_len, max_len, scale, 0)
+        if call == 1:
+            # a wrong call in between: max_kv_len below the longest sequence.  Its answer for that sequence is
+            # cut short; what matters is that it leaves the arrival counters at zero for the call after it
+            max_len_now[0] = 256
+            static_call(qq)
+            max_len_now[0] = max_len
+            continue
+        want = K.attention_decode(qq, kv, slots, kv_len, max_len, scale, window or 0)
         got = static_call(qq)
         torch.cuda.synchronize()
         assert torch.isfinite(got).all()
