@@ -2,10 +2,11 @@
 in pages of ``PAGE_TOKENS`` tokens; per-sequence state of fixed size beside them.
 
 Layout.  Cache entries (one per schedule entry that writes keys) with the same
-need -- same kind, heads, head size and window -- form a *group* with storage
-of its own: ``k, v : [entries, pages, kv_heads, PAGE_TOKENS, head_dim]``.
-A sequence's keys are found through the group's block table
-``table[slot, i] -> page``.
+need -- same kind, key and value rows and window -- form a *group* with storage
+of its own: ``k, v : [entries, pages, kv_heads, PAGE_TOKENS, head_dim]`` for
+attention.  A sequence's keys are found through the group's block table
+``table[slot, i] -> page``.  Kinds of storage are classes registered by name
+(``CACHE_KINDS``); two are built in:
 
 * ``full`` groups draw pages from a pool sized by ``max_tokens`` (each live
   sequence's length rounded up to a page), as they are needed.
@@ -49,43 +50,49 @@ class KVView:
 
 
 class KVGroup:
+    """Storage of the cache entries that share one need.  A kind of cache is a subclass registered under its
+    name (``CACHE_KINDS.register(kind, cls)``); ``SequenceCache`` talks to groups through this interface
+    only: ``pages_needed`` / ``grow`` / ``shrink`` / ``release`` (room for a slot's tokens), ``flush`` (block
+    tables to the device), ``view`` (what a mixer's kernels address), ``free_pages`` / ``pages_held``.
+
+    Rows.  A token stores a key row of shape ``need.key_row()`` and a value row of shape
+    ``need.value_row()``; a page holds ``PAGE_TOKENS`` of them with the token axis before the row's last
+    axis: ``k : [entries, pages, *key_row[:-1], PAGE_TOKENS, key_row[-1]]`` (for attention
+    ``[entries, pages, kv_heads, PAGE_TOKENS, head_dim]``, which is what its kernels read).
+    """
+
+    kind = None                 # set by the registry
+    ring = 0                    # 0: position j is stored at j; else at j % ring
+    pool = None                 # the free list of pages, if pages are handed out as sequences grow
+
     def __init__(self, need: CacheNeed, entries: Sequence[int], max_tokens: int, max_seqs: int,
                  max_seq_len: int, dtype: torch.dtype, device):
         self.need = need
         self.entries = list(entries)
         self.index = {c: i for i, c in enumerate(self.entries)}
-        self.kind = need.kind
-        if need.kind == "window":
-            self.ring = _ceil_div(need.window, PAGE_TOKENS) * PAGE_TOKENS
-            self.pages_per_seq = self.ring // PAGE_TOKENS
-            self.n_pages = self.pages_per_seq * max_seqs
-            self.pool = None
-        elif need.kind == "full":
-            self.ring = 0
-            self.pages_per_seq = _ceil_div(max_seq_len, PAGE_TOKENS)
-            self.n_pages = _ceil_div(max_tokens, PAGE_TOKENS)
-            self.pool = FreeList(self.n_pages, "cache page")
-        else:
-            raise CacheError(f"unknown cache kind {need.kind!r}")
-        shape = (len(self.entries), self.n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.pages_per_seq, self.n_pages = self.layout(need, max_tokens, max_seqs, max_seq_len)
+        kr, vr = need.key_row(), need.value_row()
+        self.k = torch.zeros((len(self.entries), self.n_pages) + kr[:-1] + (PAGE_TOKENS, kr[-1]), dtype=dtype, device=device)
+        self.v = torch.zeros((len(self.entries), self.n_pages) + vr[:-1] + (PAGE_TOKENS, vr[-1]), dtype=dtype, device=device)
         pin = torch.device(device).type == "cuda"
-        self.table_host = torch.zeros((max_seqs, self.pages_per_seq), dtype=torch.int32,
-                                      pin_memory=pin)
-        if self.kind == "window":
-            base = torch.arange(max_seqs, dtype=torch.int32)[:, None] * self.pages_per_seq
-            self.table_host.copy_(base + torch.arange(self.pages_per_seq, dtype=torch.int32)[None, :])
+        self.table_host = torch.zeros((max_seqs, self.pages_per_seq), dtype=torch.int32, pin_memory=pin)
+        self.fill_table(max_seqs)
         self.table = self.table_host.to(device)
         self.pages_of: Dict[int, List[int]] = {}
         self._dirty: List[Tuple[int, int, int]] = []
 
-    # pages ------------------------------------------------------------------
-    def pages_needed(self, slot: int, new_len: int) -> int:
-        if self.kind != "full":
-            return 0
-        return max(0, _ceil_div(new_len, PAGE_TOKENS) - len(self.pages_of.get(slot, ())))
+    # what a kind decides -----------------------------------------------------
+    def layout(self, need, max_tokens, max_seqs, max_seq_len) -> Tuple[int, int]:
+        """(pages a sequence's block table holds, pages of the whole group)."""
+        raise NotImplementedError
 
+    def fill_table(self, max_seqs: int) -> None:
+        """Block-table entries that never change (kinds with fixed pages per slot)."""
+
+    def pages_needed(self, slot: int, new_len: int) -> int:
+        return 0
+
+    # pages ------------------------------------------------------------------
     def grow(self, slot: int, new_len: int) -> int:
         """Give ``slot`` the pages that ``new_len`` tokens need; returns how many were added."""
         n = self.pages_needed(slot, new_len)
@@ -107,9 +114,19 @@ class KVGroup:
             self.pool.give_back(mine.pop())
 
     def release(self, slot: int) -> None:
-        if self.kind == "full":
+        if self.pool is not None:
             for p in self.pages_of.pop(slot, []):
                 self.pool.give_back(p)
+
+    def room_for(self, slot: int, new_len: int) -> bool:
+        """True if ``new_len`` tokens of ``slot`` fit what it already holds (no page to hand out)."""
+        return self.pool is None or new_len <= PAGE_TOKENS * len(self.pages_of.get(slot, ()))
+
+    def free_pages(self) -> Optional[int]:
+        return None if self.pool is None else self.pool.n_free
+
+    def pages_held(self) -> int:
+        return 0 if self.pool is None else self.pool.n_held
 
     def flush(self) -> None:
         for slot, first, n in self._dirty:
@@ -122,6 +139,66 @@ class KVGroup:
         return KVView(k=self.k[i], v=self.v[i], table=self.table, ring=self.ring,
                       n_kv_heads=self.need.n_kv_heads, head_dim=self.need.head_dim,
                       window=self.need.window)
+
+    def bytes(self) -> int:
+        return self.k.numel() * self.k.element_size() + self.v.numel() * self.v.element_size()
+
+
+class _KindRegistry:
+    """Cache kinds by name; another mixer's kind registers here, like parts do in ``parts.base``."""
+
+    def __init__(self):
+        self._by_kind: Dict[str, type] = {}
+
+    def register(self, kind: str, cls: type = None):
+        def put(c):
+            if not (isinstance(c, type) and issubclass(c, KVGroup)):
+                raise TypeError(f"cache kind {kind!r} must be a subclass of KVGroup")
+            c.kind = kind
+            self._by_kind[kind] = c
+            return c
+        return put if cls is None else put(cls)
+
+    def get(self, kind: str) -> type:
+        try:
+            return self._by_kind[kind]
+        except KeyError:
+            raise CacheError(f"unknown cache kind {kind!r}; registered: {sorted(self._by_kind)}") from None
+
+    def kinds(self) -> List[str]:
+        return sorted(self._by_kind)
+
+
+CACHE_KINDS = _KindRegistry()
+
+
+@CACHE_KINDS.register("full")
+class PagedGroup(KVGroup):
+    """Every key and value kept: pages drawn from a pool sized by ``max_tokens`` as sequences grow."""
+
+    def layout(self, need, max_tokens, max_seqs, max_seq_len):
+        n_pages = _ceil_div(max_tokens, PAGE_TOKENS)
+        self.pool = FreeList(n_pages, "cache page")
+        return _ceil_div(max_seq_len, PAGE_TOKENS), n_pages
+
+    def pages_needed(self, slot: int, new_len: int) -> int:
+        return max(0, _ceil_div(new_len, PAGE_TOKENS) - len(self.pages_of.get(slot, ())))
+
+
+@CACHE_KINDS.register("window")
+class RingGroup(KVGroup):
+    """The last ``window`` keys and values kept, in a ring of whole pages that belongs to the slot."""
+
+    def layout(self, need, max_tokens, max_seqs, max_seq_len):
+        if not need.window or need.window <= 0:
+            raise CacheError("a window cache needs a positive window")
+        self.ring = _ceil_div(need.window, PAGE_TOKENS) * PAGE_TOKENS
+        per_seq = self.ring // PAGE_TOKENS
+        return per_seq, per_seq * max_seqs
+
+    def fill_table(self, max_seqs: int) -> None:
+        base = torch.arange(max_seqs, dtype=torch.int32)[:, None] * self.pages_per_seq
+        self.table_host.copy_(base + torch.arange(self.pages_per_seq, dtype=torch.int32)[None, :])
 
 
 class SequenceCache:
@@ -154,7 +231,8 @@ class SequenceCache:
                 by_key.setdefault(need.group_key(), []).append(cid)
                 key_need[need.group_key()] = need
         self.groups: List[KVGroup] = [
-            KVGroup(key_need[k], ids, self.max_tokens, self.max_seqs, self.max_seq_len, dtype, device)
+            CACHE_KINDS.get(key_need[k].kind)(key_need[k], ids, self.max_tokens, self.max_seqs, self.max_seq_len,
+                                              dtype, device)
             for k, ids in by_key.items()]
         self._group_of = {cid: g for g in self.groups for cid in g.entries}
         self.state: Dict[int, torch.Tensor] = {}
@@ -194,16 +272,16 @@ class SequenceCache:
             if new_len > self.max_seq_len:
                 raise CacheError(f"a sequence of {new_len} tokens exceeds the cache's limit of "
                                  f"{self.max_seq_len} tokens per sequence")
-        full = [g for g in self.groups if g.kind == "full"]
-        if all(n <= PAGE_TOKENS * len(g.pages_of.get(s, ())) for g in full for s, n in wanted):
+        if all(g.room_for(s, n) for g in self.groups for s, n in wanted):
             return                                   # (most single-token steps: the last page has room)
         for g in self.groups:
-            if g.kind == "full":
+            free = g.free_pages()
+            if free is not None:
                 need = sum(g.pages_needed(s, n) for s, n in wanted)
-                if need > g.pool.n_free:
+                if need > free:
                     raise CacheError(
                         f"the cache is full: {need} more pages of {PAGE_TOKENS} tokens are needed, "
-                        f"{g.pool.n_free} of {g.n_pages} are free (max_tokens={self.max_tokens})")
+                        f"{free} of {g.n_pages} are free (max_tokens={self.max_tokens})")
         for g in self.groups:
             for s, n in wanted:
                 g.grow(s, n)
@@ -240,8 +318,8 @@ class SequenceCache:
 
     # accounting (tests) -----------------------------------------------------
     def pages_held(self) -> int:
-        return sum(g.pool.n_held for g in self.groups if g.pool is not None)
+        return sum(g.pages_held() for g in self.groups)
 
     def bytes(self) -> int:
-        n = sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups)
+        n = sum(g.bytes() for g in self.groups)
         return n + sum(s.numel() * s.element_size() for s in self.state.values())

@@ -22,10 +22,17 @@ import os
 from dataclasses import dataclass, asdict
 from typing import Optional, Tuple
 
-from .specs import (AttentionSpec, ConfigError, GatedMLPSpec, LayerSpec, ModelSpec,
+from .specs import (AttentionNames, AttentionSpec, ConfigError, GatedMLPNames, GatedMLPSpec, LayerSpec, ModelSpec,
                     NormSpec, RotarySpec, default_schedule)
 
 ARCHITECTURE = "Qwen3ForCausalLM"
+
+# The checkpoint's tensor names, as the reference's offline pass walks them (src/detllm/prepare.py:323-384):
+# behind "model.layers.{i}." for the layers' tensors.
+ATTENTION_NAMES = AttentionNames(q="self_attn.q_proj.weight", k="self_attn.k_proj.weight", v="self_attn.v_proj.weight",
+                                 o="self_attn.o_proj.weight", q_norm="self_attn.q_norm.weight",
+                                 k_norm="self_attn.k_norm.weight")
+MLP_NAMES = GatedMLPNames(gate="mlp.gate_proj.weight", up="mlp.up_proj.weight", down="mlp.down_proj.weight")
 
 
 def _need(d: dict, key: str):
@@ -167,13 +174,16 @@ class Qwen3Config:
                 hidden=self.hidden_size, n_heads=self.num_attention_heads,
                 n_kv_heads=self.num_key_value_heads, head_dim=self.head_dim,
                 softmax_scale=1.0 / math.sqrt(self.head_dim),  # src/detllm/prepare.py:338
-                qk_norm=True, qk_norm_eps=self.rms_norm_eps, position=rot,
+                qk_norm=True, qk_norm_eps=self.rms_norm_eps, position=rot, names=ATTENTION_NAMES,
                 window=self.window_of_layer(i))
-            ff = GatedMLPSpec(hidden=self.hidden_size, intermediate=self.intermediate_size)
+            ff = GatedMLPSpec(hidden=self.hidden_size, intermediate=self.intermediate_size, names=MLP_NAMES)
             norm = NormSpec(size=self.hidden_size, eps=self.rms_norm_eps)
             layers.append(LayerSpec(prefix=f"model.layers.{i}.", mixer=mixer, feed_forward=ff,
-                                    mixer_norm=norm, feed_forward_norm=norm))
+                                    mixer_norm=norm, feed_forward_norm=norm,
+                                    mixer_norm_prefix="input_layernorm.",
+                                    feed_forward_norm_prefix="post_attention_layernorm."))
         return ModelSpec(
+            embed_name="model.embed_tokens.weight", final_norm_prefix="model.norm.", head_name="lm_head.weight",
             architecture=ARCHITECTURE, vocab_size=self.vocab_size, hidden=self.hidden_size,
             layers=tuple(layers), schedule=default_schedule(self.num_hidden_layers),
             final_norm=NormSpec(size=self.hidden_size, eps=self.rms_norm_eps),

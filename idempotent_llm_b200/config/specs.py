@@ -22,26 +22,55 @@ class ConfigError(ValueError):
 
 @dataclass(frozen=True)
 class RotarySpec:
-    """Rotary position encoding over the whole head dimension.
+    """Rotary position encoding.
 
     Angles are ``position * theta ** (-2 j / dim)`` for ``j < dim / 2``, tiled
     twice (not interleaved); pairs are ``(d, d + dim / 2)``
-    (reference: src/detllm/ops/rope.py:25-35, 47-55).
+    (reference: src/detllm/ops/rope.py:25-35, 47-55).  ``variant`` names how the
+    rotation sits in a head, which the mixer's kernels must have:
+    ``"half_whole_head"`` (``dim`` = the head size, pairs half a head apart) is the
+    one built; a partial rotation (``dim`` < head size) or interleaved pairs would
+    be other variants, refused by name until a kernel has them.
     """
 
     theta: float
     dim: int
     max_positions: int
+    variant: str = "half_whole_head"
     kind: str = "rotary"
 
 
 @dataclass(frozen=True)
 class NormSpec:
-    """Root-mean-square norm over the last axis, weight applied afterwards."""
+    """Root-mean-square norm over the last axis, weight applied afterwards.
+    ``weight``: the tensor's name behind the prefix the block gives the norm."""
 
     size: int
     eps: float
+    weight: str = "weight"
     kind: str = "rmsnorm"
+
+
+@dataclass(frozen=True)
+class AttentionNames:
+    """Checkpoint names of an attention layer's tensors, behind the layer's prefix.  An architecture's
+    configuration sets them; the part has none of its own."""
+
+    q: str
+    k: str
+    v: str
+    o: str
+    q_norm: str
+    k_norm: str
+
+
+@dataclass(frozen=True)
+class GatedMLPNames:
+    """Checkpoint names of a gated feed-forward's matrices, behind the layer's prefix."""
+
+    gate: str
+    up: str
+    down: str
 
 
 @dataclass(frozen=True)
@@ -64,6 +93,7 @@ class AttentionSpec:
     qk_norm: bool
     qk_norm_eps: float
     position: Optional[RotarySpec]
+    names: AttentionNames
     window: Optional[int] = None
     kv_from_other: bool = False
     kind: str = "attention"
@@ -76,6 +106,7 @@ class GatedMLPSpec:
 
     hidden: int
     intermediate: int
+    names: GatedMLPNames
     activation: str = "silu"
     kind: str = "gated_mlp"
 
@@ -84,8 +115,9 @@ class GatedMLPSpec:
 class LayerSpec:
     """One layer: which block arrangement, and the parts inside it.
 
-    ``prefix`` is the weight-name prefix of the layer (``model.layers.3.``).
-    ``mixer`` and ``feed_forward`` are specs of any registered kind.
+    ``prefix`` is the weight-name prefix of the layer (``model.layers.3.``);
+    ``mixer_norm_prefix`` / ``feed_forward_norm_prefix`` follow it for the two norms'
+    tensors.  ``mixer`` and ``feed_forward`` are specs of any registered kind.
     """
 
     prefix: str
@@ -93,6 +125,8 @@ class LayerSpec:
     feed_forward: object
     mixer_norm: NormSpec
     feed_forward_norm: NormSpec
+    mixer_norm_prefix: str
+    feed_forward_norm_prefix: str
     kind: str = "prenorm"
 
 
@@ -121,9 +155,9 @@ class ModelSpec:
     final_norm: NormSpec
     tie_embeddings: bool
     max_positions: int
-    embed_name: str = "model.embed_tokens.weight"
-    final_norm_prefix: str = "model.norm."
-    head_name: str = "lm_head.weight"
+    embed_name: str                     # checkpoint names: set by the architecture's configuration
+    final_norm_prefix: str
+    head_name: str
     stop_token_ids: Tuple[int, ...] = ()
     init_std: float = 0.02
     extra: dict = field(default_factory=dict, compare=False)

@@ -35,16 +35,36 @@ class StepContext:
     memo: Dict = field(default_factory=dict)   # per-step shared tables (position encodings)
 
 
+class PackedLayout:
+    """Where the arrays of a packed step lie inside its one int32 buffer: for ``n`` tokens of ``n_seq``
+    sequences, back to back, tokens[n], token_seq[n], positions[n], cu_q[n_seq + 1], slots[n_seq],
+    q_start[n_seq], kv_len[n_seq], then whatever the step appends from ``extra_at`` on (its wanted rows).
+    The one definition of that order: packing, the views a step's kernels read, the in-place advance of a
+    single-token step and the device-side decode loop all take their offsets from here."""
+
+    def __init__(self, n: int, n_seq: int):
+        o = 3 * n
+        self.n, self.n_seq = n, n_seq
+        self.tokens = slice(0, n)
+        self.token_seq = slice(n, 2 * n)
+        self.positions = slice(2 * n, o)
+        self.cu_q = slice(o, o + n_seq + 1)
+        self.slots = slice(o + n_seq + 1, o + 2 * n_seq + 1)
+        self.q_start = slice(o + 2 * n_seq + 1, o + 3 * n_seq + 1)
+        self.kv_len = slice(o + 3 * n_seq + 1, o + 4 * n_seq + 1)
+        self.extra_at = o + 4 * n_seq + 1
+
+
 def pack_step_host(slots: List[int], starts: List[int], token_lists: List[List[int]],
                    extra: Sequence[int] = ()):
-    """Host-side packing: returns one int32 tensor holding, back to back,
-    tokens[N], token_seq[N], positions[N], cu_q[S+1], slots[S], q_start[S], kv_len[S]
-    and then ``extra`` (the step's wanted rows), plus N and the sequences' token counts."""
+    """Host-side packing: returns one int32 tensor laid out as ``PackedLayout`` says, with ``extra`` (the
+    step's wanted rows) behind it, plus N and the sequences' token counts."""
     n_seq = len(slots)
     q_lens = [len(t) for t in token_lists]
     n = sum(q_lens)
+    lay = PackedLayout(n, n_seq)
     o = 3 * n
-    buf = np.empty(o + 4 * n_seq + 1 + len(extra), dtype=np.int32)
+    buf = np.empty(lay.extra_at + len(extra), dtype=np.int32)
     st = np.asarray(starts, dtype=np.int32).reshape(n_seq)
     ql = np.asarray(q_lens, dtype=np.int32).reshape(n_seq)
     if n == n_seq and (n_seq == 0 or min(q_lens) == 1):            # one token each
@@ -58,12 +78,12 @@ def pack_step_host(slots: List[int], starts: List[int], token_lists: List[List[i
         buf[n:2 * n] = seq_of
         buf[2 * n:o] = np.arange(n, dtype=np.int32) - first[seq_of] + st[seq_of]
     buf[o] = 0
-    buf[o + 1:o + n_seq + 1] = np.cumsum(ql)
-    buf[o + n_seq + 1:o + 2 * n_seq + 1] = slots
-    buf[o + 2 * n_seq + 1:o + 3 * n_seq + 1] = st
-    buf[o + 3 * n_seq + 1:o + 4 * n_seq + 1] = st + ql
+    buf[o + 1:lay.cu_q.stop] = np.cumsum(ql)
+    buf[lay.slots] = slots
+    buf[lay.q_start] = st
+    buf[lay.kv_len] = st + ql
     if len(extra):
-        buf[o + 4 * n_seq + 1:] = extra
+        buf[lay.extra_at:] = extra
     return torch.from_numpy(buf), n, q_lens
 
 
@@ -72,22 +92,23 @@ def advance_packed_single(buf: np.ndarray, n_seq: int, tokens: Sequence[int]) ->
     becomes the step that follows it for the same sequences: ``tokens`` are the new tokens, positions,
     first new positions and lengths move on by one; sequence numbers, ``cu_q``, slots and the wanted
     rows stay."""
-    n = n_seq
-    buf[0:n] = tokens
-    buf[2 * n:3 * n] += 1                      # positions
-    buf[5 * n + 1:7 * n + 1] += 1              # q_start and kv_len
+    lay = PackedLayout(n_seq, n_seq)
+    buf[lay.tokens] = tokens
+    buf[lay.positions] += 1
+    buf[lay.q_start] += 1
+    buf[lay.kv_len] += 1
 
 
 def context_from_packed(dev_buf: torch.Tensor, n: int, slots: List[int], q_lens: List[int],
                         starts: List[int], max_kv_len=None) -> StepContext:
     n_seq = len(slots)
-    o = 3 * n
+    lay = PackedLayout(n, n_seq)
     return StepContext(
         n_tokens=n, n_seqs=n_seq,
-        tokens=dev_buf[0:n], token_seq=dev_buf[n:2 * n], positions=dev_buf[2 * n:3 * n],
-        cu_q=dev_buf[o:o + n_seq + 1], slots=dev_buf[o + n_seq + 1:o + 2 * n_seq + 1],
-        q_start=dev_buf[o + 2 * n_seq + 1:o + 3 * n_seq + 1],
-        kv_len=dev_buf[o + 3 * n_seq + 1:o + 4 * n_seq + 1],
+        tokens=dev_buf[lay.tokens], token_seq=dev_buf[lay.token_seq], positions=dev_buf[lay.positions],
+        cu_q=dev_buf[lay.cu_q], slots=dev_buf[lay.slots],
+        q_start=dev_buf[lay.q_start],
+        kv_len=dev_buf[lay.kv_len],
         max_q_len=max(q_lens) if q_lens else 0,
         max_kv_len=max_kv_len if max_kv_len is not None else max(s + q for s, q in zip(starts, q_lens)),
         single_token=all(q == 1 for q in q_lens),

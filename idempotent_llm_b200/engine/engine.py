@@ -18,7 +18,7 @@ import torch
 
 from ..cache import CacheError, SequenceCache
 from .assembly import CausalLM, cache_needs
-from .batch import StepContext, advance_packed_single, context_from_packed, pack_step_host
+from .batch import PackedLayout, StepContext, advance_packed_single, context_from_packed, pack_step_host
 
 
 class _DecodeGraph:
@@ -29,7 +29,8 @@ class _DecodeGraph:
     def __init__(self, engine: "Engine", n_seqs: int, temperature: Optional[float] = None, keys: bool = False):
         self.n = n_seqs
         dev = engine.device
-        self.packed_size = 7 * n_seqs + 1 + n_seqs
+        self.layout = PackedLayout(n_seqs, n_seqs)       # one token per sequence; the wanted rows (one each) behind
+        self.packed_size = self.layout.extra_at + n_seqs
         # the rows' 64-bit keys lie behind the packed step on an 8-byte border
         self.keys_at = (self.packed_size + 1) // 2 * 2
         self.size = self.keys_at + (2 * n_seqs if keys else 0)
@@ -63,7 +64,7 @@ class _DecodeGraph:
         if self.graph is None:
             ctx = context_from_packed(self.dev, self.n, slots, q_lens, starts,
                                       max_kv_len=engine.cache.max_seq_len)
-            rows = self.dev[7 * self.n + 1:self.packed_size]
+            rows = self.dev[self.layout.extra_at:self.packed_size]
             dev_keys = self.dev[self.keys_at:].view(torch.int64) if self.keys else None
             K = engine.rt.kernels
 
@@ -110,7 +111,8 @@ class DecodeSession:
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.ctx = context_from_packed(self.dev, B, self.slots, q_lens, self.starts,
                                        max_kv_len=cache.max_seq_len)
-        self.rows = self.dev[7 * B + 1:]
+        self.layout = PackedLayout(B, B)
+        self.rows = self.dev[self.layout.extra_at:]
         self.steps_done = 0
         self.launches_per_step = 0
         backup, keep = self.dev.clone(), cache.snapshot_state(self.slots)
@@ -133,8 +135,8 @@ class DecodeSession:
         self.ctx.memo.clear()
         logits = e.model.forward(self.ctx, e.cache, self.rows)
         picked = K.sample(logits, 0.0, None)
-        d = self.dev
-        K.decode_advance(d[0:B], d[2 * B:3 * B], d[5 * B + 1:6 * B + 1], d[6 * B + 1:7 * B + 1], picked,
+        d, lay = self.dev, self.layout
+        K.decode_advance(d[lay.tokens], d[lay.positions], d[lay.q_start], d[lay.kv_len], picked,
                          self.history, self.counter)
 
     def run(self, n_steps: int) -> None:

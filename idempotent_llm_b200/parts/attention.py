@@ -27,17 +27,17 @@ class GQAAttention(Mixer):
 
     @classmethod
     def declare(cls, spec, prefix):
-        p = prefix + "self_attn."
+        nm = spec.names
         q_rows, kv_rows = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
-        d = [TensorDecl(p + "q_proj.weight", (q_rows, spec.hidden))]
+        d = [TensorDecl(prefix + nm.q, (q_rows, spec.hidden))]
         if not spec.kv_from_other:
-            d += [TensorDecl(p + "k_proj.weight", (kv_rows, spec.hidden)),
-                  TensorDecl(p + "v_proj.weight", (kv_rows, spec.hidden))]
-        d.append(TensorDecl(p + "o_proj.weight", (spec.hidden, q_rows)))
+            d += [TensorDecl(prefix + nm.k, (kv_rows, spec.hidden)),
+                  TensorDecl(prefix + nm.v, (kv_rows, spec.hidden))]
+        d.append(TensorDecl(prefix + nm.o, (spec.hidden, q_rows)))
         if spec.qk_norm:
-            d.append(TensorDecl(p + "q_norm.weight", (spec.head_dim,), init="one_plus_normal"))
+            d.append(TensorDecl(prefix + nm.q_norm, (spec.head_dim,), init="one_plus_normal"))
             if not spec.kv_from_other:
-                d.append(TensorDecl(p + "k_norm.weight", (spec.head_dim,), init="one_plus_normal"))
+                d.append(TensorDecl(prefix + nm.k_norm, (spec.head_dim,), init="one_plus_normal"))
         return d
 
     @classmethod
@@ -53,22 +53,29 @@ class GQAAttention(Mixer):
                              f"on 16-byte borders); got hidden {spec.hidden}, heads x head_dim {spec.n_heads * spec.head_dim}")
         self.spec = spec
         self.rt = rt
-        p = prefix + "self_attn."
-        mats = [weights[p + "q_proj.weight"]]
+        nm = spec.names
+        mats = [weights[prefix + nm.q]]
         if not spec.kv_from_other:
-            mats += [weights[p + "k_proj.weight"], weights[p + "v_proj.weight"]]
+            mats += [weights[prefix + nm.k], weights[prefix + nm.v]]
         self.w_qkv = torch.cat([m.to(rt.dtype) for m in mats], dim=0).contiguous()
-        self.w_o = weights[p + "o_proj.weight"].to(rt.dtype).contiguous()
+        self.w_o = weights[prefix + nm.o].to(rt.dtype).contiguous()
         self.q_gamma = self.k_gamma = None
         if spec.qk_norm:
-            self.q_gamma = weights[p + "q_norm.weight"].to(torch.float32).contiguous()
+            self.q_gamma = weights[prefix + nm.q_norm].to(torch.float32).contiguous()
             if not spec.kv_from_other:
-                self.k_gamma = weights[p + "k_norm.weight"].to(torch.float32).contiguous()
+                self.k_gamma = weights[prefix + nm.k_norm].to(torch.float32).contiguous()
         if spec.kv_from_other and spec.window:
             raise ValueError("a mixer that reads another layer's windowed cache is not built: a prompt's "
                              "own keys are not all in the ring")
         self.position = None
         if spec.position is not None:
+            # what this mixer's kernels do with a position encoding's table: rotate pairs half a head apart
+            # over the whole head.  Another arrangement is refused by name, not by a shape error later.
+            variant = getattr(spec.position, "variant", None)
+            if variant != "half_whole_head" or getattr(spec.position, "dim", spec.head_dim) != spec.head_dim:
+                raise ValueError(f"attention: position encoding variant {variant!r} over "
+                                 f"{getattr(spec.position, 'dim', '?')} of {spec.head_dim} dims is not built; the kernels "
+                                 f"rotate pairs (d, d + head_dim / 2) over the whole head ('half_whole_head')")
             self.position = POSITIONS.get(spec.position.kind)(spec.position, weights, prefix, rt)
 
     def forward(self, x, ctx, kv, state, writes_cache: bool, residual=None):

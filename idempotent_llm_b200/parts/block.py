@@ -13,19 +13,19 @@ class PreNormBlock(Block):
     @classmethod
     def declare(cls, spec, prefix=None):
         p = spec.prefix
-        return (NORMS.get(spec.mixer_norm.kind).declare(spec.mixer_norm, p + "input_layernorm.")
+        return (NORMS.get(spec.mixer_norm.kind).declare(spec.mixer_norm, p + spec.mixer_norm_prefix)
                 + MIXERS.get(spec.mixer.kind).declare(spec.mixer, p)
                 + NORMS.get(spec.feed_forward_norm.kind).declare(spec.feed_forward_norm,
-                                                                 p + "post_attention_layernorm.")
+                                                                 p + spec.feed_forward_norm_prefix)
                 + FEED_FORWARDS.get(spec.feed_forward.kind).declare(spec.feed_forward, p))
 
     def __init__(self, spec, weights, prefix, rt):
         p = spec.prefix
         self.spec = spec
-        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, weights, p + "input_layernorm.", rt)
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, weights, p + spec.mixer_norm_prefix, rt)
         self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, weights, p, rt)
         self.feed_forward_norm = NORMS.get(spec.feed_forward_norm.kind)(
-            spec.feed_forward_norm, weights, p + "post_attention_layernorm.", rt)
+            spec.feed_forward_norm, weights, p + spec.feed_forward_norm_prefix, rt)
         self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, weights, p, rt)
 
     def forward(self, h, pending, ctx, kv, state, writes_cache: bool):

@@ -17,18 +17,18 @@ class GatedMLP(FeedForward):
 
     @classmethod
     def declare(cls, spec, prefix):
-        p = prefix + "mlp."
-        return [TensorDecl(p + "gate_proj.weight", (spec.intermediate, spec.hidden)),
-                TensorDecl(p + "up_proj.weight", (spec.intermediate, spec.hidden)),
-                TensorDecl(p + "down_proj.weight", (spec.hidden, spec.intermediate))]
+        nm = spec.names
+        return [TensorDecl(prefix + nm.gate, (spec.intermediate, spec.hidden)),
+                TensorDecl(prefix + nm.up, (spec.intermediate, spec.hidden)),
+                TensorDecl(prefix + nm.down, (spec.hidden, spec.intermediate))]
 
     def __init__(self, spec, weights, prefix, rt):
         if spec.activation != "silu":
             raise ValueError(f"activation {spec.activation!r} is not built; only 'silu'")
         self.spec = spec
         self.rt = rt
-        p = prefix + "mlp."
-        gate, up = weights[p + "gate_proj.weight"].to(rt.dtype), weights[p + "up_proj.weight"].to(rt.dtype)
+        nm = spec.names
+        gate, up = weights[prefix + nm.gate].to(rt.dtype), weights[prefix + nm.up].to(rt.dtype)
         # with the fused kernels the activation is the epilogue of the gate/up product, which wants
         # gate and up rows interleaved in tiles; otherwise the rows are simply concatenated
         if rt.dtype == torch.bfloat16 and (spec.hidden % 8 or spec.intermediate % 8):
@@ -39,7 +39,7 @@ class GatedMLP(FeedForward):
             self.w_gate_up = rt.kernels.tile_gate_up(gate, up)
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
-        self.w_down = weights[p + "down_proj.weight"].to(rt.dtype).contiguous()
+        self.w_down = weights[prefix + nm.down].to(rt.dtype).contiguous()
 
     def forward(self, x, ctx, residual=None):
         """Returns the delta ``[P, N, hidden]``, or None after adding it into ``residual`` in place."""

@@ -19,12 +19,12 @@ from .base import NORMS, Norm
 class RMSNorm(Norm):
     @classmethod
     def declare(cls, spec, prefix):
-        return [TensorDecl(prefix + "weight", (spec.size,), init="one_plus_normal")]
+        return [TensorDecl(prefix + spec.weight, (spec.size,), init="one_plus_normal")]
 
     def __init__(self, spec, weights, prefix, rt):
         self.spec = spec
         self.rt = rt
-        self.weight = weights[prefix + "weight"].to(torch.float32).contiguous()
+        self.weight = weights[prefix + spec.weight].to(torch.float32).contiguous()
 
     def forward(self, h, delta, ctx, rows=None):
         return self.rt.kernels.add_rmsnorm(h, delta, self.weight, self.spec.eps, rows=rows)

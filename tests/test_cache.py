@@ -122,3 +122,35 @@ def test_limits():
     assert c.max_tokens == 128 and c.max_seqs == 2 and c.max_seq_len == 128
     with pytest.raises(CacheError):
         SequenceCache({}, 0, torch.float32, "cpu")
+
+
+def test_another_kind_of_cache_registers_from_outside():
+    """A kind of storage that is neither of the built-in two: every sequence keeps its first 64 tokens in one
+    page of its own and nothing after them, keys and values of unequal widths.  It is a class in this file,
+    registered by name; the cache builds it, sizes it and hands out its view like any other."""
+    from idempotent_llm_b200.cache import CACHE_KINDS, KVGroup
+
+    @CACHE_KINDS.register("toy_first_page")
+    class FirstPageGroup(KVGroup):
+        def layout(self, need, max_tokens, max_seqs, max_seq_len):
+            return 1, max_seqs                      # one page per slot, fixed
+
+        def fill_table(self, max_seqs):
+            self.table_host[:, 0] = torch.arange(max_seqs, dtype=torch.int32)
+
+    need = CacheNeed("toy_first_page", k_row=(3, 8), v_row=(24,))
+    cache = SequenceCache({0: need, 1: need, 2: CacheNeed("full", 2, 16)}, 64 * 6, torch.float32, "cpu", max_seqs=4)
+    assert sorted(g.kind for g in cache.groups) == ["full", "toy_first_page"]
+    toy = next(g for g in cache.groups if g.kind == "toy_first_page")
+    assert toy.k.shape == (2, 4, 3, 64, 8) and toy.v.shape == (2, 4, 64, 24) and toy.entries == [0, 1]
+    s = cache.alloc_slot()
+    cache.reserve([(s, 200)])                       # the full group hands out pages; the toy kind needs none
+    assert cache.pages_held() == 4 and toy.pages_held() == 0
+    v = cache.view(1)
+    assert v.k.shape == (4, 3, 64, 8) and int(v.table[s, 0]) == s and v.ring == 0
+    cache.free_slot(s)
+    assert cache.pages_held() == 0
+    with pytest.raises(CacheError, match="unknown cache kind 'nope'.*toy_first_page"):
+        SequenceCache({0: CacheNeed("nope", 1, 8)}, 64, torch.float32, "cpu")
+    with pytest.raises(TypeError):
+        CACHE_KINDS.register("bad", dict)

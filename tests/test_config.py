@@ -76,7 +76,7 @@ def test_registry_unknown_and_missing(tmp_path):
 def test_schedule_validation():
     spec = Qwen3Config.from_dict(helpers.TINY["A"]).to_model_spec()
     kw = {f: getattr(spec, f) for f in ("architecture", "vocab_size", "hidden", "layers", "final_norm",
-                                        "tie_embeddings", "max_positions")}
+                                        "tie_embeddings", "max_positions", "embed_name", "final_norm_prefix", "head_name")}
     ModelSpec(schedule=(RunEntry(0, 0), RunEntry(1, 1), RunEntry(1, 2)), **kw)          # a layer named twice
     with pytest.raises(ConfigError, match="written by two"):
         ModelSpec(schedule=(RunEntry(0, 0), RunEntry(1, 0)), **kw)

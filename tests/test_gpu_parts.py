@@ -12,6 +12,8 @@ import plain_qwen3 as plain
 from idempotent_llm_b200.cache import CacheNeed, SequenceCache
 from idempotent_llm_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, NormSpec, Qwen3Config,
                                         RotarySpec, RunEntry)
+from idempotent_llm_b200.config.qwen3 import ATTENTION_NAMES, MLP_NAMES
+from idempotent_llm_b200.config.specs import AttentionNames, GatedMLPNames
 from idempotent_llm_b200.engine import CausalLM, Engine, cache_needs, declare_weights
 from idempotent_llm_b200.engine.batch import context_from_packed, pack_step_host
 from idempotent_llm_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward, Mixer,
@@ -73,7 +75,7 @@ def test_attention_part_prompt_then_single_tokens(dtype, window):
     cfg = dict(num_attention_heads=6, num_key_value_heads=2, head_dim=32, hidden_size=72, rms_norm_eps=1e-5,
                rope_theta=3e4)
     spec = AttentionSpec(hidden=72, n_heads=6, n_kv_heads=2, head_dim=32, softmax_scale=32 ** -0.5, qk_norm=True,
-                         qk_norm_eps=1e-5, position=RotarySpec(3e4, 32, 4096), window=window)
+                         qk_norm_eps=1e-5, position=RotarySpec(3e4, 32, 4096), names=ATTENTION_NAMES, window=window)
     cls = MIXERS.get(spec.kind)
     w = random_weights(cls.declare(spec, "L."), 2, 0.2, dtype=DT[dtype], device="cuda")
     assert cls.cache_need(spec) == CacheNeed("window" if window else "full", 2, 32, window=window)
@@ -95,7 +97,7 @@ def test_attention_part_prompt_then_single_tokens(dtype, window):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_feed_forward_part(dtype):
     rt = _rt(dtype)
-    spec = GatedMLPSpec(hidden=72, intermediate=200)
+    spec = GatedMLPSpec(hidden=72, intermediate=200, names=MLP_NAMES)
     cls = FEED_FORWARDS.get(spec.kind)
     w = random_weights(cls.declare(spec, "L."), 4, 0.2, dtype=DT[dtype], device="cuda")
     part = cls(spec, w, "L.", rt)
@@ -109,7 +111,15 @@ def test_unknown_kinds_and_bad_parts_are_refused():
     with pytest.raises(KeyError, match="no mixer registered"):
         MIXERS.get("nope")
     with pytest.raises(ValueError, match="activation"):
-        FEED_FORWARDS.get("gated_mlp")(GatedMLPSpec(8, 8, activation="gelu"), {}, "", None)
+        FEED_FORWARDS.get("gated_mlp")(GatedMLPSpec(8, 8, names=MLP_NAMES, activation="gelu"), {}, "", None)
+    # a position encoding whose rotation sits otherwise in the head is refused by name, before any shape meets a kernel
+    for pos in (RotarySpec(1e4, 16, 512), RotarySpec(1e4, 32, 512, variant="interleaved")):
+        bad = AttentionSpec(hidden=64, n_heads=2, n_kv_heads=2, head_dim=32, softmax_scale=0.2, qk_norm=False,
+                            qk_norm_eps=1e-6, position=pos, names=ATTENTION_NAMES)
+        with pytest.raises(ValueError, match="half_whole_head"):
+            MIXERS.get("attention")(bad, {ATTENTION_NAMES.q: torch.zeros(64, 64), ATTENTION_NAMES.k: torch.zeros(64, 64),
+                                          ATTENTION_NAMES.v: torch.zeros(64, 64), ATTENTION_NAMES.o: torch.zeros(64, 64)},
+                                    "", Runtime(device=torch.device("cpu"), dtype=torch.float32, kernels=None))
 
 
 def _custom_schedule_spec(schedule):
@@ -120,9 +130,11 @@ def _custom_schedule_spec(schedule):
         m = layers[1].mixer
         reader = AttentionSpec(**{**m.__dict__, "kv_from_other": True})
         layers.append(LayerSpec(prefix="model.layers.2.", mixer=reader, feed_forward=layers[1].feed_forward,
-                                mixer_norm=layers[1].mixer_norm, feed_forward_norm=layers[1].feed_forward_norm))
+                                mixer_norm=layers[1].mixer_norm, feed_forward_norm=layers[1].feed_forward_norm,
+                                mixer_norm_prefix=layers[1].mixer_norm_prefix,
+                                feed_forward_norm_prefix=layers[1].feed_forward_norm_prefix))
     kw = {f: getattr(base, f) for f in ("architecture", "vocab_size", "hidden", "final_norm", "tie_embeddings",
-                                        "max_positions")}
+                                        "max_positions", "embed_name", "final_norm_prefix", "head_name")}
     return ModelSpec(layers=tuple(layers), schedule=tuple(schedule), **kw)
 
 
@@ -213,29 +225,46 @@ class ToyConfig:
         return cls(**{k: d[k] for k in ("vocab_size", "hidden_size", "decay") if k in d})
 
     def to_model_spec(self):
-        norm = NormSpec(self.hidden_size, 1e-5)
-        ff = GatedMLPSpec(self.hidden_size, 64)
+        # every tensor name is this toy architecture's own: the product's parts take them from the specs
+        norm = NormSpec(self.hidden_size, 1e-5, weight="scale")
+        ff = GatedMLPSpec(self.hidden_size, 64, names=TOY_MLP_NAMES)
         attn = AttentionSpec(hidden=self.hidden_size, n_heads=3, n_kv_heads=1, head_dim=16, softmax_scale=0.25,
-                             qk_norm=True, qk_norm_eps=1e-5, position=RotarySpec(1e4, 16, 512))
-        layers = (LayerSpec("model.layers.0.", ToyDecaySpec(self.hidden_size, self.decay), ff, norm, norm),
-                  LayerSpec("model.layers.1.", attn, ff, norm, norm),
-                  LayerSpec("model.layers.2.", ToyDecaySpec(self.hidden_size, self.decay), ff, norm, norm))
+                             qk_norm=True, qk_norm_eps=1e-5, position=RotarySpec(1e4, 16, 512), names=TOY_ATTN_NAMES)
+        layer = lambda i, mixer: LayerSpec(f"blk{i}.", mixer, ff, norm, norm, mixer_norm_prefix="ln_a.",
+                                           feed_forward_norm_prefix="ln_b.")
+        layers = (layer(0, ToyDecaySpec(self.hidden_size, self.decay)), layer(1, attn),
+                  layer(2, ToyDecaySpec(self.hidden_size, self.decay)))
         return ModelSpec(architecture="ToyForCausalLM", vocab_size=self.vocab_size, hidden=self.hidden_size,
                          layers=layers, schedule=tuple(RunEntry(i, i) for i in range(3)),
-                         final_norm=norm, tie_embeddings=True, max_positions=512)
+                         final_norm=norm, tie_embeddings=True, max_positions=512,
+                         embed_name="tok.table", final_norm_prefix="ln_out.", head_name="out.table")
+
+
+TOY_ATTN_NAMES = AttentionNames(q="att.wq", k="att.wk", v="att.wv", o="att.wo", q_norm="att.q_scale", k_norm="att.k_scale")
+TOY_MLP_NAMES = GatedMLPNames(gate="ff.w_gate", up="ff.w_up", down="ff.w_down")
+
+
+def _as_plain_names(w, p):
+    """The toy layer's attention and feed-forward tensors under the names the plain functions look up."""
+    out = dict(w)
+    for theirs, ours in ((ATTENTION_NAMES, TOY_ATTN_NAMES), (MLP_NAMES, TOY_MLP_NAMES)):
+        for f in theirs.__dataclass_fields__:
+            if p + getattr(ours, f) in w:
+                out[p + getattr(theirs, f)] = w[p + getattr(ours, f)]
+    return out
 
 
 def _toy_plain(w, ids, cfg: ToyConfig):
     ids = torch.as_tensor(ids)
     T = ids.numel()
-    h = w["model.embed_tokens.weight"][ids]
+    h = w["tok.table"][ids]
     acfg = dict(num_attention_heads=3, num_key_value_heads=1, head_dim=16, hidden_size=cfg.hidden_size,
                 rms_norm_eps=1e-5, rope_theta=1e4)
     for i in range(3):
-        p = f"model.layers.{i}."
-        x = plain.rmsnorm(h, w[p + "input_layernorm.weight"], 1e-5)
+        p = f"blk{i}."
+        x = plain.rmsnorm(h, w[p + "ln_a.scale"], 1e-5)
         if i == 1:
-            a, _ = plain.attention_block(x, w, p, acfg, torch.arange(T), None)
+            a, _ = plain.attention_block(x, _as_plain_names(w, p), p, acfg, torch.arange(T), None)
         else:
             s, rows = torch.zeros(cfg.hidden_size, dtype=F64), []
             for t in range(T):
@@ -243,8 +272,8 @@ def _toy_plain(w, ids, cfg: ToyConfig):
                 rows.append(s @ w[p + "toy.weight"].T)
             a = torch.stack(rows)
         h = h + a
-        h = h + plain.mlp_block(plain.rmsnorm(h, w[p + "post_attention_layernorm.weight"], 1e-5), w, p)
-    return plain.rmsnorm(h, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T
+        h = h + plain.mlp_block(plain.rmsnorm(h, w[p + "ln_b.scale"], 1e-5), _as_plain_names(w, p), p)
+    return plain.rmsnorm(h, w["ln_out.scale"], 1e-5) @ w["tok.table"].T
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -376,6 +405,7 @@ class ToyScaledRotarySpec:
     theta: float
     dim: int
     factor: float
+    variant: str = "half_whole_head"       # (the table the attention kernels rotate with: pairs half a head apart)
     kind: str = "toy_scaled_rotary"
 
 
@@ -408,13 +438,16 @@ class ToyRoutedConfig:
     def to_model_spec(self):
         norm = NormSpec(self.hidden_size, 1e-5)
         attn = lambda pos: AttentionSpec(hidden=self.hidden_size, n_heads=2, n_kv_heads=2, head_dim=16, softmax_scale=0.25,
-                                         qk_norm=True, qk_norm_eps=1e-5, position=pos)
+                                         qk_norm=True, qk_norm_eps=1e-5, position=pos, names=ATTENTION_NAMES)
+        pre = dict(mixer_norm_prefix="input_layernorm.", feed_forward_norm_prefix="post_attention_layernorm.")
         layers = (LayerSpec("model.layers.0.", attn(ToyScaledRotarySpec(1e4, 16, self.factor)),
-                            ToyRoutedSpec(self.hidden_size, self.n_experts), norm, norm),
-                  LayerSpec("model.layers.1.", attn(RotarySpec(1e4, 16, 512)), GatedMLPSpec(self.hidden_size, 56), norm, norm))
+                            ToyRoutedSpec(self.hidden_size, self.n_experts), norm, norm, **pre),
+                  LayerSpec("model.layers.1.", attn(RotarySpec(1e4, 16, 512)),
+                            GatedMLPSpec(self.hidden_size, 56, names=MLP_NAMES), norm, norm, **pre))
         return ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=self.vocab_size, hidden=self.hidden_size,
                          layers=layers, schedule=tuple(RunEntry(i, i) for i in range(2)),
-                         final_norm=norm, tie_embeddings=True, max_positions=512)
+                         final_norm=norm, tie_embeddings=True, max_positions=512,
+                         embed_name="model.embed_tokens.weight", final_norm_prefix="model.norm.", head_name="lm_head.weight")
 
 
 def _toy_routed_plain(w, ids, cfg: ToyRoutedConfig):
