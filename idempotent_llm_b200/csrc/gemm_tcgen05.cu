@@ -51,14 +51,42 @@ __device__ int g_gemm_error = 0;
 // compiled out otherwise)
 #if defined(IDM_TRACE)
 __device__ unsigned long long g_gemm_trace[64];
+__device__ int g_gemm_trace_base = 0;          // set by the kernel's first thread: 10 stamps per kind of product
 __device__ __forceinline__ void trace_stamp(int i) {
-    if (blockIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); g_gemm_trace[i] = t; }
+    if (blockIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); g_gemm_trace[(g_gemm_trace_base + i) & 63] = t; }
 }
 extern "C" int idm_gemm_trace_read(unsigned long long* out) {
     return (int)cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned long long) * 64);
 }
+// per block of the last launch of each kind of product: wait over, first operands, accumulator ready, done, SM
+__device__ unsigned long long g_gemm_block_trace[5][512][5];
+__device__ __forceinline__ void block_stamp(int kind, int i) {
+    if (blockIdx.x < 512) {
+        unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_gemm_block_trace[kind][blockIdx.x][i] = t;
+        if (i == 0) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); g_gemm_block_trace[kind][blockIdx.x][4] = sm; }
+    }
+}
+extern "C" int idm_gemm_block_trace_read(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_gemm_block_trace, sizeof(g_gemm_block_trace));
+}
+// block 0's MMA thread: when each group's operands were there, and when its MMAs had been issued
+__device__ unsigned long long g_gemm_mma_trace[5][64][2];
+extern "C" int idm_gemm_mma_trace_read(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_gemm_mma_trace, sizeof(g_gemm_mma_trace));
+}
+// a log of block 0 of every launch, in order: kind, started, wait over, done
+__device__ unsigned long long g_gemm_log[2048][4];
+__device__ unsigned int g_gemm_log_n = 0;
+extern "C" int idm_gemm_log_read(unsigned long long* out, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_gemm_log, sizeof(g_gemm_log));
+    unsigned int zero = 0;
+    if (reset) cudaMemcpyToSymbol(g_gemm_log_n, &zero, sizeof(zero));
+    return (int)e;
+}
 #else
 __device__ __forceinline__ void trace_stamp(int) {}
+__device__ __forceinline__ void block_stamp(int, int) {}
 #endif
 
 enum { EPI_STORE = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
@@ -287,7 +315,8 @@ struct QkvTokensSmem {
 // One head of one token: norm, rotation, stores.  col0: the head's first accumulator column (with the
 // warp's lanes); cs_row: the token's row of the rotation table; cs_dim: the same table by dim (the
 // tokens of a dim side by side: two lines per request instead of 32), or null.
-template <int HD>
+// (KEEP also says that gamma and cs_row may lie in shared memory: they are read with plain loads then)
+template <int HD, bool KEEP = false>
 __device__ __forceinline__ void qkv_tokens_head(const QkvArgs& a, uint32_t col0, const float* gamma, bool rotate,
                                                 const float2* cs_row, const float2* cs_dim, int n_tokens,
                                                 T* dst_a, T* dst_b) {
@@ -295,7 +324,14 @@ __device__ __forceinline__ void qkv_tokens_head(const QkvArgs& a, uint32_t col0,
     float cs4[4][8];                                               // (cos, sin) of 16 dims
     auto ask_cs = [&](int c) {
         if (!rotate) return;
-        if (cs_dim != nullptr) {
+        if (KEEP) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 u = *reinterpret_cast<const float4*>(cs_row + c + 4 * i), w = *reinterpret_cast<const float4*>(cs_row + c + 4 * i + 2);
+                cs4[i][0] = u.x; cs4[i][1] = u.y; cs4[i][2] = u.z; cs4[i][3] = u.w;
+                cs4[i][4] = w.x; cs4[i][5] = w.y; cs4[i][6] = w.z; cs4[i][7] = w.w;
+            }
+        } else if (cs_dim != nullptr) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const float2 v = __ldg(cs_dim + (size_t)(c + i) * n_tokens);
@@ -307,6 +343,9 @@ __device__ __forceinline__ void qkv_tokens_head(const QkvArgs& a, uint32_t col0,
                 load8_readonly(reinterpret_cast<const float*>(cs_row + c + 4 * i), cs4[i]);
         }
     };
+    // KEEP (a block with few tokens and registers to spare): the whole head stays in registers after the sum of
+    // squares, so the second pass reads no tensor memory again.  The arithmetic is the same either way.
+    uint32_t all[KEEP ? HD : 1];
     uint32_t cur[32];                                              // 16 dims of each half: this step's, then the next's
     float inv = 1.f;
     {
@@ -327,19 +366,19 @@ __device__ __forceinline__ void qkv_tokens_head(const QkvArgs& a, uint32_t col0,
             }
 #pragma unroll
             for (int i = 0; i < 16; ++i) cur[16 * h + i] = raw[i];
+            if (KEEP) {
+#pragma unroll
+                for (int i = 0; i < HALF; ++i) all[h * HALF + i] = raw[i];
+            }
         }
         if (gamma != nullptr) inv = head_inv_rms(a, (s4[0] + s4[1]) + (s4[2] + s4[3]));
     }
-    // dims d and d + HALF together, 16 of each per step; the next step's columns are asked for before
-    // this step's arithmetic (the loop stays a loop: unrolled, the compiler moves all steps' loads of the
-    // norm weight to the front and runs out of registers)
-#pragma unroll 1
-    for (int c = 0; c < HALF; c += 16) {
+    // dims d and d + HALF together, 16 of each per step
+    auto step = [&](int c, const uint32_t* lo_raw, const uint32_t* hi_raw) {
         float lo[16], hi[16];
-        if (c > 0) tc_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { lo[i] = __uint_as_float(cur[i]); hi[i] = __uint_as_float(cur[16 + i]); }
-        if (c + 16 < HALF) {
+        for (int i = 0; i < 16; ++i) { lo[i] = __uint_as_float(lo_raw[i]); hi[i] = __uint_as_float(hi_raw[i]); }
+        if (!KEEP && c + 16 < HALF) {
             tc_ld16_issue(col0 + (uint32_t)(c + 16), cur);
             tc_ld16_issue(col0 + (uint32_t)(HALF + c + 16), cur + 16);
         }
@@ -347,8 +386,9 @@ __device__ __forceinline__ void qkv_tokens_head(const QkvArgs& a, uint32_t col0,
             // the norm weight four values a request (every lane asks for the same address)
 #pragma unroll
             for (int i = 0; i < 16; i += 4) {
-                const float4 gl = __ldg(reinterpret_cast<const float4*>(gamma + c + i));
-                const float4 gh = __ldg(reinterpret_cast<const float4*>(gamma + HALF + c + i));
+                const float4 gl = KEEP ? *reinterpret_cast<const float4*>(gamma + c + i) : __ldg(reinterpret_cast<const float4*>(gamma + c + i));
+                const float4 gh = KEEP ? *reinterpret_cast<const float4*>(gamma + HALF + c + i)
+                                       : __ldg(reinterpret_cast<const float4*>(gamma + HALF + c + i));
                 lo[i] = __fmul_rn(__fmul_rn(lo[i], inv), gl.x); lo[i + 1] = __fmul_rn(__fmul_rn(lo[i + 1], inv), gl.y);
                 lo[i + 2] = __fmul_rn(__fmul_rn(lo[i + 2], inv), gl.z); lo[i + 3] = __fmul_rn(__fmul_rn(lo[i + 3], inv), gl.w);
                 hi[i] = __fmul_rn(__fmul_rn(hi[i], inv), gh.x); hi[i + 1] = __fmul_rn(__fmul_rn(hi[i + 1], inv), gh.y);
@@ -367,6 +407,18 @@ __device__ __forceinline__ void qkv_tokens_head(const QkvArgs& a, uint32_t col0,
         if (c + 16 < HALF) ask_cs(c + 16);                         // before this step's stores queue up
         if (dst_a) { store16(dst_a + c, lo); store16(dst_a + HALF + c, hi); }
         if (dst_b) { store16(dst_b + c, lo); store16(dst_b + HALF + c, hi); }
+    };
+    if (KEEP) {
+#pragma unroll
+        for (int c = 0; c < HALF; c += 16) step(c, all + c, all + HALF + c);
+    } else {
+        // the next step's columns are asked for before this step's arithmetic (the loop stays a loop: unrolled,
+        // the compiler moves all steps' loads of the norm weight to the front and runs out of registers)
+#pragma unroll 1
+        for (int c = 0; c < HALF; c += 16) {
+            if (c > 0) tc_ld_wait();
+            step(c, cur, cur + 16);                                // (its values are taken before the next columns are asked into it)
+        }
     }
 }
 
@@ -551,10 +603,11 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const
     return 0;
 }
 // ------------------------------------------------------------------- few tokens (up to 128)
-// The step's tokens on the accumulator's lanes (MMA M = 128: the rows of x, of which only the first
-// `tbox` are fetched; what the other rows of the operand hold is whatever lies behind the slot in
-// shared memory, and goes into accumulator lanes nobody reads), `bf` output features along its
-// columns.  A block owns features [bf * blockIdx.x, + bf) and walks the whole inner axis: one chain
+// The step's tokens on the accumulator's lanes (MMA M = 64 for up to 64 tokens, else 128: the rows of x,
+// of which only the first `tbox` are fetched; what the other rows of the operand hold is whatever lies
+// behind the slot in shared memory, and goes into accumulator lanes nobody reads), `bf` output features
+// along its columns.  (An MMA of few columns costs what its operands' bytes cost to read from shared
+// memory, about 64 a cycle, with a floor of ~46 cycles: hence as few rows as the tokens allow.)  A block owns features [bf * blockIdx.x, + bf) and walks the whole inner axis: one chain
 // per element.  Warp 4 issues the TMA loads, `gk` k-blocks per request and barrier (a three-dimensional
 // view of the matrices: k within a block, row, k-block) -- the weight slices of the first `stages`
 // groups before the wait on the kernel before (no kernel writes weights), the activations after it;
@@ -564,10 +617,13 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const
 #define GS_MAX_STAGES 16
 #define GS_BAR_BYTES 1024
 
+// rows of the MMA's M axis: 64 for up to 64 tokens (half the operand bytes per instruction), else 128
+__host__ __device__ inline int gs_mma_rows(int tbox) { return tbox <= 64 ? 64 : 128; }
+
 __host__ __device__ inline uint32_t gs_data_bytes(int tbox, int bf, int gk, int stages) {
     const uint32_t a_slot = (uint32_t)tbox * 128u, b_slot = (uint32_t)bf * 128u;
     uint32_t data = (uint32_t)(stages * gk) * (a_slot + b_slot);
-    const uint32_t reach = (uint32_t)(stages * gk - 1) * a_slot + GT_BM * 128u;   // the MMA reads 128 rows from every A slot
+    const uint32_t reach = (uint32_t)(stages * gk - 1) * a_slot + (uint32_t)gs_mma_rows(tbox) * 128u;   // the MMA reads that many rows from every A slot
     if (reach > data) data = reach;
     return (data + 1023u) & ~1023u;
 }
@@ -607,7 +663,13 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = *tmem_slot;
+#if defined(IDM_TRACE)
+    // (stamps of the four fused products of a layer side by side: residual with a short / long inner axis, SwiGLU, q/k/v)
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_gemm_trace_base = EPI == EPI_RESIDUAL ? (kb_total > 32 ? 10 : 0) : EPI == EPI_SWIGLU ? 20 : EPI == EPI_QKV ? 30 : 40;
+    __syncthreads();
+#endif
     if (threadIdx.x == 0) trace_stamp(0);                        // set-up done
+    const int trace_kind = EPI == EPI_RESIDUAL ? (kb_total > 32 ? 1 : 0) : EPI == EPI_SWIGLU ? 2 : EPI == EPI_QKV ? 3 : 4;
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
@@ -635,6 +697,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
             trace_stamp(1);                                      // early weight loads issued
             pdl_wait();
             trace_stamp(2);                                      // the kernel before is done
+            block_stamp(trace_kind, 0);
             for (int gi = 0; gi < early; ++gi) load_x(gi, gi);
             trace_stamp(3);                                      // early activation loads issued
             int s = 0; uint32_t phase = 0;                       // the ring goes round: stage and the parity of its use
@@ -650,7 +713,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(GT_BM, bf);
+            const uint32_t idesc = umma_idesc(gs_mma_rows(tbox), bf);
             const uint64_t a_desc0 = umma_desc_kmajor(a_base), b_desc0 = umma_desc_kmajor(b_base);
             const uint32_t a_step = a_slot >> 4, b_step = b_slot >> 4;     // descriptors count in 16 bytes
             bool ok = true;
@@ -659,7 +722,10 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
             for (int gi = 0; gi < n_groups && ok; ++gi) {
                 ok = mbar_wait(full_bar(s), phase, abort_flag, &g_gemm_error);
                 if (!ok) break;
-                if (gi == 0) trace_stamp(5);                     // first operands landed
+                if (gi == 0) { trace_stamp(5); block_stamp(trace_kind, 1); }   // first operands landed
+#if defined(IDM_TRACE)
+                if (blockIdx.x == 0 && gi < 64) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); g_gemm_mma_trace[trace_kind][gi][0] = t; }
+#endif
                 tc_fence_after();
                 const int nk = min(gk, kb_total - gi * gk);
                 uint64_t ad = a_desc, bd = b_desc;
@@ -669,6 +735,9 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
                     acc = 1u;
                     ad += a_step; bd += b_step;
                 }
+#if defined(IDM_TRACE)
+                if (blockIdx.x == 0 && gi < 64) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); g_gemm_mma_trace[trace_kind][gi][1] = t; }
+#endif
                 if (gi + stages < n_groups) tc_commit(empty_bar(s));      // the stage is free once these MMAs have read it
                 a_desc += (uint64_t)gk * a_step; b_desc += (uint64_t)gk * b_step;
                 if (++s == stages) { s = 0; phase ^= 1; a_desc = a_desc0; b_desc = b_desc0; }
@@ -678,11 +747,29 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 0-3): thread = token
-        const int t = warp * 32 + lane;
-        const bool live = t < n_tokens;
+        // (an accumulator of 128 rows has row i on lane i; one of 64 rows has row i on lane 32 (i / 16) + i % 16:
+        // sixteen tokens on the first sixteen lanes of each warp)
+        const bool m64 = gs_mma_rows(tbox) == 64;
+        const int t = m64 ? warp * 16 + lane : warp * 32 + lane;
+        const bool live = t < n_tokens && (!m64 || lane < 16);
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         pdl_wait();
-        if (warp * 32 < n_tokens) {                              // (a warp without tokens has nothing to read)
+        float* tab = reinterpret_cast<float*>(gen_base + bar_off + GS_BAR_BYTES);      // q/k/v: gq[hd], gk[hd], then a (cos, sin) row per token
+        if (EPI == EPI_QKV) {
+            // the norm weights and this block's tokens' rows of the rotation table go to shared memory while the
+            // product is being made (all four warps carry them): the epilogue then waits for no load
+            const QkvArgs& a = e.q;
+            const int hd_ = a.hd, rows = min(n_tokens, tbox);
+            for (int i = threadIdx.x; i < hd_; i += 128) {
+                tab[i] = a.gq ? a.gq[i] : 0.f;
+                tab[hd_ + i] = a.gk ? a.gk[i] : 0.f;
+            }
+            if (a.cs != nullptr)
+                for (int i = threadIdx.x; i < rows * hd_; i += 128)
+                    tab[2 * hd_ + i] = reinterpret_cast<const float*>(a.cs)[i];        // rows of hd / 2 (cos, sin) pairs: hd floats each
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        if ((m64 ? warp * 16 : warp * 32) < n_tokens) {          // (a warp without tokens has nothing to read)
             size_t place = 0;
             if (EPI == EPI_QKV) {
                 const QkvArgs& a = e.q;
@@ -693,8 +780,16 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
                     place = (size_t)page * a.n_kv * IDM_PAGE + r % IDM_PAGE;   // row of kv-head 0; kv-head g: + g * IDM_PAGE
                 }
             }
+            // RESIDUAL: the stream's old values of the first 16 features, asked for while the product is still being made
+            float4 old4[4];
+            const bool have_old = EPI == EPI_RESIDUAL && live && (n_features & 3) == 0 && f0 + 16 <= n_features;
+            if (have_old) {
+                const float4* p4 = reinterpret_cast<const float4*>(e.out + (size_t)t * n_features + f0);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) old4[i] = __ldcg(p4 + i);
+            }
             if (mbar_wait(accum_bar, 0, abort_flag, &g_gemm_error)) {
-                if (threadIdx.x == 0) trace_stamp(7);            // accumulator complete
+                if (threadIdx.x == 0) { trace_stamp(7); block_stamp(trace_kind, 2); }   // accumulator complete
                 tc_fence_after();
                 if (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
                     const bool vec = (n_features & 3) == 0;
@@ -710,7 +805,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
                             float4 o[4];
                             if (EPI == EPI_RESIDUAL) {
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) o[i] = p4[i];
+                                for (int i = 0; i < 4; ++i) o[i] = (c0 == 0 && have_old) ? old4[i] : p4[i];
                             }
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
@@ -725,36 +820,44 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
                         }
                     }
                 } else if (EPI == EPI_SWIGLU) {
-                    // the tile's columns are gate, up, gate, up, ... of the features f0 / 2 ..
+                    // the tile's columns are gate, up, gate, up, ... of the features f0 / 2 ..; 32 columns are asked
+                    // for before the first is waited for
 #pragma unroll 1
-                    for (int c0 = 0; c0 < bf; c0 += 16) {
-                        const int fg = (f0 + c0) >> 1;
-                        if (fg >= e.inter) break;
-                        float v[16];
-                        tc_ld16(tmem_d + lane_base + (uint32_t)c0, v);
+                    for (int c0 = 0; c0 < bf; c0 += 32) {
+                        if (((f0 + c0) >> 1) >= e.inter) break;
+                        uint32_t raw[32];
+                        tc_ld16_issue(tmem_d + lane_base + (uint32_t)c0, raw);
+                        if (c0 + 16 < bf) tc_ld16_issue(tmem_d + lane_base + (uint32_t)(c0 + 16), raw + 16);
+                        tc_ld_wait();
                         if (!live) continue;
-                        float y8[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) y8[i] = silu_mul(v[2 * i], v[2 * i + 1]);
-                        T* dst = e.y + (size_t)t * e.inter + fg;
-                        if ((e.inter & 7) == 0 && fg + 8 <= e.inter) {
-                            store8(dst, y8);
-                        } else {
+                        for (int h = 0; h < 2; ++h) {
+                            const int fg = (f0 + c0 + 16 * h) >> 1;
+                            if (c0 + 16 * h >= bf || fg >= e.inter) break;
+                            float y8[8];
 #pragma unroll
                             for (int i = 0; i < 8; ++i)
-                                if (fg + i < e.inter) from_f32(dst[i], y8[i]);
+                                y8[i] = silu_mul(__uint_as_float(raw[16 * h + 2 * i]), __uint_as_float(raw[16 * h + 2 * i + 1]));
+                            T* dst = e.y + (size_t)t * e.inter + fg;
+                            if ((e.inter & 7) == 0 && fg + 8 <= e.inter) {
+                                store8(dst, y8);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    if (fg + i < e.inter) from_f32(dst[i], y8[i]);
+                            }
                         }
                     }
                 } else if (EPI == EPI_QKV) {
                     const QkvArgs& a = e.q;
-                    const int hd = a.hd, half = hd >> 1, heads = a.n_q + 2 * a.n_kv;
-                    const float2* cs_row = a.cs + (size_t)(live ? t : 0) * half;
+                    const int hd = a.hd, heads = a.n_q + 2 * a.n_kv;
+                    const float2* cs_row = reinterpret_cast<const float2*>(tab + 2 * hd + (live ? t : 0) * hd);
                     for (int hh = 0; hh < bf / hd; ++hh) {
                         const int head = f0 / hd + hh;
                         if (head >= heads) break;
                         const uint32_t col0 = tmem_d + lane_base + (uint32_t)(hh * hd);
                         const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
-                        const float* gamma = is_q ? a.gq : (is_k ? a.gk : nullptr);
+                        const float* gamma = is_q ? (a.gq ? tab : nullptr) : (is_k ? (a.gk ? tab + hd : nullptr) : nullptr);
                         T* dst_a = nullptr; T* dst_b = nullptr;
                         if (live) {
                             if (is_q) {
@@ -767,15 +870,23 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
                             }
                         }
                         const bool rotate = (is_q || is_k) && a.cs != nullptr;
-                        if (hd == 128) qkv_tokens_head<128>(a, col0, gamma, rotate, cs_row, nullptr, n_tokens, dst_a, dst_b);
-                        else if (hd == 64) qkv_tokens_head<64>(a, col0, gamma, rotate, cs_row, nullptr, n_tokens, dst_a, dst_b);
-                        else qkv_tokens_head<32>(a, col0, gamma, rotate, cs_row, nullptr, n_tokens, dst_a, dst_b);
+                        if (hd == 128) qkv_tokens_head<128, true>(a, col0, gamma, rotate, cs_row, nullptr, n_tokens, dst_a, dst_b);
+                        else if (hd == 64) qkv_tokens_head<64, true>(a, col0, gamma, rotate, cs_row, nullptr, n_tokens, dst_a, dst_b);
+                        else qkv_tokens_head<32, true>(a, col0, gamma, rotate, cs_row, nullptr, n_tokens, dst_a, dst_b);
                     }
                 }
             }
         }
     }
-    if (threadIdx.x == 0) trace_stamp(8);                        // epilogue done
+    if (threadIdx.x == 0) { trace_stamp(8); block_stamp(trace_kind, 3); }   // epilogue done
+#if defined(IDM_TRACE)
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        const unsigned int i = atomicAdd(&g_gemm_log_n, 1u) & 2047u;
+        unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_gemm_log[i][0] = trace_kind; g_gemm_log[i][1] = g_gemm_trace[(g_gemm_trace_base + 0) & 63];
+        g_gemm_log[i][2] = g_gemm_trace[(g_gemm_trace_base + 2) & 63]; g_gemm_log[i][3] = t;
+    }
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 5) tmem_dealloc(tmem_d, (uint32_t)tmem_cols);
@@ -978,21 +1089,24 @@ static int launch_small(const void* x, const void* w, const GemmEpi& e, int M, i
     int bf = g_small_bf && g_small_bf % unit == 0 ? g_small_bf : small_slice(N, tbox, unit);
     if (EPI == EPI_QKV && bf < e.q.hd) bf = e.q.hd;
     const int kb_bytes = (tbox + bf) * 128;                       // one k-block of both operands
-    // k-blocks per request: about 32 KB, at most 8, and no more than a quarter of the inner axis
-    int gk = g_small_gk ? g_small_gk : 32 * 1024 / kb_bytes;
+    // k-blocks per request and barrier: up to 64 KB, at most 8, and no more than half of the inner axis (the thread
+    // that issues the MMAs spends ~0.2 us per barrier on waiting and bookkeeping, as much as eight MMAs take)
+    int gk = g_small_gk ? g_small_gk : 64 * 1024 / kb_bytes;
     if (gk > 8) gk = 8;
-    if (gk > kb_total / 4) gk = kb_total / 4;
+    if (gk > kb_total / 2) gk = kb_total / 2;
     if (gk < 1) gk = 1;
     const int grouped = (K % GT_BK == 0 && gk > 1) ? 1 : 0;
     if (!grouped && K % GT_BK) gk = 1;
     const int n_groups = (kb_total + gk - 1) / gk;
-    int stages = g_small_budget / (gk * kb_bytes);
+    int stages = (g_small_budget - (EPI == EPI_QKV ? (2 + tbox) * e.q.hd * 4 : 0)) / (gk * kb_bytes);
     if (stages < 2) stages = 2;
     if (stages > n_groups) stages = n_groups;
     if (stages > GS_MAX_STAGES) stages = GS_MAX_STAGES;
     int tmem_cols = 32;
     while (tmem_cols < bf) tmem_cols *= 2;
-    const int smem = (int)gs_data_bytes(tbox, bf, gk, stages) + GS_BAR_BYTES + 1024;      // + slack to align to 1024
+    // behind the barriers: the q/k/v epilogue's tables (two norm weights, a row of the rotation table per token)
+    const int tab_bytes = EPI == EPI_QKV ? (2 + tbox) * e.q.hd * 4 : 0;
+    const int smem = (int)gs_data_bytes(tbox, bf, gk, stages) + GS_BAR_BYTES + tab_bytes + 1024;   // + slack to align to 1024
     IDM_REQUIRE(smem <= 227 * 1024, "gemm: %d bytes of shared memory for %d tokens x %d features a block", smem, tbox, bf);
     static int configured = 0;
     if (smem > configured) {

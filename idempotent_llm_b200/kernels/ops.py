@@ -87,6 +87,9 @@ SIGNATURES = {
     "idm_wait_probe": (c_int, "qipp"),
     # only in a library compiled with -DIDM_TRACE (time stamps from inside two kernels: a measuring aid)
     "idm_gemm_trace_read": (c_int, "p"),
+    "idm_gemm_block_trace_read": (c_int, "p"),
+    "idm_gemm_log_read": (c_int, "pi"),
+    "idm_gemm_mma_trace_read": (c_int, "p"),
     "idm_attention_tc_trace_read": (c_int, "p"),
 }
 
