@@ -114,6 +114,70 @@ __device__ __forceinline__ void store_out16(T* dst, const float (&o)[16], float 
     *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
+// Where run `run` of a tile and head group leaves its result: rows_cap rows of (HD + 2) floats, as
+// [HD / 4][rows_cap] pieces of four dims and then [rows_cap] pairs (m, l).
+__device__ __forceinline__ size_t run_part_floats(int rows_cap, int hd) {
+    return ((size_t)rows_cap * (hd + 2) + 3) & ~(size_t)3;       // (16-byte pieces)
+}
+
+// The end of a block that has written its run's result to scratch, called by its 128 row threads
+// (r = 0 .. 127; named barrier 1): the arrival is counted, and the block that comes last for the tile
+// and head group folds all runs, in the order of the runs whoever it is, divides by the sum and writes
+// the output rows.  (A block whose wait ran out, ok == false, still counts: the error is reported, the
+// result is wrong, and nobody waits for anybody for ever.)
+template <int HD>
+__device__ __forceinline__ void count_and_fold_runs(const AttnTcArgs& a, const float* part0, size_t part_floats, int n_runs,
+                                                    int rows_valid, int tok0, int head0, int counter_index,
+                                                    volatile int* last_flag, int r, bool ok) {
+    const int cap = a.rows_cap, gs = a.gp_shift, gp = 1 << gs;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (r == 0) {
+        int* counter = a.counters + counter_index;
+        const int is_last = atomicAdd(counter, 1) == n_runs - 1;
+        if (is_last) *counter = 0;                                 // ready for the next launch
+        *last_flag = is_last;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (!*last_flag || !ok) return;
+    __threadfence();
+    // the 128 threads share the tile's (row, four dims) pieces; each folds its piece over the runs
+    for (int w = r; w < (HD / 4) * cap; w += 128) {
+        const int row = w % cap, c4 = w / cap;
+        if (row >= rows_valid) continue;
+        float M = -INFINITY, L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i0 = 0; i0 < n_runs; i0 += 8) {                   // eight runs' loads are in flight together; the fold is a chain
+            float2 ml[8];
+            float4 o[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (i0 + u < n_runs) {
+                    const float* pi = part0 + (size_t)(i0 + u) * part_floats;
+                    ml[u] = __ldcg(reinterpret_cast<const float2*>(pi + (size_t)HD * cap) + row);
+                    o[u] = __ldcg(reinterpret_cast<const float4*>(pi) + w);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (i0 + u < n_runs) {
+                    float a_, b_;
+                    fold_coeffs(M, L, ml[u].x, ml[u].y, a_, b_);
+                    acc.x = fold_value(acc.x, a_, o[u].x, b_); acc.y = fold_value(acc.y, a_, o[u].y, b_);
+                    acc.z = fold_value(acc.z, a_, o[u].z, b_); acc.w = fold_value(acc.w, a_, o[u].w, b_);
+                }
+            }
+        }
+        const float inv = __fdiv_rn(1.0f, L);
+        T* dst = a.out + ((size_t)(tok0 + (row >> gs)) * a.n_q + head0 + (row & (gp - 1))) * HD + c4 * 4;
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(__fmul_rn(acc.x, inv), __fmul_rn(acc.y, inv));
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(__fmul_rn(acc.z, inv), __fmul_rn(acc.w, inv));
+        *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo),
+                                                    *reinterpret_cast<const uint32_t*>(&hi));
+    }
+}
+
+#include "attention_few_rows.cuh"
+
 template <int HD>
 __global__ void __launch_bounds__(AP_THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -428,7 +492,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // not the two barriers and the count: the error is reported, the result is wrong, and nobody
             // waits for anybody for ever.)
             const int cap = a.rows_cap;
-            const size_t part_floats = ((size_t)cap * (HD + 2) + 3) & ~(size_t)3;   // (16-byte pieces)
+            const size_t part_floats = run_part_floats(cap, HD);
             float* part0 = a.parts + (size_t)(tile * n_hg + hg) * a.max_runs * part_floats;
             if (ok && warp_live) {
                 tc_fence_after();
@@ -450,53 +514,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (r < cap) reinterpret_cast<float2*>(mine + (HD / 4) * cap)[r] = make_float2(m_ref, l);
                 __threadfence();
             }
-            volatile int* last_flag = (volatile int*)(gbase + S::BAR_OFF + 128);
-            asm volatile("bar.sync 1, 128;" ::: "memory");         // the four softmax warps
-            if (r == 0) {
-                int* counter = a.counters + tile * n_hg + hg;
-                const int is_last = atomicAdd(counter, 1) == n_runs - 1;
-                if (is_last) *counter = 0;                         // ready for the next launch
-                *last_flag = is_last;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 0) attn_stamp(41);                // this run's result is in scratch and counted
-            if (*last_flag && ok) {
-                __threadfence();
-                // the block's 128 threads share the tile's (row, four dims) pieces; each folds its piece over the runs
-                for (int w = r; w < (HD / 4) * cap; w += AP_BM) {
-                    const int row = w % cap, c4 = w / cap;
-                    if (row >= rows_valid) continue;
-                    float M = -INFINITY, L = 0.f;
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int i0 = 0; i0 < n_runs; i0 += 8) {       // eight runs' loads are in flight together; the fold is a chain
-                        float2 ml[8];
-                        float4 o[8];
-#pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            if (i0 + u < n_runs) {
-                                const float* pi = part0 + (size_t)(i0 + u) * part_floats;
-                                ml[u] = __ldcg(reinterpret_cast<const float2*>(pi + (size_t)HD * cap) + row);
-                                o[u] = __ldcg(reinterpret_cast<const float4*>(pi) + w);
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            if (i0 + u < n_runs) {
-                                float a_, b_;
-                                fold_coeffs(M, L, ml[u].x, ml[u].y, a_, b_);
-                                acc.x = fold_value(acc.x, a_, o[u].x, b_); acc.y = fold_value(acc.y, a_, o[u].y, b_);
-                                acc.z = fold_value(acc.z, a_, o[u].z, b_); acc.w = fold_value(acc.w, a_, o[u].w, b_);
-                            }
-                        }
-                    }
-                    const float inv = __fdiv_rn(1.0f, L);
-                    T* dst = a.out + ((size_t)(tok0 + (row >> gs)) * a.n_q + head0 + (row & (gp - 1))) * HD + c4 * 4;
-                    const __nv_bfloat162 lo = __floats2bfloat162_rn(__fmul_rn(acc.x, inv), __fmul_rn(acc.y, inv));
-                    const __nv_bfloat162 hi = __floats2bfloat162_rn(__fmul_rn(acc.z, inv), __fmul_rn(acc.w, inv));
-                    *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo),
-                                                                *reinterpret_cast<const uint32_t*>(&hi));
-                }
-            }
+            count_and_fold_runs<HD>(a, part0, part_floats, n_runs, rows_valid, tok0, head0, tile * n_hg + hg,
+                                    (volatile int*)(gbase + S::BAR_OFF + 128), r, ok);
+            if (threadIdx.x == 0) attn_stamp(41);                // this run's result is in scratch, counted, and folded if it was the last
         } else if (ok && warp_live) {
             // the last (or only) run folded onto what came before, then divided by the sum
             tc_fence_after();
@@ -545,6 +565,8 @@ static int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mk, con
     IDM_LAUNCH_CHECK("attention_tc");
     return 0;
 }
+
+static int g_attn_few_rows = 1;
 
 extern "C" int idm_attention_tc_supports(int hd) { return hd == 64 || hd == 128; }
 
@@ -613,8 +635,18 @@ extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, co
     a.n_q = n_q; a.n_kv = n_kv; a.gp_shift = gs; a.scale_log2 = scale * 1.4426950408889634f;
     a.run_blocks = run_blocks; a.max_runs = max_runs; a.rows_cap = rows_cap;
     a.counters = (int*)scratch; a.parts = scratch ? scratch + AP_COUNTERS : nullptr;
+    if (g_attn_few_rows && attention_few_rows_can(hd, rows_cap, run_blocks, max_runs))
+        return hd == 64 ? launch_attention_few_rows<64>(mk, mv, a, (const T*)q, n_tiles, stream)
+                        : launch_attention_few_rows<128>(mk, mv, a, (const T*)q, n_tiles, stream);
     return hd == 64 ? launch_attention_tc<64>(mq, mk, mv, a, n_tiles, stream)
                     : launch_attention_tc<128>(mq, mk, mv, a, n_tiles, stream);
+}
+
+// 0: tiles of few rows go through the tcgen05 kernel as well (tests compare the two bit for bit); returns the old setting
+extern "C" int idm_attention_tc_set_few_rows(int on) {
+    const int old = g_attn_few_rows;
+    g_attn_few_rows = on;
+    return old;
 }
 
 extern "C" int idm_attention_tc_status() {

@@ -75,6 +75,7 @@ SIGNATURES = {
     "idm_attention_tc_scratch_floats": (c_longlong, "iiiiii"),
     "idm_attention_tc": (c_int, "ppppipippippppiiiifiiipp"),
     "idm_attention_tc_status": (c_int, ""),
+    "idm_attention_tc_set_few_rows": (c_int, "i"),
     "idm_gemm_f32": (c_int, "pppiiip"),
     "idm_gemm_set_small": (None, "iii"),
     "idm_gemm_set_small_max": (None, "i"),
@@ -320,6 +321,11 @@ class Kernels:
             hd, scale, R, max_runs, rows_cap, _p(scratch),
             self._stream()))
         return out
+
+    def attention_tc_few_rows(self, on: bool) -> bool:
+        """Whether tiles of at most 16 rows take the kernel made for them (the default) or the one all
+        other tiles take; returns the old setting.  Tests compare the two bit for bit."""
+        return bool(self.lib.idm_attention_tc_set_few_rows(1 if on else 0))
 
     def attention_tc_status(self) -> int:
         return 0 if self.dtype == torch.float32 else self.lib.idm_attention_tc_status()

@@ -237,7 +237,7 @@ def test_attention_tensor_core_kernel(kernels, n_q, n_kv, hd):
 
 
 @pytest.mark.parametrize("run_blocks", [8, 3, 2, 1])
-@pytest.mark.parametrize("n_q,n_kv,hd", [(2, 1, 128), (3, 3, 64), (8, 2, 128)])
+@pytest.mark.parametrize("n_q,n_kv,hd", [(2, 1, 128), (3, 3, 64), (8, 2, 128), (16, 1, 64)])
 def test_attention_tensor_core_runs_and_cuts(kernels, run_blocks, n_q, n_kv, hd):
     """A row's keys are worked in runs of key blocks that are folded in ascending order.  The bits of a row
     must not depend on who works the runs (one block walking them, or a block per run meeting in
@@ -304,6 +304,52 @@ def test_attention_tensor_core_runs_and_cuts(kernels, run_blocks, n_q, n_kv, hd)
         assert K.attention_tc_status() == 0
     finally:
         K.attention_run_blocks = old
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd", [(16, 8, 128), (4, 4, 64), (32, 2, 128), (12, 4, 64), (8, 1, 128)])
+def test_attention_of_single_tokens_has_the_tile_kernel_s_bits(kernels, n_q, n_kv, hd):
+    """Steps of single tokens have a kernel of their own (a run's key blocks side by side on mma.sync
+    fragments).  It must give every row the bits of the kernel that all other steps take: lengths on
+    both sides of a page's and a run's border, free pages and page tails full of NaN, one query that
+    looks at a single far key and one at its own (the last) key."""
+    K = kernels("bfloat16")
+    lens = [1, 2, 63, 64, 65, 511, 512, 513, 1024, 1300, 3000]
+    cache, slots, ks, vs = _cache_with(K, "bfloat16", n_kv, hd, None, lens, seed=400, max_tokens=64 * 160)
+    kv = cache.view(0)
+    scale = 1.0 / math.sqrt(hd)
+    q = _randn(len(lens), n_q, hd, seed=410)
+    q[10, 0] = ks[10][70, 0] * 4.0                         # the longest sequence's first head looks at key 70
+    q[9, n_q - 1] = ks[9][1299, n_kv - 1] * 4.0            # a query that looks at its own position's key
+    qd = q.to(torch.bfloat16).cuda()
+    starts = [L - 1 for L in lens]
+    packed, n, q_lens = pack_step_host(slots, starts, [[0]] * len(lens))
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, starts)
+    assert K.attention_tc_few_rows(True) is True           # (the default)
+    try:
+        mine = K.attention_tc(qd, kv, ctx, scale).view(-1, n_q, hd)
+        mine2 = K.attention_tc(qd, kv, ctx, scale).view(-1, n_q, hd)
+        K.attention_tc_few_rows(False)
+        tile = K.attention_tc(qd, kv, ctx, scale).view(-1, n_q, hd)
+        walk = K.attention_tc(qd, kv, ctx, scale, through_scratch=False).view(-1, n_q, hd)
+    finally:
+        K.attention_tc_few_rows(True)
+    torch.cuda.synchronize()
+    assert K.attention_tc_status() == 0, "a bounded wait inside the kernel ran out"
+    assert torch.isfinite(mine).all(), "stale page contents leaked into the result"
+    for i in range(len(lens)):
+        assert torch.equal(mine[i], tile[i]), f"length {lens[i]}: other bits than the tile kernel's"
+    assert torch.equal(mine, mine2) and torch.equal(tile, walk)
+    for i, L in enumerate(lens):
+        ref = _attn_ref(qd[i].double().cpu(), ks[i], vs[i], scale, None, L - 1)
+        assert helpers.rel_err(mine[i], ref) < KTOL["bfloat16"], f"length {L}"
+    assert (mine[10, 0].double().cpu() - vs[10][70, 0]).abs().max() < 0.05, "the far key did not dominate"
+    assert (mine[9, n_q - 1].double().cpu() - vs[9][1299, n_kv - 1]).abs().max() < 0.05
+    # a shorter step: other blocks, other counters, the same rows
+    sub = [2, 7, 10]
+    packed, n3, ql3 = pack_step_host([slots[i] for i in sub], [starts[i] for i in sub], [[0]] * 3)
+    ctx3 = context_from_packed(packed.cuda(), n3, [slots[i] for i in sub], ql3, [starts[i] for i in sub], max_kv_len=4096)
+    part = K.attention_tc(qd[sub].contiguous(), kv, ctx3, scale).view(-1, n_q, hd)
+    assert torch.equal(part, mine[sub]), "a row's result depends on what else the step holds"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
