@@ -54,8 +54,18 @@ __device__ __forceinline__ void attn_stamp(int i) {
 extern "C" int idm_attention_tc_trace_read(unsigned long long* out) {
     return (int)cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(unsigned long long) * 64);
 }
+// every block of the few-rows kernel: [block][item it worked on, up to 4][stamp]
+__device__ unsigned long long g_attn_item_trace[512][4][8];
+__device__ __forceinline__ void attn_item_stamp(int nth, int i) {
+    if (blockIdx.x < 512 && nth >= 0 && nth < 4) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); g_attn_item_trace[blockIdx.x][nth][i] = t; }
+}
+extern "C" int idm_attention_item_trace_read(unsigned long long* out, int clear) {
+    if (clear) return (int)cudaMemcpyToSymbol(g_attn_item_trace, out, sizeof(unsigned long long) * 512 * 4 * 8);
+    return (int)cudaMemcpyFromSymbol(out, g_attn_item_trace, sizeof(unsigned long long) * 512 * 4 * 8);
+}
 #else
 __device__ __forceinline__ void attn_stamp(int) {}
+__device__ __forceinline__ void attn_item_stamp(int, int) {}
 #endif
 
 struct AttnTcArgs {
@@ -120,28 +130,13 @@ __device__ __forceinline__ size_t run_part_floats(int rows_cap, int hd) {
     return ((size_t)rows_cap * (hd + 2) + 3) & ~(size_t)3;       // (16-byte pieces)
 }
 
-// The end of a block that has written its run's result to scratch, called by its 128 row threads
-// (r = 0 .. 127; named barrier 1): the arrival is counted, and the block that comes last for the tile
-// and head group folds all runs, in the order of the runs whoever it is, divides by the sum and writes
-// the output rows.  (A block whose wait ran out, ok == false, still counts: the error is reported, the
-// result is wrong, and nobody waits for anybody for ever.)
+// All runs of a tile and head group folded in the order of the runs, divided by the sum, written to
+// the output rows; `n_threads` threads (r = 0 .. n_threads - 1) share the tile's (row, four dims) pieces.
 template <int HD>
-__device__ __forceinline__ void count_and_fold_runs(const AttnTcArgs& a, const float* part0, size_t part_floats, int n_runs,
-                                                    int rows_valid, int tok0, int head0, int counter_index,
-                                                    volatile int* last_flag, int r, bool ok) {
+__device__ __forceinline__ void fold_runs_and_store(const AttnTcArgs& a, const float* part0, size_t part_floats, int n_runs,
+                                                    int rows_valid, int tok0, int head0, int r, int n_threads) {
     const int cap = a.rows_cap, gs = a.gp_shift, gp = 1 << gs;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (r == 0) {
-        int* counter = a.counters + counter_index;
-        const int is_last = atomicAdd(counter, 1) == n_runs - 1;
-        if (is_last) *counter = 0;                                 // ready for the next launch
-        *last_flag = is_last;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (!*last_flag || !ok) return;
-    __threadfence();
-    // the 128 threads share the tile's (row, four dims) pieces; each folds its piece over the runs
-    for (int w = r; w < (HD / 4) * cap; w += 128) {
+    for (int w = r; w < (HD / 4) * cap; w += n_threads) {
         const int row = w % cap, c4 = w / cap;
         if (row >= rows_valid) continue;
         float M = -INFINITY, L = 0.f;
@@ -174,6 +169,27 @@ __device__ __forceinline__ void count_and_fold_runs(const AttnTcArgs& a, const f
         *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo),
                                                     *reinterpret_cast<const uint32_t*>(&hi));
     }
+}
+
+// The end of a block that has written its run's result to scratch, called by its 128 row threads
+// (r = 0 .. 127; named barrier 1): the arrival is counted, and the block that comes last for the tile
+// and head group folds all runs, whoever it is.  (A block whose wait ran out, ok == false, still counts:
+// the error is reported, the result is wrong, and nobody waits for anybody for ever.)
+template <int HD>
+__device__ __forceinline__ void count_and_fold_runs(const AttnTcArgs& a, const float* part0, size_t part_floats, int n_runs,
+                                                    int rows_valid, int tok0, int head0, int counter_index,
+                                                    volatile int* last_flag, int r, bool ok) {
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (r == 0) {
+        int* counter = a.counters + counter_index;
+        const int is_last = atomicAdd(counter, 1) == n_runs - 1;
+        if (is_last) *counter = 0;                                 // ready for the next launch
+        *last_flag = is_last;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (!*last_flag || !ok) return;
+    __threadfence();
+    fold_runs_and_store<HD>(a, part0, part_floats, n_runs, rows_valid, tok0, head0, r, 128);
 }
 
 #include "attention_few_rows.cuh"
@@ -635,7 +651,7 @@ extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, co
     a.n_q = n_q; a.n_kv = n_kv; a.gp_shift = gs; a.scale_log2 = scale * 1.4426950408889634f;
     a.run_blocks = run_blocks; a.max_runs = max_runs; a.rows_cap = rows_cap;
     a.counters = (int*)scratch; a.parts = scratch ? scratch + AP_COUNTERS : nullptr;
-    if (g_attn_few_rows && attention_few_rows_can(hd, rows_cap, run_blocks, max_runs))
+    if (g_attn_few_rows && attention_few_rows_can(hd, rows_cap, run_blocks, max_runs, groups))
         return hd == 64 ? launch_attention_few_rows<64>(mk, mv, a, (const T*)q, n_tiles, stream)
                         : launch_attention_few_rows<128>(mk, mv, a, (const T*)q, n_tiles, stream);
     return hd == 64 ? launch_attention_tc<64>(mq, mk, mv, a, n_tiles, stream)

@@ -37,8 +37,9 @@ int idm_fail(const char* fmt, ...);   // records the message, returns 1
     } while (0)
 
 // ------------------------------------------- programmatic dependent launch
-// Every kernel of this library starts with pdl_launch_dependents() and executes pdl_wait() before
-// its first access to global memory that an earlier kernel may have written (or may still read).
+// Every kernel of this library starts with pdl_launch_dependents() (but the one that moves a captured
+// step's lengths and positions on, which lets nothing start before it is done) and executes pdl_wait()
+// before its first access to global memory that an earlier kernel may have written (or may still read).
 // Launched with the programmatic-serialization attribute, the next kernel's blocks are scheduled
 // while this one still runs and do their set-up (and, in the matrix product, fetch weights, which
 // no kernel writes) before the wait returns.  Without the attribute both instructions do nothing.

@@ -110,7 +110,9 @@ extern "C" int idm_sample(const float* logits, int n_rows, int V, float temperat
 __global__ void decode_advance_kernel(int* tokens, int* positions, int* q_start, int* kv_len,
                                       const int* sampled, int* history, int* step_counter, int n_seqs,
                                       int max_history) {
-    pdl_launch_dependents();
+    // (No early launch of what follows: the kernels of the next step read the lengths and positions
+    // before their own wait for the kernel before them, as things that were there before the step began.
+    // With this kernel finished before anything of the next step starts, they are.)
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int step = *step_counter;

@@ -92,6 +92,7 @@ SIGNATURES = {
     "idm_gemm_log_read": (c_int, "pi"),
     "idm_gemm_mma_trace_read": (c_int, "p"),
     "idm_attention_tc_trace_read": (c_int, "p"),
+    "idm_attention_item_trace_read": (c_int, "pi"),
 }
 
 
@@ -133,7 +134,7 @@ class Kernels:
         self.attention_impl = os.environ.get("IDM_ATTENTION", "tcgen05")
         # key blocks (of 64) of a run of the tensor-core kernel: each run starts its sums from nothing and
         # the runs are folded in ascending order, so this number is part of the arithmetic's definition
-        self.attention_run_blocks = 8
+        self.attention_run_blocks = 4
         self.page = L.idm_page_tokens()
 
     # ------------------------------------------------------------------ helpers
@@ -328,7 +329,15 @@ class Kernels:
         return bool(self.lib.idm_attention_tc_set_few_rows(1 if on else 0))
 
     def attention_tc_status(self) -> int:
-        return 0 if self.dtype == torch.float32 else self.lib.idm_attention_tc_status()
+        """Non-zero if a bounded wait inside an attention kernel ran out since the last call (the result
+        of that launch is wrong).  The kernels' counters in scratch may then be left standing, so the
+        scratch is cleared."""
+        if self.dtype == torch.float32:
+            return 0
+        status = self.lib.idm_attention_tc_status()
+        if status and "attention_tc" in self._scratch:
+            self._scratch["attention_tc"].zero_()
+        return status
 
     def attention_generic(self, q, kv, ctx, k_new, v_new, scale: float, window) -> torch.Tensor:
         """The general kernel, whatever the step's shape (tests compare the special kernels with it)."""
