@@ -51,6 +51,12 @@ __device__ __forceinline__ bool af_bar_any(bool mine) {
                  : "=r"(r) : "r"((uint32_t)mine) : "memory");
     return r != 0;
 }
+// one arrival more at a counter, with release and acquire at the scope of the GPU; the count before
+__device__ __forceinline__ int af_count(int* counter) {
+    int old;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+    return old;
+}
 __device__ __forceinline__ void af_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // A tile and head group whose runs have all arrived: to be folded
@@ -181,10 +187,11 @@ attention_few_rows_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                     if (!waited) { pdl_wait(); waited = true; }
                     int is_last = 0;
                     if (lane == 0) {
-                        // (the working warps' stores, seen here through the barrier, are ordered before the count by this fence)
-                        __threadfence();
+                        // (release: the working warps' stores, seen here through the barrier, come before the count;
+                        // acquire: whoever counts last has the other blocks' results behind it, and so have the
+                        // working warps it hands the fold to through the item's barrier)
                         int* counter = a.counters + prev.tile * n_hg + prev.hg;
-                        is_last = atomicAdd(counter, 1) == prev.n_runs - 1;
+                        is_last = af_count(counter) == prev.n_runs - 1;
                         if (is_last) *counter = 0;               // ready for the next launch
                     }
                     if (__shfl_sync(0xffffffffu, is_last, 0)) job = prev;
@@ -216,7 +223,16 @@ attention_few_rows_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(q_full(st));
-            if (item < 0) break;
+            if (item < 0) {
+                // No more items for anybody.  The block whose scheduler comes here last puts the two counters of
+                // the items back to zero for the next launch.  (After a wait that ran out counters may be left
+                // standing: the caller, told by the status word, clears the scratch.)
+                if (lane == 0 && atomicAdd(a.counters + AF_EXIT_COUNTER, 1) == (int)gridDim.x - 1) {
+                    a.counters[AF_EXIT_COUNTER] = 0;
+                    a.counters[AF_WORK_COUNTER] = 0;
+                }
+                break;
+            }
             ok = complete(pending);
             prev.n_runs = n_runs; prev.tile = tile; prev.hg = hg; prev.rows_valid = toks_valid << gs; prev.tok0 = a.cu_q[seq] + tstart;
             prev_st = st; prev_parity = (qn / AF_QUEUE) & 1;
@@ -305,7 +321,6 @@ attention_few_rows_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             for (int f = 0; f < 2; ++f) {
                 const int f_runs = d->fold[f].n_runs;
                 if (f_runs == 0) continue;
-                __threadfence();                                   // (the scheduler warp saw all arrivals; now their results)
                 const int f_tile = d->fold[f].tile, f_hg = d->fold[f].hg;
                 const size_t part_floats = run_part_floats(a.rows_cap, HD);
                 const float* part0 = a.parts + (size_t)(f_tile * n_hg + f_hg) * a.max_runs * part_floats;
@@ -601,16 +616,6 @@ attention_few_rows_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         __syncwarp();
         if (lane == 0) { mbar_arrive(d_done(qst)); mbar_arrive(q_empty(qst)); }
         if (tid == 0) { attn_stamp(42); attn_item_stamp(qn, 4); }
-    }
-    // The block that leaves last puts the two counters back to zero for the next launch.  (Every block
-    // has seen the items run out by then.  After a wait that ran out the arrival counters of tiles may
-    // be left standing: the caller, told by the status word, clears the scratch.)
-    if (tid == 0) {
-        if (atomicAdd(a.counters + AF_EXIT_COUNTER, 1) == (int)gridDim.x - 1) {
-            a.counters[AF_EXIT_COUNTER] = 0;
-            a.counters[AF_WORK_COUNTER] = 0;
-            __threadfence();
-        }
     }
 }
 

@@ -131,43 +131,40 @@ __device__ __forceinline__ size_t run_part_floats(int rows_cap, int hd) {
 }
 
 // All runs of a tile and head group folded in the order of the runs, divided by the sum, written to
-// the output rows; `n_threads` threads (r = 0 .. n_threads - 1) share the tile's (row, four dims) pieces.
+// the output rows; `n_threads` threads (r = 0 .. n_threads - 1) share the tile's (row, two dims) pieces.
+#define FOLD_BATCH 8
 template <int HD>
 __device__ __forceinline__ void fold_runs_and_store(const AttnTcArgs& a, const float* part0, size_t part_floats, int n_runs,
                                                     int rows_valid, int tok0, int head0, int r, int n_threads) {
     const int cap = a.rows_cap, gs = a.gp_shift, gp = 1 << gs;
-    for (int w = r; w < (HD / 4) * cap; w += n_threads) {
-        const int row = w % cap, c4 = w / cap;
+    for (int w = r; w < (HD / 2) * cap; w += n_threads) {
+        const int half = w & 1, row = (w >> 1) % cap, c4 = (w >> 1) / cap;
         if (row >= rows_valid) continue;
+        const size_t at = ((size_t)c4 * cap + row) * 4 + 2 * half;
         float M = -INFINITY, L = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int i0 = 0; i0 < n_runs; i0 += 8) {                   // eight runs' loads are in flight together; the fold is a chain
-            float2 ml[8];
-            float4 o[8];
+        float2 acc = make_float2(0.f, 0.f);
+        for (int i0 = 0; i0 < n_runs; i0 += FOLD_BATCH) {          // so many runs' loads are in flight together; the fold is a chain
+            float2 ml[FOLD_BATCH], o[FOLD_BATCH];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < FOLD_BATCH; ++u) {
                 if (i0 + u < n_runs) {
                     const float* pi = part0 + (size_t)(i0 + u) * part_floats;
                     ml[u] = __ldcg(reinterpret_cast<const float2*>(pi + (size_t)HD * cap) + row);
-                    o[u] = __ldcg(reinterpret_cast<const float4*>(pi) + w);
+                    o[u] = __ldcg(reinterpret_cast<const float2*>(pi + at));
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < FOLD_BATCH; ++u) {
                 if (i0 + u < n_runs) {
                     float a_, b_;
                     fold_coeffs(M, L, ml[u].x, ml[u].y, a_, b_);
                     acc.x = fold_value(acc.x, a_, o[u].x, b_); acc.y = fold_value(acc.y, a_, o[u].y, b_);
-                    acc.z = fold_value(acc.z, a_, o[u].z, b_); acc.w = fold_value(acc.w, a_, o[u].w, b_);
                 }
             }
         }
         const float inv = __fdiv_rn(1.0f, L);
-        T* dst = a.out + ((size_t)(tok0 + (row >> gs)) * a.n_q + head0 + (row & (gp - 1))) * HD + c4 * 4;
-        const __nv_bfloat162 lo = __floats2bfloat162_rn(__fmul_rn(acc.x, inv), __fmul_rn(acc.y, inv));
-        const __nv_bfloat162 hi = __floats2bfloat162_rn(__fmul_rn(acc.z, inv), __fmul_rn(acc.w, inv));
-        *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo),
-                                                    *reinterpret_cast<const uint32_t*>(&hi));
+        T* dst = a.out + ((size_t)(tok0 + (row >> gs)) * a.n_q + head0 + (row & (gp - 1))) * HD + c4 * 4 + 2 * half;
+        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(__fmul_rn(acc.x, inv), __fmul_rn(acc.y, inv));
     }
 }
 

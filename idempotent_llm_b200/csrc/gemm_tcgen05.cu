@@ -64,7 +64,6 @@ __device__ __forceinline__ void block_stamp(int kind, int i) {
     if (blockIdx.x < 512) {
         unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
         g_gemm_block_trace[kind][blockIdx.x][i] = t;
-        if (i == 0) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); g_gemm_block_trace[kind][blockIdx.x][4] = sm; }
     }
 }
 extern "C" int idm_gemm_block_trace_read(unsigned long long* out) {
@@ -651,6 +650,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int f0 = blockIdx.x * bf;
     const int n_groups = (kb_total + gk - 1) / gk;
+    if (threadIdx.x == 0) block_stamp(EPI == EPI_RESIDUAL ? (kb_total > 32 ? 1 : 0) : EPI == EPI_SWIGLU ? 2 : EPI == EPI_QKV ? 3 : 4, 4);   // the block is there
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
