@@ -299,7 +299,7 @@ def main(argv=None) -> int:
     r.set_defaults(fn=cmd_random)
 
     k = sub.add_parser("kernel-bench", help="one kernel alone at a preset's layer sizes")
-    k.add_argument("--kernel", required=True, choices=["attention_single", "attention_single_mma", "attention_prompt", "gemm", "gemm_fused"])
+    k.add_argument("--kernel", required=True, choices=["attention_single", "attention_single_mma", "attention_prompt", "gemm", "gemm_fused", "step_trace"])
     k.add_argument("--size", default="qwen3-0.6b")
     k.add_argument("--batch", type=int, default=8)
     k.add_argument("--context", type=int, default=3000)

@@ -104,6 +104,77 @@ def run(args) -> int:
             fl, byt = 2.0 * M * N * Kd, 2.0 * N * Kd
             print(f"gemm {name} [{M} x {Kd}] . [{N} x {Kd}]^T: {t * 1e6:.1f} us, {fl / t / 1e12:.1f} TFLOP/s, "
                   f"weights {byt / t / 1e9:.0f} GB/s")
+    elif args.kernel == "step_trace":
+        return step_trace(args)
     else:
         raise ValueError(f"unknown kernel {args.kernel!r}")
+    return 0
+
+
+def step_trace(args) -> int:
+    """Where a captured single-token step's time goes, from time stamps the kernels take themselves when
+    the library is compiled with ``-DIDM_TRACE`` (``IDM_EXTRA_NVCC_FLAGS=-DIDM_TRACE IDM_BUILD_DIR=<a
+    folder of its own>``): the last layer's four products and its attention on one clock, and the
+    phases of every work item of the attention kernel.  The stamps cost a few percent of the step."""
+    import ctypes
+    import numpy as np
+    from . import from_random
+    from .config.presets import preset
+    B = args.batch
+    lm = from_random(preset(args.size), seed=0, dtype="bfloat16", max_tokens=B * args.capacity, max_seqs=B,
+                     max_seq_len=args.capacity)
+    eng, L = lm.engine, lm.model.rt.kernels.lib
+    if not hasattr(L, "idm_gemm_block_trace_read"):
+        raise SystemExit("step_trace needs a library compiled with IDM_EXTRA_NVCC_FLAGS=-DIDM_TRACE")
+    for name in ("idm_gemm_block_trace_read", "idm_attention_item_trace_read"):
+        getattr(L, name).restype = ctypes.c_int
+    L.idm_gemm_block_trace_read.argtypes = [ctypes.c_void_p]
+    L.idm_attention_item_trace_read.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    g = torch.Generator().manual_seed(0)
+    slots = [eng.open() for _ in range(B)]
+    cur = []
+    for s in slots:
+        ids = torch.randint(100, 50000, (args.context,), generator=g).tolist()
+        cur.append(eng.sample(eng.step([(s, ids)]), 0.0, 0, [0], [0])[0])
+    step = lambda i: eng.step_sample([(s, [t]) for s, t in zip(slots, cur)], 0.0, 0, list(range(B)), [i] * B)[0]
+    for i in range(6):
+        cur = step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.reps):
+        cur = step(10 + i)
+    e1.record(); torch.cuda.synchronize()
+    print(f"{args.size} batch {B} context {args.context}: {e0.elapsed_time(e1) / args.reps:.3f} ms per step with the stamps in")
+    items = np.zeros((512, 4, 8), dtype=np.uint64)
+    L.idm_attention_item_trace_read(items.ctypes.data, 1)          # (clear)
+    torch.cuda.synchronize()
+    cur = step(99)
+    torch.cuda.synchronize()
+    L.idm_attention_item_trace_read(items.ctypes.data, 0)
+    blocks = np.zeros((5, 512, 5), dtype=np.uint64)
+    L.idm_gemm_block_trace_read(blocks.ctypes.data)
+    items, blocks = items.astype(np.int64), blocks.astype(np.int64)
+    # products of the last layer: [kind][block] = wait for the kernel before over, first operands, accumulator ready, done, block started
+    # (a residual product counts as kind 1 when its inner axis has more than 32 k-blocks, else 0)
+    q = blocks[3][blocks[3][:, 0] > 0]
+    t0 = q[:, 0].min()
+    pct = lambda v: "/".join(f"{x / 1e3:.1f}" for x in np.percentile(v, [0, 50, 100]))
+    print("the last layer, microseconds after its q/k/v product's wait for the kernel before it was over (min/median/max over blocks)")
+    for kind, name in ((3, "q/k/v"), (0, "residual product, short inner axis"), (2, "gate/up"), (1, "residual product, long inner axis")):
+        x = blocks[kind][blocks[kind][:, 0] > 0]
+        if len(x):
+            print(f"  {name}: {len(x)} blocks; started {pct(x[:, 4] - t0)}; wait over {pct(x[:, 0] - t0)}; "
+                  f"accumulator ready {pct(x[:, 2] - t0)}; done {pct(x[:, 3] - t0)}")
+    live = items[:, 0, 6] > 0
+    if live.any():
+        print(f"  attention (single tokens): {live.sum()} blocks; started {pct(items[live, 0, 6] - t0)}; rehearsal and wait over {pct(items[live, 0, 5] - t0)}")
+        for nth in range(4):
+            m = live & (items[:, nth, 0] >= items[:, 0, 5]) & (items[:, nth, 4] > 0)   # (stamps older than this launch are left out)
+            if not m.any():
+                continue
+            x = items[m, nth, :5] - t0
+            ph = np.diff(x, axis=1)
+            print(f"    item {nth} of a block: {m.sum()} blocks; described {pct(x[:, 0])}; scores {pct(ph[:, 0])}; softmax {pct(ph[:, 1])}; "
+                  f"context {pct(ph[:, 2])}; result written {pct(ph[:, 3])}; done {pct(x[:, 4])}")
     return 0
