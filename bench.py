@@ -264,6 +264,48 @@ def check_against_32_bit(cfg, seed: int = 0):
     return {"bf16_vs_f32_max_rel_diff": rel, "rows": out["float32"].shape[0], "same_argmax_rows": same_pick}
 
 
+# The same configuration (Qwen3-0.6B layer sizes, batch 8, cache of 4096) with the kernels this library had
+# before a token's bfloat16 result was made the same bits in every batch and cut: products whose sums were
+# split over blocks and clusters, single tokens summed per chunk of 256 keys.  Measured then, on this
+# bench; what the cut-invariant arithmetic cost is these against today's figures.
+EARLIER_KERNELS = {"decode_tok_s": 6035.2, "ms_per_step": 1.326, "prefill_2048_ms": 3.93}
+
+
+def check_cuts_bitwise(lm, seed: int = 0):
+    """bfloat16 logits of one request: whole in one step, cut into three steps, its last 8 tokens one by one,
+    and beside another request in the batch: compared bit for bit."""
+    import torch
+    eng = lm.engine
+    g = torch.Generator().manual_seed(seed + 77)
+    V = lm.config.vocab_size
+    ids = torch.randint(min(100, V - 1), min(50000, V), (300,), generator=g).tolist()
+    other = torch.randint(min(100, V - 1), min(50000, V), (170,), generator=g).tolist()
+    want = [0, 130, 291, 292, 299]
+
+    def run(cuts, beside=False):
+        a = eng.open()
+        b = eng.open() if beside else None
+        rows, at = {}, 0
+        for n in cuts:
+            w = [p - at for p in want if at <= p < at + n]
+            entries, wants = [(a, ids[at:at + n])], [w]
+            if beside and at == 0:
+                entries.append((b, other)); wants.append([])
+            out = eng.step(entries, wants)
+            for k, p in enumerate(q for q in want if at <= q < at + n):
+                rows[p] = out[k].clone()
+            at += n
+        eng.close(a)
+        if b is not None:
+            eng.close(b)
+        return torch.stack([rows[p] for p in want])
+
+    whole = run([300])
+    same = all(torch.equal(whole, other_cut) for other_cut in
+               (run([131, 100, 69]), run([292] + [1] * 8), run([300], beside=True)))
+    return bool(same)
+
+
 def reference_arm(args) -> int:
     """The unmodified reference on the same configuration: ``baseline/reference_arm.py``."""
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -323,6 +365,7 @@ def main() -> int:
             r = decode_point(lm, headline_lengths(b, args.context, 3 * st + args.warmup + 8, seed), st, args.warmup, seed, 3)
             points[f"decode_b{b}"] = r["tps"]
             points[f"decode_b{b}_hbm_frac"] = r["bytes"] / (r["ms"] * 1e-3) / hbm
+    cuts_same = check_cuts_bitwise(lm)
     del lm
     torch.cuda.empty_cache()
     check = None if args.skip_points else check_against_32_bit(cfg)
@@ -376,6 +419,15 @@ def main() -> int:
                      "frac": gbs / pk["hbm_gbs"], "peaks": pk["source"]},
         "points": points,
         "check": check,
+        # a token's bfloat16 logits are the same bits however its sequence was cut and batched (checked on this
+        # run: one request whole, in three steps, with its last tokens one by one, beside another request),
+        # and what that cost against the kernels before, which split their sums
+        "exactness": {"bf16_bitwise_same_across_cuts": cuts_same,
+                      "earlier_kernels_decode_tok_s": EARLIER_KERNELS["decode_tok_s"],
+                      "earlier_kernels_ms_per_step": EARLIER_KERNELS["ms_per_step"],
+                      "earlier_kernels_prefill_2048_ms": EARLIER_KERNELS["prefill_2048_ms"],
+                      "decode_now_over_earlier": (tps / EARLIER_KERNELS["decode_tok_s"]
+                                                  if args.size == "qwen3-0.6b" and args.batch == 8 and not args.layers else None)},
         "spread": {"ms_per_step_min": head["ms_min"], "ms_per_step_max": head["ms_max"]},
         "clocks": clocks,
     }
