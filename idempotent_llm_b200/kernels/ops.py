@@ -13,8 +13,9 @@ a library, ``torch._int_mm``, src/detllm/backends.py:88-135).  No product is sen
 to a library here, and none is split over its inner axis: an element is one chain
 of additions whatever the step's size.
 
-Environment switches (all default to the fast path): ``IDM_FUSED``, ``IDM_PREFILL``,
-``IDM_PDL``.
+Environment switches (all default to the fast path): ``IDM_FUSED=0`` (epilogues as kernels of their
+own), ``IDM_ATTENTION=generic`` (the general attention kernel for every step), ``IDM_PDL=0`` (no
+programmatic dependent launch).
 
 The entry points are called through ctypes with declared argument types (``SIGNATURES``), so that a
 call passes plain integers and floats; the current stream's handle comes from torch without a stream

@@ -1,8 +1,8 @@
 """The entry point that allocates nothing (csrc/idm_no_alloc.h), called through its exported C
 symbol the way a host without torch's allocator would call it: the caller passes inputs and
 outputs only, the scratch between the two kernels lives inside the library.  Its output must
-equal the usual entry point's, on two calls in a row (the second call finds the first call's
-leftovers in the shared array).  This file sorts last so that a run that stops at the first
+equal the usual entry point's, on calls in a row (a later call finds an earlier call's
+leftovers in the shared array), also after a call that was refused.  This file sorts last so that a run that stops at the first
 failure has already run every other test."""
 
 import ctypes
