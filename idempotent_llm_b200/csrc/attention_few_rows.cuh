@@ -620,14 +620,16 @@ attention_few_rows_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
 }
 
 // The ring's depth and the block's shared memory for tiles of `rows` rows: two blocks per SM where the
-// ring then still holds six key or value blocks, else one block with a deeper ring.
-static int attention_few_rows_plan(int hd, int rows, int* slots_out, int* per_sm_out) {
+// ring then still holds six key or value blocks and there are more work items than SMs; else one block
+// per SM with a deeper ring (few items: every block has one, and what counts is how much of it is on its
+// way at once).
+static int attention_few_rows_plan(int hd, int rows, long long items, int n_sm, int* slots_out, int* per_sm_out) {
     AttnFewLayout lay;
     lay.block_bytes = (hd / 64) * AP_BN * 128; lay.rows = rows; lay.slots = 0;
     const int fixed = lay.total();
     const int two_per_sm = (228 * 1024) / 2 - 1024, one_per_sm = 227 * 1024;
     int slots = (two_per_sm - fixed) / lay.block_bytes, per_sm = 2;
-    if (slots < 6) { slots = (one_per_sm - fixed) / lay.block_bytes; per_sm = 1; }
+    if (slots < 6 || items <= n_sm) { slots = (one_per_sm - fixed) / lay.block_bytes; per_sm = 1; }
     if (slots > AF_MAX_SLOTS) slots = AF_MAX_SLOTS;
     *slots_out = slots; *per_sm_out = per_sm;
     lay.slots = slots;
@@ -642,15 +644,7 @@ static bool attention_few_rows_can(int hd, int rows_cap, int run_blocks, int max
 template <int HD>
 static int launch_attention_few_rows(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcArgs& a, const T* q,
                                      int n_tiles, cudaStream_t stream) {
-    int slots = 0, per_sm = 0;
-    const int bytes = attention_few_rows_plan(HD, a.rows_cap, &slots, &per_sm);
-    IDM_REQUIRE(slots >= 4, "attention_few_rows: no room for the ring (%d rows)", a.rows_cap);
     static int configured = 0, n_sm = 0;
-    if (configured < bytes) {
-        cudaError_t e = cudaFuncSetAttribute(attention_few_rows_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        IDM_REQUIRE(e == cudaSuccess, "attention_few_rows: cannot get %d bytes of shared memory: %s", bytes, cudaGetErrorString(e));
-        configured = bytes;
-    }
     if (n_sm == 0) {
         int dev = 0;
         cudaGetDevice(&dev);
@@ -659,6 +653,14 @@ static int launch_attention_few_rows(const CUtensorMap& mk, const CUtensorMap& m
     }
     const long long items = (long long)n_tiles * (a.n_q >> a.gp_shift) * a.max_runs;
     IDM_REQUIRE(items < (1ll << 30), "attention_few_rows: %lld work items in one step", items);
+    int slots = 0, per_sm = 0;
+    const int bytes = attention_few_rows_plan(HD, a.rows_cap, items, n_sm, &slots, &per_sm);
+    IDM_REQUIRE(slots >= 4, "attention_few_rows: no room for the ring (%d rows)", a.rows_cap);
+    if (configured < bytes) {
+        cudaError_t e = cudaFuncSetAttribute(attention_few_rows_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        IDM_REQUIRE(e == cudaSuccess, "attention_few_rows: cannot get %d bytes of shared memory: %s", bytes, cudaGetErrorString(e));
+        configured = bytes;
+    }
     const int grid = (int)(items < (long long)per_sm * n_sm ? items : (long long)per_sm * n_sm);
     idm_launch(attention_few_rows_kernel<HD>, dim3(grid), dim3(AF_THREADS), (size_t)bytes, stream, mk, mv, a, q, slots, n_tiles);
     IDM_LAUNCH_CHECK("attention_few_rows");

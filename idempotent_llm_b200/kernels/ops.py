@@ -135,7 +135,7 @@ class Kernels:
         self.attention_impl = os.environ.get("IDM_ATTENTION", "tcgen05")
         # key blocks (of 64) of a run of the tensor-core kernel: each run starts its sums from nothing and
         # the runs are folded in ascending order, so this number is part of the arithmetic's definition
-        self.attention_run_blocks = 4
+        self.attention_run_blocks = 8
         self.page = L.idm_page_tokens()
 
     # ------------------------------------------------------------------ helpers
