@@ -446,7 +446,8 @@ CUTS = (1, 2, 16, 17, 32, 33, 64, 65, 128, 129, 200, 256, 257, 300)
 
 @pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (8, 1000, 160), (200, 512, 1024), (17, 130, 72), (64, 1024, 3072),
                                     (33, 257, 2048), (300, 384, 136), (1, 151936, 64), (2048, 1024, 1024),
-                                    (130, 4096, 4096), (200, 1024, 12288), (256, 5120, 5120), (96, 40, 8), (100, 20000, 128)])
+                                    (130, 4096, 4096), (200, 1024, 12288), (256, 5120, 5120), (96, 40, 8), (100, 20000, 128),
+                                    (3000, 1024, 256), (5000, 2048, 192)])   # (the last two: several tiles per block)
 def test_gemm_bfloat16(kernels, M, N, K_):
     K = kernels("bfloat16")
     x, w = _randn(M, K_, seed=72).bfloat16(), _randn(N, K_, seed=73).bfloat16()
@@ -536,7 +537,8 @@ def test_gemm_fused_swiglu(kernels, M, inter, K_):
 
 @pytest.mark.parametrize("M,n_q,n_kv,hd,hidden", [(3, 6, 2, 32, 96), (9, 16, 8, 128, 1024),
                                                   (300, 8, 2, 128, 160), (64, 2, 1, 64, 72), (1030, 24, 4, 128, 192),
-                                                  (520, 40, 12, 64, 136), (300, 6, 2, 32, 96), (130, 32, 8, 128, 4096)])
+                                                  (520, 40, 12, 64, 136), (300, 6, 2, 32, 96), (130, 32, 8, 128, 4096),
+                                                  (2500, 16, 8, 128, 256)])   # (the last: three tiles per block)
 def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, hidden):
     K = kernels("bfloat16")
     x_all = _randn(M, hidden, seed=80).bfloat16().cuda()
@@ -547,7 +549,7 @@ def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, 
     def run(fused, m=M, by_dim=True, split=True):
         """The first ``m`` tokens, as two sequences (``split``) or one, starting at positions 5 and 64."""
         starts, lens = ([5, 64], [m // 2, m - m // 2]) if split and m >= 2 else ([5], [m])
-        cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, 64 * 40, torch.bfloat16, "cuda:0", max_seqs=4)
+        cache = SequenceCache({0: CacheNeed("full", n_kv, hd)}, 64 * max(40, M // 64 + 6), torch.bfloat16, "cuda:0", max_seqs=4)
         slots = [cache.alloc_slot() for _ in lens]
         cache.reserve([(s_, st + L) for s_, st, L in zip(slots, starts, lens)]); cache.flush()
         packed, n, q_lens = pack_step_host(slots, starts, [[0] * L for L in lens])
