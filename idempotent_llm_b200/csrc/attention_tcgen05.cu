@@ -79,6 +79,11 @@ struct AttnTcArgs {
     int run_blocks;                                    // key blocks of a run
     int max_runs;                                      // > 0: every run has a block of its own (grid.x = head groups x max_runs); 0: one block walks a tile's runs
     int rows_cap;                                      // the most rows any tile of the step has: what is fetched of q, and what the scratch holds of a run
+    // one block per tile, but tiles with many key blocks shared by several: block `part` of a tile walks the runs
+    // [part * runs_per_part, + runs_per_part) and leaves each run's result in the pool; the last to arrive folds
+    const int* tile_pool;                              // per tile: its first slot in the pool (head group g: + g x its runs), or -1: one block has it alone
+    int max_parts, runs_per_part;                      // max_parts == 0: no tile is shared
+    float* pool;                                       // slots of rows_cap * (HD + 2) floats
     int* counters;                                     // [n_tiles * head groups] arrivals, zero between launches
     float* parts;                                      // runs through scratch: [n_tiles * head groups, max_runs] of rows_cap * (HD + 2) floats;
                                                        // one block per tile: [n_tiles * head groups] of 128 * HD floats (the context so far)
@@ -168,25 +173,71 @@ __device__ __forceinline__ void fold_runs_and_store(const AttnTcArgs& a, const f
     }
 }
 
+// The same fold for tiles of many rows: a thread per row (r = 0 .. 127), 16 dims at a time with four runs' loads in
+// flight, so that the loads of a warp are whole lines and a row's (m, l) chain is walked by one thread.  The same
+// operations in the same order as above: the same bits.
+template <int HD>
+__device__ __forceinline__ void fold_rows_and_store(const AttnTcArgs& a, const float* part0, size_t part_floats, int n_runs,
+                                                    int rows_valid, int tok0, int head0, int r) {
+    const int cap = a.rows_cap, gs = a.gp_shift, gp = 1 << gs;
+    if (r >= rows_valid) return;
+    T* dst = a.out + ((size_t)(tok0 + (r >> gs)) * a.n_q + head0 + (r & (gp - 1))) * HD;
+#pragma unroll 1
+    for (int c = 0; c < HD; c += 16) {
+        float M = -INFINITY, L = 0.f;
+        float acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+#pragma unroll 1
+        for (int i0 = 0; i0 < n_runs; i0 += 4) {
+            float2 ml[4];
+            float4 o[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (i0 + u < n_runs) {
+                    const float* pi = part0 + (size_t)(i0 + u) * part_floats;
+                    ml[u] = __ldcg(reinterpret_cast<const float2*>(pi + (size_t)HD * cap) + r);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) o[u][k] = __ldcg(reinterpret_cast<const float4*>(pi) + (size_t)(c / 4 + k) * cap + r);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (i0 + u < n_runs) {
+                    float a_, b_;
+                    fold_coeffs(M, L, ml[u].x, ml[u].y, a_, b_);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        acc[4 * k] = fold_value(acc[4 * k], a_, o[u][k].x, b_); acc[4 * k + 1] = fold_value(acc[4 * k + 1], a_, o[u][k].y, b_);
+                        acc[4 * k + 2] = fold_value(acc[4 * k + 2], a_, o[u][k].z, b_); acc[4 * k + 3] = fold_value(acc[4 * k + 3], a_, o[u][k].w, b_);
+                    }
+                }
+            }
+        }
+        store_out16(dst + c, acc, __fdiv_rn(1.0f, L));
+    }
+}
+
 // The end of a block that has written its run's result to scratch, called by its 128 row threads
 // (r = 0 .. 127; named barrier 1): the arrival is counted, and the block that comes last for the tile
 // and head group folds all runs, whoever it is.  (A block whose wait ran out, ok == false, still counts:
 // the error is reported, the result is wrong, and nobody waits for anybody for ever.)
 template <int HD>
 __device__ __forceinline__ void count_and_fold_runs(const AttnTcArgs& a, const float* part0, size_t part_floats, int n_runs,
-                                                    int rows_valid, int tok0, int head0, int counter_index,
+                                                    int n_arrivals, int rows_valid, int tok0, int head0, int counter_index,
                                                     volatile int* last_flag, int r, bool ok) {
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (r == 0) {
         int* counter = a.counters + counter_index;
-        const int is_last = atomicAdd(counter, 1) == n_runs - 1;
+        const int is_last = atomicAdd(counter, 1) == n_arrivals - 1;
         if (is_last) *counter = 0;                                 // ready for the next launch
         *last_flag = is_last;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (!*last_flag || !ok) return;
     __threadfence();
-    fold_runs_and_store<HD>(a, part0, part_floats, n_runs, rows_valid, tok0, head0, r, 128);
+    if (a.rows_cap > 32) fold_rows_and_store<HD>(a, part0, part_floats, n_runs, rows_valid, tok0, head0, r);
+    else fold_runs_and_store<HD>(a, part0, part_floats, n_runs, rows_valid, tok0, head0, r, 128);
 }
 
 #include "attention_few_rows.cuh"
@@ -223,9 +274,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // blocks start in this order: all head groups (and runs) of the longest tile first.  What is read
     // here was written before the step began, not by the kernel before this one.
     const bool through_scratch = a.max_runs > 0;
+    const bool parted = !through_scratch && a.max_parts > 0;
     const int tile = blockIdx.y;
-    const int hg = through_scratch ? blockIdx.x / a.max_runs : blockIdx.x;
+    const int hg = through_scratch ? blockIdx.x / a.max_runs : parted ? blockIdx.x / a.max_parts : blockIdx.x;
     const int run = through_scratch ? blockIdx.x % a.max_runs : 0;
+    const int part = parted ? blockIdx.x % a.max_parts : 0;
     const int gs = a.gp_shift, gp = 1 << gs;
     const int seq = a.tile_seq[tile], tstart = a.tile_start[tile];
     const int head0 = hg << gs;                                  // the tile's first q-head
@@ -241,8 +294,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int R = a.run_blocks;
     const int n_runs = (nb_tile + R - 1) / R;
     if (through_scratch && run >= n_runs) return;                // (the whole block, before anything is set up)
-    const int b_first = through_scratch ? run * R : 0;           // this block's key blocks b_first .. b_first + nb - 1
-    const int nb = through_scratch ? min(R, nb_tile - b_first) : nb_tile;
+    const int pool_at = parted ? a.tile_pool[tile] : -1;
+    const int n_parts = pool_at >= 0 ? (n_runs + a.runs_per_part - 1) / a.runs_per_part : 1;
+    if (part >= n_parts) return;
+    const bool shared = n_parts > 1;                             // this tile's runs go through the pool, several blocks walk them
+    // this block's key blocks b_first .. b_first + nb - 1
+    const int b_first = through_scratch ? run * R : shared ? part * a.runs_per_part * R : 0;
+    const int nb = through_scratch ? min(R, nb_tile - b_first) : shared ? min(a.runs_per_part * R, nb_tile - b_first) : nb_tile;
     const int n_hg = a.n_q >> gs;
 
     if (threadIdx.x == 0) {
@@ -358,7 +416,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(prow + (c << 4)) = make_uint4(0, 0, 0, 0);
         }
         // one block per tile, more than one run: the row's context so far lives in scratch of this block's own
-        float* tot = (!through_scratch && n_runs > 1) ? a.parts + (size_t)(tile * n_hg + hg) * (AP_BM * HD) : nullptr;
+        float* tot = (!through_scratch && !shared && n_runs > 1) ? a.parts + (size_t)(tile * n_hg + hg) * (AP_BM * HD) : nullptr;
+        // where the runs of this tile and head group leave their results (a block per run, or a tile shared by several blocks)
+        const int cap = a.rows_cap;
+        const size_t part_floats = run_part_floats(cap, HD);
+        float* part0 = through_scratch ? a.parts + (size_t)(tile * n_hg + hg) * a.max_runs * part_floats
+                                       : shared ? a.pool + ((size_t)pool_at + (size_t)hg * n_runs) * part_floats : nullptr;
+        // a finished run's (m, l) and context, from tensor memory to its slot (64 columns are asked for before the first is waited for)
+        auto leave_run = [&](int which, float m_run, float l_run) {
+            float4* mine = reinterpret_cast<float4*>(part0 + (size_t)which * part_floats);
+#pragma unroll 1
+            for (int c = 0; c < HD; c += 64) {
+                uint32_t o[64];
+#pragma unroll
+                for (int u = 0; u < 64; u += 16) tc_ld16_issue(tmem_o + lane_base + c + u, o + u);
+                tc_ld_wait();
+                if (r < cap) {
+#pragma unroll
+                    for (int k = 0; k < 16; ++k)
+                        mine[(c / 4 + k) * cap + r] = make_float4(__uint_as_float(o[4 * k]), __uint_as_float(o[4 * k + 1]),
+                                                                  __uint_as_float(o[4 * k + 2]), __uint_as_float(o[4 * k + 3]));
+                }
+            }
+            if (r < cap) reinterpret_cast<float2*>(part0 + (size_t)which * part_floats + (size_t)HD * cap)[r] = make_float2(m_run, l_run);
+        };
         float m_ref = -INFINITY, l = 0.f;                        // the current run
         float M_tot = -INFINITY, L_tot = 0.f;                    // the runs folded so far
         bool ok = true;
@@ -425,7 +506,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 ok = mbar_wait(o_done, (b - 1) & 1, abort_flag, &g_attn_tc_error);   // P is free, O is settled
                 if (!ok) break;
                 tc_fence_after();
-                if (run_start) {
+                if (run_start && shared) {
+                    // the run before this block is complete: its result goes to its slot (the MMA that starts the
+                    // new run's context overwrites O only after this warp's arrival below)
+                    if (warp_live) leave_run((b_first + b) / R - 1, m_prev, l_prev);
+                } else if (run_start) {
                     // the run before this block is complete: fold it into the row's context so far (the MMA
                     // that starts the new run's context overwrites O only after this warp's arrival below)
                     if (warp_live) {
@@ -499,36 +584,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ok = __all_sync(0xffffffffu, ok);                          // (one answer per warp for what follows)
         if (threadIdx.x == 0) attn_stamp(40);                    // the last context is complete
         T* orow = a.out + ((size_t)(tok0 + (r >> gs)) * a.n_q + head0 + (r & (gp - 1))) * HD;
-        if (through_scratch && n_runs > 1) {
-            // This run's result goes to its place among the tile's; the block that comes last folds them
-            // all, in the order of the runs whoever it is.  (A warp whose wait ran out skips the work but
-            // not the two barriers and the count: the error is reported, the result is wrong, and nobody
-            // waits for anybody for ever.)
-            const int cap = a.rows_cap;
-            const size_t part_floats = run_part_floats(cap, HD);
-            float* part0 = a.parts + (size_t)(tile * n_hg + hg) * a.max_runs * part_floats;
+        if ((through_scratch || shared) && n_runs > 1) {
+            // This block's (last) run's result goes to its place among the tile's; the block that comes last
+            // folds them all, in the order of the runs whoever it is.  (A warp whose wait ran out skips the
+            // work but not the two barriers and the count: the error is reported, the result is wrong, and
+            // nobody waits for anybody for ever.)
             if (ok && warp_live) {
                 tc_fence_after();
-                float4* mine = reinterpret_cast<float4*>(part0 + (size_t)run * part_floats);
-                // (64 columns are asked for before the first is waited for)
-#pragma unroll 1
-                for (int c = 0; c < HD; c += 64) {
-                    uint32_t o[64];
-#pragma unroll
-                    for (int u = 0; u < 64; u += 16) tc_ld16_issue(tmem_o + lane_base + c + u, o + u);
-                    tc_ld_wait();
-                    if (r < cap) {
-#pragma unroll
-                        for (int k = 0; k < 16; ++k)
-                            mine[(c / 4 + k) * cap + r] = make_float4(__uint_as_float(o[4 * k]), __uint_as_float(o[4 * k + 1]),
-                                                                      __uint_as_float(o[4 * k + 2]), __uint_as_float(o[4 * k + 3]));
-                    }
-                }
-                if (r < cap) reinterpret_cast<float2*>(mine + (HD / 4) * cap)[r] = make_float2(m_ref, l);
+                leave_run(through_scratch ? run : (b_first + nb - 1) / R, m_ref, l);
                 __threadfence();
             }
-            count_and_fold_runs<HD>(a, part0, part_floats, n_runs, rows_valid, tok0, head0, tile * n_hg + hg,
-                                    (volatile int*)(gbase + S::BAR_OFF + 128), r, ok);
+            count_and_fold_runs<HD>(a, part0, part_floats, n_runs, through_scratch ? n_runs : n_parts, rows_valid, tok0, head0,
+                                    tile * n_hg + hg, (volatile int*)(gbase + S::BAR_OFF + 128), r, ok);
             if (threadIdx.x == 0) attn_stamp(41);                // this run's result is in scratch, counted, and folded if it was the last
         } else if (ok && warp_live) {
             // the last (or only) run folded onto what came before, then divided by the sum
@@ -573,7 +640,7 @@ static int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mk, con
         configured = true;
     }
     const int n_hg = a.n_q >> a.gp_shift;
-    dim3 grid(n_hg * (a.max_runs > 0 ? a.max_runs : 1), n_tiles);
+    dim3 grid(n_hg * (a.max_runs > 0 ? a.max_runs : a.max_parts > 0 ? a.max_parts : 1), n_tiles);
     idm_launch(attention_tc_kernel<HD>, dim3(grid), dim3(AP_THREADS), S::TOTAL, stream, mq, mk, mv, a);
     IDM_LAUNCH_CHECK("attention_tc");
     return 0;
@@ -611,7 +678,11 @@ extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, co
                                 const int* table, int table_stride, const int* tile_seq, const int* tile_start,
                                 int n_tiles, const int* cu_q, const int* q_start, const int* kv_len,
                                 const int* slots, int n_tokens, int n_q, int n_kv, int hd, float scale,
-                                int run_blocks, int max_runs, int rows_cap, float* scratch, cudaStream_t stream) {
+                                int run_blocks, int max_runs, int rows_cap, float* scratch, const int* tile_pool,
+                                int max_parts, int runs_per_part, cudaStream_t stream) {
+    // (tile_pool / max_parts / runs_per_part, with max_runs == 0: tiles whose entry in tile_pool is not -1 are shared
+    // by up to max_parts blocks of runs_per_part runs each; their runs' results lie in the scratch behind the
+    // one-context-per-tile region, from the slot tile_pool names on, head group after head group)
     if (n_tiles == 0 || n_tokens == 0) return 0;
     IDM_REQUIRE(idm_attention_tc_supports(hd), "attention_tc: head_dim=%d has no kernel here", hd);
     IDM_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention_tc: bad head counts %d/%d", n_q, n_kv);
@@ -648,6 +719,10 @@ extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, co
     a.n_q = n_q; a.n_kv = n_kv; a.gp_shift = gs; a.scale_log2 = scale * 1.4426950408889634f;
     a.run_blocks = run_blocks; a.max_runs = max_runs; a.rows_cap = rows_cap;
     a.counters = (int*)scratch; a.parts = scratch ? scratch + AP_COUNTERS : nullptr;
+    a.tile_pool = tile_pool; a.max_parts = (max_runs == 0 && tile_pool != nullptr) ? max_parts : 0; a.runs_per_part = runs_per_part;
+    a.pool = a.parts ? a.parts + groups * (long long)(AP_BM * hd) : nullptr;
+    IDM_REQUIRE(a.max_parts == 0 || (scratch != nullptr && runs_per_part >= 1 && groups <= AP_COUNTERS),
+                "attention_tc: shared tiles need scratch, runs_per_part >= 1 and at most %d tiles x head groups (got %lld)", AP_COUNTERS, groups);
     if (g_attn_few_rows && attention_few_rows_can(hd, rows_cap, run_blocks, max_runs, groups))
         return hd == 64 ? launch_attention_few_rows<64>(mk, mv, a, (const T*)q, n_tiles, stream)
                         : launch_attention_few_rows<128>(mk, mv, a, (const T*)q, n_tiles, stream);

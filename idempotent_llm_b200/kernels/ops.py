@@ -74,7 +74,7 @@ SIGNATURES = {
     "idm_attention_tc_supports": (c_int, "i"),
     "idm_attention_tc_heads_per_tile": (c_int, "ii"),
     "idm_attention_tc_scratch_floats": (c_longlong, "iiiiii"),
-    "idm_attention_tc": (c_int, "ppppipippippppiiiifiiipp"),
+    "idm_attention_tc": (c_int, "ppppipippippppiiiifiiippiip"),
     "idm_attention_tc_status": (c_int, ""),
     "idm_attention_tc_set_few_rows": (c_int, "i"),
     "idm_gemm_f32": (c_int, "pppiiip"),
@@ -136,6 +136,11 @@ class Kernels:
         # key blocks (of 64) of a run of the tensor-core kernel: each run starts its sums from nothing and
         # the runs are folded in ascending order, so this number is part of the arithmetic's definition
         self.attention_run_blocks = 8
+        # prompts: tiles with more key blocks than a fair share are shared by several blocks; the pool holds that
+        # many runs' results (of 128 rows x (head_dim + 2) floats)
+        self.attention_share_tiles = True
+        self.attention_pool_slots = 4096
+        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self.page = L.idm_page_tokens()
 
     # ------------------------------------------------------------------ helpers
@@ -267,12 +272,14 @@ class Kernels:
             return self.attention_tc(q, kv, ctx, scale)
         return self.attention_generic(q, kv, ctx, k_new, v_new, scale, window)
 
-    def attention_tc(self, q, kv, ctx, scale: float, out=None, through_scratch=None) -> torch.Tensor:
+    def attention_tc(self, q, kv, ctx, scale: float, out=None, through_scratch=None, share=None) -> torch.Tensor:
         """Causal attention on the tensor cores: tiles of (128 / gp tokens) x (gp q-heads of one kv-head).
 
         Steps with few tokens per sequence (at most 32 rows a tile: single tokens above all) give every
         run of key blocks a block of its own, and the runs meet in scratch; other steps let one block
-        walk a tile's runs.  ``through_scratch`` forces one or the other (tests: the bits are the same)."""
+        walk a tile's runs, except that tiles with more key blocks than a fair share of the step's are
+        shared by several blocks.  ``through_scratch`` and ``share`` force one way or the other (tests: the
+        bits are the same)."""
         n, n_q, hd = q.shape
         n_kv = kv.n_kv_heads
         if out is None:
@@ -297,11 +304,29 @@ class Kernels:
                 for st in range(0, L, tok):
                     items.append((ctx.host_starts[i] + min(st + tok - 1, L - 1), i, st))
             items.sort(key=lambda t: -t[0])
-            host = torch.tensor([[i for _, i, _ in items], [st for _, _, st in items]], dtype=torch.int32)
-            dev = host.to(self.device)
             rows_cap = min(tok, max(ctx.host_q_lens)) * gp
-            tiles = ctx.memo[("attention_tc_tiles", gp)] = (dev, dev[0].data_ptr(), dev[1].data_ptr(), len(items), rows_cap)
-        _, tile_seq, tile_start, n_tiles, rows_cap = tiles
+            # Tiles with more key blocks than a fair share of the step's are shared by several blocks, each
+            # walking `per` runs and leaving every run's result in a pool; the last block to arrive folds them
+            # in the order of the runs (the same bits as one block walking them all: the runs are the same).
+            n_hg = n_q // gp
+            blocks_of = [last // self.page + 1 for last, _, _ in items]
+            fair = -(-sum(blocks_of) * n_hg // (2 * self.sm_count))
+            per = max(2, -(-fair // R))                           # runs a block walks
+            pool, slots_used, max_parts = [], 0, 1
+            for nb in blocks_of:
+                runs = -(-nb // R)
+                if self.attention_share_tiles and rows_cap == 128 and runs > per and slots_used + runs * n_hg <= self.attention_pool_slots:
+                    pool.append(slots_used)
+                    slots_used += runs * n_hg
+                    max_parts = max(max_parts, -(-runs // per))
+                else:
+                    pool.append(-1)
+            host = torch.tensor([[i for _, i, _ in items], [st for _, _, st in items], pool], dtype=torch.int32)
+            dev = host.to(self.device)
+            plan = (dev[2].data_ptr(), max_parts, per, slots_used) if slots_used else (None, 0, 0, 0)
+            tiles = ctx.memo[("attention_tc_tiles", gp)] = (dev, dev[0].data_ptr(), dev[1].data_ptr(), len(items), rows_cap, plan)
+        _, tile_seq, tile_start, n_tiles, rows_cap = tiles[:5]
+        tile_pool, max_parts, per, pool_slots = tiles[5] if len(tiles) > 5 else (None, 0, 0, 0)
         # an upper bound of the key blocks any tile has (a captured step is replayed at growing lengths)
         longest = -(-ctx.max_kv_len // self.page)
         max_runs = -(-longest // R)
@@ -312,15 +337,19 @@ class Kernels:
             through_scratch = rows_cap <= 32
         if through_scratch:
             need = self.lib.idm_attention_tc_scratch_floats(n_tiles, n_q, n_kv, hd, max_runs, rows_cap)
+            tile_pool, max_parts, per = None, 0, 0
         else:
-            need = self.lib.idm_attention_tc_scratch_floats(n_tiles, n_q, n_kv, hd, 0, 0) if max_runs > 1 else 0
+            if share is False:
+                tile_pool, max_parts, per, pool_slots = None, 0, 0, 0
+            need = self.lib.idm_attention_tc_scratch_floats(n_tiles, n_q, n_kv, hd, 0, 0) if (max_runs > 1 or pool_slots) else 0
+            need += pool_slots * (-(-(128 * (hd + 2)) // 4) * 4)
             max_runs = 0
         scratch = self.scratch("attention_tc", need) if need else None
         self._check(self.lib.idm_attention_tc(
             _p(q), _p(out), _p(kv.k), _p(kv.v), kv.k.shape[0],
             _p(kv.table), kv.table.shape[1], tile_seq, tile_start, n_tiles, _p(ctx.cu_q), _p(ctx.q_start),
             _p(ctx.kv_len), _p(ctx.slots), n, n_q, n_kv,
-            hd, scale, R, max_runs, rows_cap, _p(scratch),
+            hd, scale, R, max_runs, rows_cap, _p(scratch), tile_pool, max_parts, per,
             self._stream()))
         return out
 

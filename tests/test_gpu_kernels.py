@@ -260,8 +260,14 @@ def test_attention_tensor_core_runs_and_cuts(kernels, run_blocks, n_q, n_kv, hd)
     old = K.attention_run_blocks
     K.attention_run_blocks = run_blocks
     try:
-        out = K.attention_tc(qd, kv, ctx, scale, through_scratch=False).view(-1, n_q, hd)
-        again = K.attention_tc(qd, kv, ctx, scale, through_scratch=False).view(-1, n_q, hd)
+        out = K.attention_tc(qd, kv, ctx, scale, through_scratch=False, share=False).view(-1, n_q, hd)
+        again = K.attention_tc(qd, kv, ctx, scale, through_scratch=False, share=False).view(-1, n_q, hd)
+        # long tiles shared by several blocks that each walk a few runs (the default for prompts), twice
+        for _ in range(2):
+            shared = K.attention_tc(qd, kv, ctx, scale, through_scratch=False).view(-1, n_q, hd)
+            assert torch.equal(out, shared), "a tile shared by several blocks gives other bits than one block walking it"
+        assert ctx.memo[("attention_tc_tiles", K.lib.idm_attention_tc_heads_per_tile(n_q, n_kv))][5][3] > 0, "no tile was shared"
+
         met = K.attention_tc(qd, kv, ctx, scale, through_scratch=True).view(-1, n_q, hd)
         met2 = K.attention_tc(qd, kv, ctx, scale, through_scratch=True).view(-1, n_q, hd)
         torch.cuda.synchronize()
