@@ -139,6 +139,7 @@ class Kernels:
         # prompts: tiles with more key blocks than a fair share are shared by several blocks; the pool holds that
         # many runs' results (of 128 rows x (head_dim + 2) floats)
         self.attention_share_tiles = True
+        self.attention_share_scale, self.attention_share_min_runs = 1.0, 2
         self.attention_pool_slots = 4096
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self.page = L.idm_page_tokens()
@@ -310,8 +311,8 @@ class Kernels:
             # in the order of the runs (the same bits as one block walking them all: the runs are the same).
             n_hg = n_q // gp
             blocks_of = [last // self.page + 1 for last, _, _ in items]
-            fair = -(-sum(blocks_of) * n_hg // (2 * self.sm_count))
-            per = max(2, -(-fair // R))                           # runs a block walks
+            fair = -(-int(sum(blocks_of) * n_hg * self.attention_share_scale) // (2 * self.sm_count))
+            per = max(self.attention_share_min_runs, -(-fair // R))   # runs a block walks
             pool, slots_used, max_parts = [], 0, 1
             for nb in blocks_of:
                 runs = -(-nb // R)
