@@ -80,6 +80,7 @@ class KVGroup:
         self.table = self.table_host.to(device)
         self.pages_of: Dict[int, List[int]] = {}
         self._dirty: List[Tuple[int, int, int]] = []
+        self._uploaded = None       # event behind the last flush's copies: the host table is theirs until it has passed
 
     # what a kind decides -----------------------------------------------------
     def layout(self, need, max_tokens, max_seqs, max_seq_len) -> Tuple[int, int]:
@@ -98,6 +99,12 @@ class KVGroup:
         n = self.pages_needed(slot, new_len)
         if n == 0:
             return 0
+        # The copies of the last flush read the host table when the GPU gets to them, which may be long after
+        # the call: a slot given back and taken again in the meantime would have its new pages uploaded for
+        # the old request's steps.  So the table is not written before those copies are done.
+        if self._uploaded is not None:
+            self._uploaded.synchronize()
+            self._uploaded = None
         mine = self.pages_of.setdefault(slot, [])
         first = len(mine)
         for _ in range(n):
@@ -129,10 +136,16 @@ class KVGroup:
         return 0 if self.pool is None else self.pool.n_held
 
     def flush(self) -> None:
+        if not self._dirty:
+            return
         for slot, first, n in self._dirty:
             self.table[slot, first:first + n].copy_(self.table_host[slot, first:first + n],
                                                     non_blocking=True)
         self._dirty.clear()
+        if self.table.is_cuda:
+            if self._uploaded is None:
+                self._uploaded = torch.cuda.Event()
+            self._uploaded.record()
 
     def view(self, cache_id: int) -> KVView:
         i = self.index[cache_id]

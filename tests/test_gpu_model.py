@@ -182,6 +182,41 @@ def test_first_tokens_and_junk_in_freed_pages(loaded, name, dtype):
     _check_clean(lm)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_slot_taken_again_while_the_gpu_is_behind(loaded, dtype):
+    """The block tables go up by copies that the GPU runs later than the call.  A request's last token
+    opens a new page while the GPU is held up; the request ends and the next one takes its slot and (last
+    given back, first taken) its pages in another order before that step has run.  The first request's
+    last token must still find its own page."""
+    lm, cfg, w = loaded("B", dtype)
+    eng = lm.engine
+    first = helpers.rand_ids(3 * 64 + 1, cfg["vocab_size"], 301)
+    second = helpers.rand_ids(5 * 64 - 9, cfg["vocab_size"], 302)
+
+    def run(hold_up):
+        s = eng.open()
+        eng.step([(s, first[:-3])], [[]])
+        out = []
+        for i, t in enumerate(first[-3:]):
+            if hold_up and i == 2:
+                torch.cuda.synchronize()
+                torch.cuda._sleep(400_000_000)      # some tenths of a second in which the host runs ahead
+            out.append(eng.step([(s, [t])], [[0]]).clone())
+        eng.close(s)
+        s = eng.open()
+        out.append(eng.step([(s, second)], [[len(second) - 1]]).clone())
+        eng.close(s)
+        torch.cuda.synchronize()
+        return torch.cat(out)
+
+    want, got = run(False), run(True)
+    assert torch.equal(got[:3], want[:3]), "the first request's last tokens read another request's pages"
+    assert torch.equal(got[3:], want[3:])
+    ref = plain.forward(cfg, w, first)[-3:]
+    assert helpers.rel_err(want[:3], ref) < helpers.TOL[dtype]
+    _check_clean(lm)
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_greedy_generation_through_the_entry_point(loaded, name, dtype):
     lm, cfg, w = loaded(name, dtype)
