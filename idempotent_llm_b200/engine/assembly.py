@@ -56,12 +56,52 @@ class CausalLM:
         self.blocks = [BLOCKS.get(layer.kind)(layer, weights, layer.prefix, rt) for layer in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, weights,
                                                           spec.final_norm_prefix, rt)
+        self._programs = {}
         self.graph_safe = all(getattr(part, "graph_safe", True) for b in self.blocks
                               for part in vars(b).values())
+
+    def program(self, cache):
+        """The model's kernel calls over ``cache`` as a step program (``kernels/program.py``), made once; None
+        if a part cannot emit its calls, the kernels hold no programs (32-bit; separate epilogues), or a
+        stand-in for the kernels has none."""
+        key = id(cache)
+        if key not in self._programs:
+            self._programs[key] = (cache, self._emit(cache))   # (the cache is kept: its id stays its own)
+        return self._programs[key][1]
+
+    def _emit(self, cache):
+        K = self.rt.kernels
+        if not hasattr(K, "use_programs"):
+            return None
+        from ..kernels.program import NotProgrammable, StepProgram
+        hidden = self.spec.hidden
+        try:
+            prog = StepProgram(K)
+            h = prog.buffer("stream", per_token=4 * hidden)
+            prog.embed(self.embed, h)
+            for e in self.spec.schedule:
+                block = self.blocks[e.layer]
+                state = cache.state_of(e.cache)
+                if not hasattr(block, "emit") or (state is not None and state.numel()):
+                    raise NotProgrammable("a block without emit, or with per-sequence state")
+                block.emit(prog, h, cache.view(e.cache), state, e.writes_cache)
+            if not hasattr(self.final_norm, "emit"):
+                raise NotProgrammable("the final norm has no emit")
+            x = prog.buffer("head.x", per_row=2 * hidden)
+            self.final_norm.emit(prog, h, x, rows=True)
+            logits = prog.buffer("logits")
+            prog.gemm_store(x, self.head, hidden, logits, rows=True)
+            return prog.finish(logits, self.head.shape[0])
+        except NotProgrammable:
+            return None
 
     def forward(self, ctx, cache, want_rows: torch.Tensor) -> torch.Tensor:
         """Run the step's tokens; returns 32-bit logits ``[len(want_rows), vocab]``."""
         K = self.rt.kernels
+        if getattr(K, "use_programs", False):
+            prog = self.program(cache)
+            if prog is not None:
+                return prog.run(ctx, want_rows)
         h = K.embed(ctx.tokens, self.embed)
         pending = None
         for e in self.spec.schedule:

@@ -37,7 +37,7 @@ SOURCES: Dict[str, List[str]] = {
     "float32": ["runtime.cu", "elementwise.cu", "sampler.cu", "attention_generic.cu",
                 "attention_decode.cu", "gemm_f32.cu"],
     "bfloat16": ["runtime.cu", "elementwise.cu", "sampler.cu", "attention_generic.cu",
-                 "attention_decode.cu", "gemm_tcgen05.cu", "attention_tcgen05.cu"],
+                 "attention_decode.cu", "gemm_tcgen05.cu", "attention_tcgen05.cu", "step_program.cu"],
 }
 DEFINES = {"float32": "-DIDM_F32", "bfloat16": "-DIDM_BF16"}
 _LOADED: Dict[str, ctypes.CDLL] = {}

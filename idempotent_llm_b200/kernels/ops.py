@@ -15,7 +15,8 @@ of additions whatever the step's size.
 
 Environment switches (all default to the fast path): ``IDM_FUSED=0`` (epilogues as kernels of their
 own), ``IDM_ATTENTION=generic`` (the general attention kernel for every step), ``IDM_PDL=0`` (no
-programmatic dependent launch).
+programmatic dependent launch), ``IDM_PROGRAM=0`` (every kernel of a step called from Python instead
+of one call that runs the step's list of calls).
 
 The entry points are called through ctypes with declared argument types (``SIGNATURES``), so that a
 call passes plain integers and floats; the current stream's handle comes from torch without a stream
@@ -87,6 +88,8 @@ SIGNATURES = {
     "idm_gemm_bf16_qkv": (c_int, "ppiiiiippfppppppppiipppp"),
     "idm_gemm_status": (c_int, ""),
     "idm_wait_probe": (c_int, "qipp"),
+    "idm_program_layout": (c_int, "p"),
+    "idm_run_program": (c_int, "pipp"),
     # only in a library compiled with -DIDM_TRACE (time stamps from inside two kernels: a measuring aid)
     "idm_gemm_trace_read": (c_int, "p"),
     "idm_gemm_block_trace_read": (c_int, "p"),
@@ -143,6 +146,16 @@ class Kernels:
         self.attention_pool_slots = 4096
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self.page = L.idm_page_tokens()
+        # a model whose parts can emit their calls runs a step by one call into the library (program.py);
+        # switched off (IDM_PROGRAM=0, or this attribute), every kernel is called from Python: the same bits
+        self.use_programs = self.fused and os.environ.get("IDM_PROGRAM", "1") != "0"
+        if hasattr(L, "idm_program_layout"):
+            from . import program
+            seen = (c_int * 16)()
+            n = L.idm_program_layout(seen)
+            if list(seen[:n]) != program.layout():
+                raise KernelError(f"the records of a step program differ between the library {list(seen[:n])} "
+                                  f"and the binding {program.layout()}")
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -282,9 +295,23 @@ class Kernels:
         shared by several blocks.  ``through_scratch`` and ``share`` force one way or the other (tests: the
         bits are the same)."""
         n, n_q, hd = q.shape
-        n_kv = kv.n_kv_heads
         if out is None:
             out = torch.empty((n, n_q * hd), dtype=self.dtype, device=self.device)
+        (tile_seq, tile_start, n_tiles, rows_cap, max_runs, scratch, tile_pool, max_parts,
+         per) = self.attention_tc_plan(ctx, n_q, kv.n_kv_heads, hd, through_scratch, share)
+        self._check(self.lib.idm_attention_tc(
+            _p(q), _p(out), _p(kv.k), _p(kv.v), kv.k.shape[0],
+            _p(kv.table), kv.table.shape[1], tile_seq, tile_start, n_tiles, _p(ctx.cu_q), _p(ctx.q_start),
+            _p(ctx.kv_len), _p(ctx.slots), n, n_q, kv.n_kv_heads,
+            hd, scale, self.attention_run_blocks, max_runs, rows_cap, scratch, tile_pool, max_parts, per,
+            self._stream()))
+        return out
+
+    def attention_tc_plan(self, ctx, n_q: int, n_kv: int, hd: int, through_scratch=None, share=None):
+        """What the attention launches of one step share, for one arrangement of heads: the list of tiles
+        (on the device; made once a step), how the tiles' runs are spread over blocks, and the scratch.
+        Returns (tile_seq, tile_start, n_tiles, rows_cap, max_runs, scratch, tile_pool, max_parts,
+        runs_per_part) as ``idm_attention_tc`` takes them (addresses as integers or None)."""
         gp = self.lib.idm_attention_tc_heads_per_tile(n_q, n_kv)
         tok = 128 // gp
         R = self.attention_run_blocks
@@ -346,13 +373,7 @@ class Kernels:
             need += pool_slots * (-(-(128 * (hd + 2)) // 4) * 4)
             max_runs = 0
         scratch = self.scratch("attention_tc", need) if need else None
-        self._check(self.lib.idm_attention_tc(
-            _p(q), _p(out), _p(kv.k), _p(kv.v), kv.k.shape[0],
-            _p(kv.table), kv.table.shape[1], tile_seq, tile_start, n_tiles, _p(ctx.cu_q), _p(ctx.q_start),
-            _p(ctx.kv_len), _p(ctx.slots), n, n_q, n_kv,
-            hd, scale, R, max_runs, rows_cap, _p(scratch), tile_pool, max_parts, per,
-            self._stream()))
-        return out
+        return tile_seq, tile_start, n_tiles, rows_cap, max_runs, _p(scratch), tile_pool, max_parts, per
 
     def attention_tc_few_rows(self, on: bool) -> bool:
         """Whether tiles of at most 16 rows take the kernel made for them (the default) or the one all

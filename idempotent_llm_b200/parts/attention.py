@@ -78,6 +78,23 @@ class GQAAttention(Mixer):
                                  f"rotate pairs (d, d + head_dim / 2) over the whole head ('half_whole_head')")
             self.position = POSITIONS.get(spec.position.kind)(spec.position, weights, prefix, rt)
 
+    def emit(self, prog, x, h, kv, state, writes_cache: bool):
+        """The calls of ``forward`` on the fused path without a window, adding into the stream ``h``."""
+        from ..kernels.program import NotProgrammable
+        s = self.spec
+        if writes_cache == s.kv_from_other:
+            raise ValueError("a mixer with its own k/v must write its cache entry; one without must not")
+        if s.window or kv.ring:
+            raise NotProgrammable("a windowed layer reads a prompt's own keys from buffers of the step")
+        cs = self.position.emit(prog) if self.position is not None else None
+        width = s.n_heads * s.head_dim
+        q = prog.buffer("attention.q", per_token=2 * width)
+        prog.gemm_qkv(x, self.w_qkv, s.hidden, s.n_heads, 0 if s.kv_from_other else s.n_kv_heads, s.head_dim,
+                      self.q_gamma, self.k_gamma, s.qk_norm_eps, cs, q, kv if writes_cache else None)
+        o = prog.buffer("attention.o", per_token=2 * width)
+        prog.attention(q, kv, s.n_heads, s.softmax_scale, o)
+        prog.gemm_residual(o, self.w_o, width, h)
+
     def forward(self, x, ctx, kv, state, writes_cache: bool, residual=None):
         """Returns the delta ``[P, N, hidden]``, or None after adding it into ``residual`` in place."""
         s, K = self.spec, self.rt.kernels

@@ -27,6 +27,15 @@ Interfaces (duck-typed; the base classes document them):
 A mixer or feed-forward whose class sets ``accepts_residual = True`` also takes ``residual=h``
 and may add its output into ``h`` itself (fused into its last kernel) and return None.
 
+Optional, beside ``forward``: ``emit``.  A part whose kernel calls never change from step to step may
+write them down once in a ``StepProgram`` (``kernels/program.py``), which the library then runs for
+every step with one call from the host: ``Norm.emit(prog, h, out, rows=False)``,
+``Mixer.emit(prog, x, h, kv, state, writes_cache)`` and ``FeedForward.emit(prog, x, h)`` (both add their
+output into the stream ``h``), ``PositionEncoding.emit(prog) -> its table's buffers``,
+``Block.emit(prog, h, kv, state, writes_cache)``; buffers are the program's, by index.  ``emit`` must
+make exactly the calls ``forward`` makes.  A part without it, or one that raises ``NotProgrammable``,
+makes its model run call by call from ``forward``: nothing else changes.
+
 ``delta`` is always 32-bit ``[P, N, hidden]``: P partial sums whose total is the
 part's output (P is 1 unless a matrix product was split along its inner axis);
 the consumer adds them in ascending order.

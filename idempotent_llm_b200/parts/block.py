@@ -28,6 +28,19 @@ class PreNormBlock(Block):
             spec.feed_forward_norm, weights, p + spec.feed_forward_norm_prefix, rt)
         self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, weights, p, rt)
 
+    def emit(self, prog, h, kv, state, writes_cache: bool):
+        """The block's calls in a step program; every part must be able to emit its own."""
+        from ..kernels.program import NotProgrammable
+        parts = (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        for part in parts:
+            if not hasattr(part, "emit"):
+                raise NotProgrammable(f"{type(part).__name__} has no emit")
+        x = prog.buffer("block.x", per_token=2 * self.spec.mixer_norm.size)
+        self.mixer_norm.emit(prog, h, x)
+        self.mixer.emit(prog, x, h, kv, state, writes_cache)
+        self.feed_forward_norm.emit(prog, h, x)
+        self.feed_forward.emit(prog, x, h)
+
     def forward(self, h, pending, ctx, kv, state, writes_cache: bool):
         x = self.mixer_norm.forward(h, pending, ctx)
         if getattr(self.mixer, "accepts_residual", False):

@@ -41,6 +41,16 @@ class GatedMLP(FeedForward):
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = weights[prefix + nm.down].to(rt.dtype).contiguous()
 
+    def emit(self, prog, x, h):
+        """The calls of ``forward`` on the fused path, adding into the stream ``h``."""
+        from ..kernels.program import NotProgrammable
+        if not self.fused:
+            raise NotProgrammable("the activation as a kernel of its own is called from forward")
+        s = self.spec
+        y = prog.buffer("feed_forward.y", per_token=2 * s.intermediate)
+        prog.gemm_swiglu(x, self.w_gate_up, s.hidden, s.intermediate, y)
+        prog.gemm_residual(y, self.w_down, s.intermediate, h)
+
     def forward(self, x, ctx, residual=None):
         """Returns the delta ``[P, N, hidden]``, or None after adding it into ``residual`` in place."""
         K = self.rt.kernels

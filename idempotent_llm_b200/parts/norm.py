@@ -28,3 +28,6 @@ class RMSNorm(Norm):
 
     def forward(self, h, delta, ctx, rows=None):
         return self.rt.kernels.add_rmsnorm(h, delta, self.weight, self.spec.eps, rows=rows)
+
+    def emit(self, prog, h, out, rows=False):
+        prog.add_rmsnorm(h, self.weight, self.spec.eps, out, self.spec.size, rows=rows)

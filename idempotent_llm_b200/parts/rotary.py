@@ -25,6 +25,17 @@ class Rotary(PositionEncoding):
         j = torch.arange(0, spec.dim // 2, dtype=torch.float64)
         self.inv_freq = (float(spec.theta) ** (-2.0 * j / spec.dim)).to(rt.device)
 
+    def emit(self, prog):
+        """The table's two buffers in a step program (made once a step, like ``tables``)."""
+        key = ("rotary", float(self.spec.theta), self.spec.dim)
+        bufs = prog.shared.get(key)
+        if bufs is None:
+            per_token = self.spec.dim // 2 * 2 * 4
+            bufs = prog.shared[key] = (prog.buffer(f"rotary.{len(prog.shared)}", per_token),
+                                       prog.buffer(f"rotary.{len(prog.shared)}.by_dim", per_token))
+            prog.rope_table(self.inv_freq, *bufs)
+        return bufs
+
     def tables(self, ctx):
         key = ("rotary", float(self.spec.theta), self.spec.dim)
         t = ctx.memo.get(key)

@@ -217,6 +217,65 @@ def test_a_slot_taken_again_while_the_gpu_is_behind(loaded, dtype):
     _check_clean(lm)
 
 
+HEADS_OF_64 = dict(helpers._BASE, num_hidden_layers=3, hidden_size=136, num_attention_heads=6, num_key_value_heads=2,
+                   head_dim=64, intermediate_size=200, vocab_size=517, rope_theta=30000.0, rms_norm_eps=1e-5,
+                   tie_word_embeddings=False, max_position_embeddings=4096, initializer_range=0.04)
+
+
+@pytest.mark.parametrize("name", ["C", "heads of 64"])
+def test_a_step_by_one_call_has_the_bits_of_its_calls_one_by_one(loaded, tmp_path_factory, name):
+    """Models whose parts emit their calls run a step as one call into the library; with that switched off
+    every kernel is called from Python.  Prompts of unequal lengths, single tokens (captured and not) and
+    rows wanted from the middle: the same bits, the same number of kernels."""
+    import idempotent_llm_b200 as idm
+    if name == "C":
+        lm, cfg, w = loaded(name, "bfloat16")
+    else:
+        d = helpers.make_model_dir(HEADS_OF_64, str(tmp_path_factory.mktemp("heads64")), seed=3)
+        lm = idm.load(d, dtype="bfloat16", max_tokens=64 * 40, max_seqs=8)
+        cfg, w = plain.read_model(d)
+    eng, K = lm.engine, lm.model.rt.kernels
+    prog = lm.model.program(eng.cache)
+    assert prog is not None and prog.n_calls == 2 + 7 * cfg["num_hidden_layers"] + 2
+    V = cfg["vocab_size"]
+    reqs = [helpers.rand_ids(n, V, 400 + n) for n in (150, 1, 67, 300)]
+    wants = [[0, 70, 149], [0], [], [5, 299]]
+
+    def run():
+        before = K.launches
+        slots = [eng.open() for _ in reqs]
+        out = [eng.step(list(zip(slots, reqs)), wants).clone()]
+        for i in range(3):
+            out.append(eng.step([(s, [7 + i + k]) for k, s in enumerate(slots)]).clone())
+        out.append(eng.step([(slots[3], [11, 12, 13])], [[0, 1, 2]]).clone())
+        for s in slots:
+            eng.close(s)
+        torch.cuda.synchronize()
+        return torch.cat(out), K.launches - before
+
+    assert K.use_programs
+    run()                                    # (single-token steps are captured at their first run)
+    got, n_got = run()
+    K.use_programs = False
+    graphs, eng._graphs = eng._graphs, {}    # captured steps hold whichever way captured them
+    try:
+        run()
+        want, n_want = run()
+    finally:
+        K.use_programs, eng._graphs = True, graphs
+    assert torch.equal(got, want)
+    assert n_got == n_want
+    ref = plain.forward(cfg, w, reqs[0], rows=wants[0])
+    assert helpers.rel_err(got[:3], ref) < helpers.TOL["bfloat16"]
+    # a configuration with a window, or a head size without the fused kernels, has no program and runs as before
+    for other in ("A", "B", "D"):
+        lm2, _, _ = loaded(other, "bfloat16")
+        assert lm2.model.program(lm2.engine.cache) is None
+    lm3, _, _ = loaded("C", "float32")
+    assert lm3.model.program(lm3.engine.cache) is None
+    _check_clean(lm)
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_greedy_generation_through_the_entry_point(loaded, name, dtype):
     lm, cfg, w = loaded(name, dtype)
