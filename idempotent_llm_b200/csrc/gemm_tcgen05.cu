@@ -21,7 +21,8 @@
 //                       lane is a token), its N axis a narrow slice of 16 to 128 output features, so
 //                       that even a matrix of 1024 rows is spread over 64 blocks; each block streams
 //                       its slice of the weight once, all of it in flight before the kernel before
-//                       this one has ended.
+//                       this one has ended.  It also takes steps of more tokens, a block per 128 tokens
+//                       and slice, where the kernels below would have too few tiles for the SMs.
 //   more than 128       gemm_persistent_kernel: 128 features on the lanes, 128 or 256 tokens along the
 //                       columns, one block per SM walking over tiles, two accumulators.
 //   q/k/v, more than 128 gemm_qkv_tokens_kernel: tokens on the lanes, 256 features (whole heads) along
@@ -649,6 +650,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int f0 = blockIdx.x * bf;
+    const int t0 = blockIdx.y * 128;                             // more than 128 tokens: a block per 128 of them (and slice)
     const int n_groups = (kb_total + gk - 1) / gk;
     if (threadIdx.x == 0) block_stamp(EPI == EPI_RESIDUAL ? (kb_total > 32 ? 1 : 0) : EPI == EPI_SWIGLU ? 2 : EPI == EPI_QKV ? 3 : 4, 4);   // the block is there
 
@@ -683,9 +685,9 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
             };
             auto load_x = [&](int gi, int s) {
                 const uint32_t dst = a_base + (uint32_t)(s * gk) * a_slot;
-                if (grouped) { tma_load_3d(dst, &map_x, 0, 0, gi * gk, full_bar(s)); return; }
+                if (grouped) { tma_load_3d(dst, &map_x, 0, t0, gi * gk, full_bar(s)); return; }
                 for (int k = 0; k < gk && gi * gk + k < kb_total; ++k)
-                    tma_load_2d(dst + k * a_slot, &map_x, (gi * gk + k) * GT_BK, 0, full_bar(s));
+                    tma_load_2d(dst + k * a_slot, &map_x, (gi * gk + k) * GT_BK, t0, full_bar(s));
             };
             // (a grouped request always brings gk k-blocks: those past the end come as zeros)
             auto group_bytes = [&](int gi) { return (uint32_t)(grouped ? gk : min(gk, kb_total - gi * gk)) * (a_slot + b_slot); };
@@ -750,7 +752,8 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
         // (an accumulator of 128 rows has row i on lane i; one of 64 rows has row i on lane 32 (i / 16) + i % 16:
         // sixteen tokens on the first sixteen lanes of each warp)
         const bool m64 = gs_mma_rows(tbox) == 64;
-        const int t = m64 ? warp * 16 + lane : warp * 32 + lane;
+        const int tl = m64 ? warp * 16 + lane : warp * 32 + lane;   // the token within the block's 128, and in the step
+        const int t = t0 + tl;
         const bool live = t < n_tokens && (!m64 || lane < 16);
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         pdl_wait();
@@ -759,17 +762,17 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
             // the norm weights and this block's tokens' rows of the rotation table go to shared memory while the
             // product is being made (all four warps carry them): the epilogue then waits for no load
             const QkvArgs& a = e.q;
-            const int hd_ = a.hd, rows = min(n_tokens, tbox);
+            const int hd_ = a.hd, rows = min(n_tokens - t0, tbox);
             for (int i = threadIdx.x; i < hd_; i += 128) {
                 tab[i] = a.gq ? a.gq[i] : 0.f;
                 tab[hd_ + i] = a.gk ? a.gk[i] : 0.f;
             }
             if (a.cs != nullptr)
                 for (int i = threadIdx.x; i < rows * hd_; i += 128)
-                    tab[2 * hd_ + i] = reinterpret_cast<const float*>(a.cs)[i];        // rows of hd / 2 (cos, sin) pairs: hd floats each
+                    tab[2 * hd_ + i] = reinterpret_cast<const float*>(a.cs)[(size_t)t0 * hd_ + i];   // rows of hd / 2 (cos, sin) pairs: hd floats each
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
-        if ((m64 ? warp * 16 : warp * 32) < n_tokens) {          // (a warp without tokens has nothing to read)
+        if (t0 + (m64 ? warp * 16 : warp * 32) < n_tokens) {     // (a warp without tokens has nothing to read)
             size_t place = 0;
             if (EPI == EPI_QKV) {
                 const QkvArgs& a = e.q;
@@ -851,7 +854,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const __grid_con
                 } else if (EPI == EPI_QKV) {
                     const QkvArgs& a = e.q;
                     const int hd = a.hd, heads = a.n_q + 2 * a.n_kv;
-                    const float2* cs_row = reinterpret_cast<const float2*>(tab + 2 * hd + (live ? t : 0) * hd);
+                    const float2* cs_row = reinterpret_cast<const float2*>(tab + 2 * hd + (live ? tl : 0) * hd);
                     for (int hh = 0; hh < bf / hd; ++hh) {
                         const int head = f0 / hd + hh;
                         if (head >= heads) break;
@@ -1046,13 +1049,13 @@ static int device_sms() {
 // Features per block of the kernel for few tokens: the slice width that leaves the fullest SM the
 // fewest bytes to fetch (its blocks' weight slices plus the activations each of them reads again).
 // Wider than 128 features is never useful; the q/k/v epilogue needs whole heads.
-static int small_slice(int N, int tbox, int unit) {
+static int small_slice(int N, int tbox, int unit, int token_tiles = 1) {
     const int sms = device_sms();
     int best = 0;
     long long best_cost = 0;
     for (int bf = 16; bf <= 128; bf *= 2) {
         if (bf % unit) continue;
-        const long long blocks = (N + bf - 1) / bf;
+        const long long blocks = (long long)((N + bf - 1) / bf) * token_tiles;
         const long long cost = ((blocks + sms - 1) / sms) * (tbox + bf);
         if (best == 0 || cost < best_cost) { best = bf; best_cost = cost; }
     }
@@ -1086,7 +1089,8 @@ static int launch_small(const void* x, const void* w, const GemmEpi& e, int M, i
     const int tbox = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     int unit = 16;
     if (EPI == EPI_QKV) unit = e.q.hd < 16 ? 16 : e.q.hd;
-    int bf = g_small_bf && g_small_bf % unit == 0 ? g_small_bf : small_slice(N, tbox, unit);
+    const int token_tiles = (M + 127) / 128;
+    int bf = g_small_bf && g_small_bf % unit == 0 ? g_small_bf : small_slice(N, tbox, unit, token_tiles);
     if (EPI == EPI_QKV && bf < e.q.hd) bf = e.q.hd;
     const int kb_bytes = (tbox + bf) * 128;                       // one k-block of both operands
     // k-blocks per request and barrier: up to 64 KB, at most 8, and no more than half of the inner axis (the thread
@@ -1122,15 +1126,20 @@ static int launch_small(const void* x, const void* w, const GemmEpi& e, int M, i
         if (make_map(&mw, w, N, K, bf)) return 1;
         if (make_map(&mx, x, M, K, tbox)) return 1;
     }
-    idm_launch(gemm_small_kernel<EPI>, dim3((N + bf - 1) / bf), dim3(GS_THREADS), (size_t)smem, stream, mw, mx, e, M, N,
+    idm_launch(gemm_small_kernel<EPI>, dim3((N + bf - 1) / bf, token_tiles), dim3(GS_THREADS), (size_t)smem, stream, mw, mx, e, M, N,
                kb_total, bf, tbox, gk, grouped, stages, tmem_cols);
     IDM_LAUNCH_CHECK("gemm_small");
     return 0;
 }
 
-// Up to how many tokens the kernel with the tokens on the lanes runs (at most 128: the lanes of the accumulator).
-static int g_gemm_small_max = 128;
+// Up to 128 tokens the kernel with the tokens on the lanes runs (fewer: for measurements).  Beyond that it
+// takes a block per 128 tokens and slice, and runs where the persistent kernels would have no more than
+// `g_gemm_small_tiles` tiles for their one block per SM (measured at 129-512 tokens: products of 1024
+// features, 16-32 tiles, 18 -> 14 us and 22 -> 16 us, a whole prompt step of 0.6B sizes 2.2-2.6 -> 1.9-2.3 ms;
+// 4096 features at 129-256 tokens, 64 tiles, 4 % of a step; with more tiles the persistent kernels win).
+static int g_gemm_small_max = 128, g_gemm_small_tiles = 64;
 extern "C" void idm_gemm_set_small_max(int tokens) { g_gemm_small_max = tokens < 0 ? 0 : tokens > 128 ? 128 : tokens; }
+extern "C" void idm_gemm_set_small_tiles(int tiles) { g_gemm_small_tiles = tiles < 0 ? 0 : tiles; }
 // From how many output features on a plain product of few tokens runs with the features on the lanes.
 static int g_gemm_wide_from = 16384;
 extern "C" void idm_gemm_set_wide_from(int features) { g_gemm_wide_from = features; }
@@ -1149,8 +1158,10 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, int M, int N, int K
         IDM_REQUIRE(on32(e.q.q_out) && on32(e.q.k_new) && on32(e.q.v_new) && on32(e.q.cache.k) && on32(e.q.cache.v) &&
                     on32(e.q.cs) && on32(e.q.gq) && on32(e.q.gk), "gemm_qkv: outputs, tables and norm weights must lie on 32-byte borders");
     }
-    if (M <= g_gemm_small_max) {
-        if (EPI == EPI_STORE && N >= g_gemm_wide_from) {
+    const int token_tiles = (M + 127) / 128;
+    const long long persistent_tiles = (long long)((N + (EPI == EPI_QKV ? 255 : 127)) / (EPI == EPI_QKV ? 256 : 128)) * token_tiles;
+    if (M <= g_gemm_small_max || (M > 128 && persistent_tiles <= g_gemm_small_tiles)) {
+        if (EPI == EPI_STORE && N >= g_gemm_wide_from && M <= 128) {
             // some hundred feature tiles: features on the lanes, every epilogue thread at work
             if (M <= 16) return launch_wide<16, 6>(x, w, e.out, M, N, K, stream);
             if (M <= 32) return launch_wide<32, 6>(x, w, e.out, M, N, K, stream);

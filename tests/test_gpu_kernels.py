@@ -499,7 +499,8 @@ def test_a_product_element_is_one_chain_whatever_the_instruction(kernels):
 
 @pytest.mark.parametrize("M,N,K_", [(1, 320, 96), (8, 1024, 2048), (64, 1024, 3072), (200, 512, 1024), (300, 384, 136),
                                     (2048, 1024, 1024), (5, 151936, 64), (1030, 4096, 192), (700, 16000, 72),
-                                    (130, 4096, 4096), (8, 131, 80)])
+                                    (130, 4096, 4096), (8, 131, 80),
+                                    (513, 256, 512), (640, 1024, 2048)])   # (tokens on the lanes, a block per 128 tokens)
 def test_gemm_fused_store_and_residual(kernels, M, N, K_):
     K = kernels("bfloat16")
     x, w = _randn(M, K_, seed=74).bfloat16(), _randn(N, K_, seed=75).bfloat16()
@@ -522,7 +523,7 @@ def test_gemm_fused_store_and_residual(kernels, M, N, K_):
 
 
 @pytest.mark.parametrize("M,inter,K_", [(1, 128, 64), (8, 3072, 1024), (7, 224, 96), (130, 136, 80), (2048, 288, 160),
-                                        (1030, 2000, 192)])
+                                        (1030, 2000, 192), (400, 600, 256)])
 def test_gemm_fused_swiglu(kernels, M, inter, K_):
     K = kernels("bfloat16")
     x = _randn(M, K_, seed=77).bfloat16()
@@ -544,7 +545,8 @@ def test_gemm_fused_swiglu(kernels, M, inter, K_):
 @pytest.mark.parametrize("M,n_q,n_kv,hd,hidden", [(3, 6, 2, 32, 96), (9, 16, 8, 128, 1024),
                                                   (300, 8, 2, 128, 160), (64, 2, 1, 64, 72), (1030, 24, 4, 128, 192),
                                                   (520, 40, 12, 64, 136), (300, 6, 2, 32, 96), (130, 32, 8, 128, 4096),
-                                                  (2500, 16, 8, 128, 256)])   # (the last: three tiles per block)
+                                                  (2500, 16, 8, 128, 256),    # (three tiles per block)
+                                                  (513, 4, 2, 64, 128)])      # (tokens on the lanes, five blocks of tokens)
 def test_gemm_fused_qkv_matches_the_separate_kernels(kernels, M, n_q, n_kv, hd, hidden):
     K = kernels("bfloat16")
     x_all = _randn(M, hidden, seed=80).bfloat16().cuda()
