@@ -1140,6 +1140,9 @@ static int launch_small(const void* x, const void* w, const GemmEpi& e, int M, i
 static int g_gemm_small_max = 128, g_gemm_small_tiles = 64;
 extern "C" void idm_gemm_set_small_max(int tokens) { g_gemm_small_max = tokens < 0 ? 0 : tokens > 128 ? 128 : tokens; }
 extern "C" void idm_gemm_set_small_tiles(int tiles) { g_gemm_small_tiles = tiles < 0 ? 0 : tiles; }
+// From how many tiles of 256 tokens on the persistent kernel takes those instead of tiles of 128 tokens.
+static int g_gemm_wide_tiles = 120;
+extern "C" void idm_gemm_set_wide_tiles(int tiles) { g_gemm_wide_tiles = tiles < 1 ? 1 : tiles; }
 // From how many output features on a plain product of few tokens runs with the features on the lanes.
 static int g_gemm_wide_from = 16384;
 extern "C" void idm_gemm_set_wide_from(int features) { g_gemm_wide_from = features; }
@@ -1179,7 +1182,7 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, int M, int N, int K
     }
     // many tokens: the persistent kernel; 256-token tiles unless 128 fill more of the SMs
     const int tiles_x = (N + GT_BM - 1) / GT_BM;
-    const bool wide = (long long)tiles_x * ((M + 255) / 256) >= 120;
+    const bool wide = (long long)tiles_x * ((M + 255) / 256) >= g_gemm_wide_tiles;
     if (make_map(&mw, w, N, K, GT_BM)) return 1;
     if (make_map(&mx, x, M, K, wide ? 256 : 128)) return 1;
     return wide ? launch_persistent<256, 4, EPI>(mw, mx, e, M, N, kb_total, stream)

@@ -82,6 +82,7 @@ SIGNATURES = {
     "idm_gemm_set_small": (None, "iii"),
     "idm_gemm_set_small_max": (None, "i"),
     "idm_gemm_set_small_tiles": (None, "i"),
+    "idm_gemm_set_wide_tiles": (None, "i"),
     "idm_gemm_set_wide_from": (None, "i"),
     "idm_gemm_bf16": (c_int, "pppiiip"),
     "idm_gemm_bf16_residual": (c_int, "pppiiip"),
