@@ -14,7 +14,7 @@
 // kernels below runs.  (Sums of partial chains differ from the one chain in the last bits, which is
 // why nothing is split.)
 //
-// Three kernels.
+// The kernels.
 //   up to 128 tokens,   gemm_wide_kernel: 128 features on the lanes, the tokens along the columns, a block per 128
 //   >= 16384 features   features (the lm_head).
 //   up to 128 tokens    gemm_small_kernel: the MMA's M axis carries the step's tokens (an accumulator
@@ -24,7 +24,11 @@
 //                       this one has ended.  It also takes steps of more tokens, a block per 128 tokens
 //                       and slice, where the kernels below would have too few tiles for the SMs.
 //   more than 128       gemm_persistent_kernel: 128 features on the lanes, 128 or 256 tokens along the
-//                       columns, one block per SM walking over tiles, two accumulators.
+//                       columns, one block per SM walking over tiles, two accumulators; the tiles in bands
+//                       of the weight that stay in the L2.  gemm_pair_kernel: the same with the two blocks
+//                       of a cluster on one tile of 256 features x 256 tokens (cta_group::2: each block
+//                       fetches half of the token tile), for stored and residual products with tiles
+//                       enough for every pair of SMs.
 //   q/k/v, more than 128 gemm_qkv_tokens_kernel: tokens on the lanes, 256 features (whole heads) along
 //                       the columns.
 //
@@ -127,11 +131,90 @@ struct PersistSmem {
 
 __device__ __forceinline__ void group_sync(int g) { asm volatile("bar.sync %0, 128;" ::"r"(1 + g) : "memory"); }     // one group
 
+// Where tile number `tile` of a persistent kernel lies: tiles are walked in bands of `band` feature tiles, inside a
+// band token tile after token tile, so that the blocks at work together read a band of the weight that stays in the
+// L2 (a weight of some hundred MB walked whole for every row of token tiles came from HBM every time: 33 GB for one
+// product of 32B sizes with 16 384 tokens).
+__device__ __forceinline__ void tile_place(int tile, int tiles_x, int n_tiles, int band, int& fx, int& ty) {
+    const int tiles_y = n_tiles / tiles_x, per_band = band * tiles_y;
+    const int b = tile / per_band, r = tile - b * per_band;
+    const int width = min(band, tiles_x - b * band);               // the last band may be narrower
+    ty = r / width;
+    fx = b * band + r % width;
+}
+
+// The epilogue of one tile of the persistent kernels: the accumulator at `tmem_acc` (128 lanes = features f0 .., BN
+// columns = tokens t0 ..) goes out as the EPI says.  Called by the 16 epilogue warps (group `grp`, accumulator
+// lanes 32 `quarter` ..); `xs`: the group's buffer of [16 tokens][128 features] floats; `tx`: f0 / 128.
+template <int BN, int EPI>
+__device__ __forceinline__ void persistent_tile_epilogue(const GemmEpi& e, uint32_t tmem_acc, float* xs, int grp, int quarter,
+                                                         int lane, int tx, int t0, int n_tokens, int n_features) {
+    const int fl = quarter * 32 + lane;                            // feature within the tile = accumulator lane
+    const int f0 = tx * GT_BM, f = f0 + fl;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    // the accumulator columns of a chunk are asked for while the chunk before is worked on (two sets of
+    // registers in turn; the loop is unrolled so that which set is which is known at compile time)
+    uint32_t raw[2][GP_CHUNK];
+    if (t0 + grp * GP_CHUNK < n_tokens) tc_ld16_issue(tmem_acc + lane_base + (uint32_t)(grp * GP_CHUNK), raw[0]);
+#pragma unroll
+    for (int ci = 0; ci < BN / (GP_GROUPS * GP_CHUNK); ++ci) {
+        const int c0 = grp * GP_CHUNK + ci * GP_GROUPS * GP_CHUNK;
+        if (t0 + c0 >= n_tokens) break;                    // uniform over the group
+        const int cols = min(GP_CHUNK, n_tokens - t0 - c0);
+        float v[GP_CHUNK];
+        tc_ld_wait();
+#pragma unroll
+        for (int j = 0; j < GP_CHUNK; ++j) v[j] = __uint_as_float(raw[ci & 1][j]);
+        if (ci + 1 < BN / (GP_GROUPS * GP_CHUNK) && t0 + c0 + GP_GROUPS * GP_CHUNK < n_tokens)
+            tc_ld16_issue(tmem_acc + lane_base + (uint32_t)(c0 + GP_GROUPS * GP_CHUNK), raw[(ci + 1) & 1]);
+        if (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+            if (f < n_features) {
+                float old[GP_CHUNK];
+                if (EPI == EPI_RESIDUAL) {
+#pragma unroll
+                    for (int j = 0; j < GP_CHUNK; ++j)
+                        old[j] = j < cols ? e.out[(size_t)(t0 + c0 + j) * n_features + f] : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < GP_CHUNK; ++j)
+                    if (j < cols)
+                        e.out[(size_t)(t0 + c0 + j) * n_features + f] = EPI == EPI_RESIDUAL ? old[j] + v[j] : v[j];
+            }
+        } else {
+            // through shared memory, so that a thread ends up with consecutive features of one token
+#pragma unroll
+            for (int j = 0; j < GP_CHUNK; ++j) xs[j * GT_BM + fl] = v[j];
+            group_sync(grp);
+            if (EPI == EPI_SWIGLU) {
+                // 8 consecutive features of y (16 tile rows: gate, up, gate, up, ...) per thread, one
+                // 16-byte store; the group's 128 threads cover the chunk's 16 token rows
+                const int j = fl >> 3, sub = fl & 7;
+                if (j < cols) {
+                    const float4* src = reinterpret_cast<const float4*>(xs + j * GT_BM + sub * 16);
+                    const float4 p0 = src[0], p1 = src[1], p2 = src[2], p3 = src[3];
+                    const float y8[8] = {silu_mul(p0.x, p0.y), silu_mul(p0.z, p0.w), silu_mul(p1.x, p1.y), silu_mul(p1.z, p1.w),
+                                         silu_mul(p2.x, p2.y), silu_mul(p2.z, p2.w), silu_mul(p3.x, p3.y), silu_mul(p3.z, p3.w)};
+                    const int fg = tx * 64 + sub * 8;
+                    T* dst = e.y + (size_t)(t0 + c0 + j) * e.inter + fg;
+                    if ((e.inter & 7) == 0 && fg + 8 <= e.inter) {
+                        store8(dst, y8);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (fg + i < e.inter) from_f32(dst[i], y8[i]);
+                    }
+                }
+            }
+            group_sync(grp);                               // the buffer is free for the group's next chunk
+        }
+    }
+}
+
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                      const __grid_constant__ CUtensorMap map_x,
                                                                      const GemmEpi e, int n_tokens, int n_features,
-                                                                     int kb_total, int tiles_x, int n_tiles) {
+                                                                     int kb_total, int tiles_x, int n_tiles, int band) {
     using S = PersistSmem<BN, STAGES>;
     constexpr int TMEM_COLS = 2 * BN;                              // 256 or 512
     extern __shared__ uint8_t smem_raw[];
@@ -164,7 +247,9 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __gri
         if (lane == 0) {
             uint32_t cnt = 0;                                      // k-blocks issued so far, over all tiles
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-                const int f0 = (tile % tiles_x) * GT_BM, t0 = (tile / tiles_x) * BN;
+                int fx, ty;
+                tile_place(tile, tiles_x, n_tiles, band, fx, ty);
+                const int f0 = fx * GT_BM, t0 = ty * BN;
                 bool ok = true;
                 for (int i = 0; i < kb_total && ok; ++i, ++cnt) {
                     const int s = cnt % STAGES;
@@ -212,73 +297,17 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __gri
         // ------------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3, grp = warp >> 2;             // accumulator lanes 32 quarter ..; group 0 or 1
         float* xs = (float*)(gen_base + S::XS_OFF) + grp * (GP_CHUNK * GT_BM);
-        const int fl = quarter * 32 + lane;                        // feature within the tile = accumulator lane
-        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-            const int tx = tile % tiles_x, f0 = tx * GT_BM, t0 = (tile / tiles_x) * BN;
-            const int f = f0 + fl;
+            int tx, ty;
+            tile_place(tile, tiles_x, n_tiles, band, tx, ty);
+            const int t0 = ty * BN;
             const uint32_t acc = it & 1;
             ok = mbar_wait(tfull_bar(acc), (it >> 1) & 1, abort_flag, &g_gemm_error);
             if (!ok) break;
             tc_fence_after();
-            // the accumulator columns of a chunk are asked for while the chunk before is worked on (two sets of
-            // registers in turn; the loop is unrolled so that which set is which is known at compile time)
-            uint32_t raw[2][GP_CHUNK];
-            if (t0 + grp * GP_CHUNK < n_tokens) tc_ld16_issue(tmem + acc * BN + lane_base + (uint32_t)(grp * GP_CHUNK), raw[0]);
-#pragma unroll
-            for (int ci = 0; ci < BN / (GP_GROUPS * GP_CHUNK); ++ci) {
-                const int c0 = grp * GP_CHUNK + ci * GP_GROUPS * GP_CHUNK;
-                if (t0 + c0 >= n_tokens) break;                    // uniform over the group
-                const int cols = min(GP_CHUNK, n_tokens - t0 - c0);
-                float v[GP_CHUNK];
-                tc_ld_wait();
-#pragma unroll
-                for (int j = 0; j < GP_CHUNK; ++j) v[j] = __uint_as_float(raw[ci & 1][j]);
-                if (ci + 1 < BN / (GP_GROUPS * GP_CHUNK) && t0 + c0 + GP_GROUPS * GP_CHUNK < n_tokens)
-                    tc_ld16_issue(tmem + acc * BN + lane_base + (uint32_t)(c0 + GP_GROUPS * GP_CHUNK), raw[(ci + 1) & 1]);
-                if (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
-                    if (f < n_features) {
-                        float old[GP_CHUNK];
-                        if (EPI == EPI_RESIDUAL) {
-#pragma unroll
-                            for (int j = 0; j < GP_CHUNK; ++j)
-                                old[j] = j < cols ? e.out[(size_t)(t0 + c0 + j) * n_features + f] : 0.f;
-                        }
-#pragma unroll
-                        for (int j = 0; j < GP_CHUNK; ++j)
-                            if (j < cols)
-                                e.out[(size_t)(t0 + c0 + j) * n_features + f] = EPI == EPI_RESIDUAL ? old[j] + v[j] : v[j];
-                    }
-                } else {
-                    // through shared memory, so that a thread ends up with consecutive features of one token
-#pragma unroll
-                    for (int j = 0; j < GP_CHUNK; ++j) xs[j * GT_BM + fl] = v[j];
-                    group_sync(grp);
-                    if (EPI == EPI_SWIGLU) {
-                        // 8 consecutive features of y (16 tile rows: gate, up, gate, up, ...) per thread, one
-                        // 16-byte store; the group's 128 threads cover the chunk's 16 token rows
-                        const int j = fl >> 3, sub = fl & 7;
-                        if (j < cols) {
-                            const float4* src = reinterpret_cast<const float4*>(xs + j * GT_BM + sub * 16);
-                            const float4 p0 = src[0], p1 = src[1], p2 = src[2], p3 = src[3];
-                            const float y8[8] = {silu_mul(p0.x, p0.y), silu_mul(p0.z, p0.w), silu_mul(p1.x, p1.y), silu_mul(p1.z, p1.w),
-                                                 silu_mul(p2.x, p2.y), silu_mul(p2.z, p2.w), silu_mul(p3.x, p3.y), silu_mul(p3.z, p3.w)};
-                            const int fg = tx * 64 + sub * 8;
-                            T* dst = e.y + (size_t)(t0 + c0 + j) * e.inter + fg;
-                            if ((e.inter & 7) == 0 && fg + 8 <= e.inter) {
-                                store8(dst, y8);
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < 8; ++i)
-                                    if (fg + i < e.inter) from_f32(dst[i], y8[i]);
-                            }
-                        }
-                    }
-                    group_sync(grp);                               // the buffer is free for the group's next chunk
-                }
-            }
+            persistent_tile_epilogue<BN, EPI>(e, tmem + acc * BN, xs, grp, quarter, lane, tx, t0, n_tokens, n_features);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -287,6 +316,140 @@ __global__ void __launch_bounds__(GP_THREADS) gemm_persistent_kernel(const __gri
     tc_fence_before();
     __syncthreads();
     if (warp == GP_EPI_WARPS + 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// --------------------------------------------------- many tokens, a pair of blocks on one tile (cta_group::2)
+// The persistent scheme above with tiles of 256 features x BN tokens worked by the two blocks of a cluster: block
+// r holds features f0 + 128 r .. (its rows of w, its half of the accumulator) and fetches tokens t0 + BN/2 r ..
+// (its half of the rows of x); block 0's MMA thread issues every MMA for both.  Per k-block a block fetches
+// 128 + BN/2 rows for 128 x BN products, where the kernel above fetches 128 + BN: the way from the L2 to the SMs
+// is what bounds these products.  Who waits for whom:
+//   full[s]    in block 0: the bytes of both blocks' loads of stage s (each block's TMA counts there)
+//   empty[s]   in each block: stage s has been read by the MMAs (a commit to both blocks)
+//   tfull[a]   in each block: accumulator a is complete (a commit to both blocks)
+//   tempty[a]  in block 0: the epilogue warps of BOTH blocks have read accumulator a
+// Every wait is bounded; a block whose wait ran out falls through to the end, where both blocks meet before
+// tensor memory is given back (the other block's waits then run out by themselves).
+template <int BN, int STAGES>
+struct PairSmem {
+    static constexpr int A_BYTES = GT_BM * GT_BK * 2;
+    static constexpr int B_BYTES = (BN / 2) * GT_BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int XS_BYTES = GP_GROUPS * GP_CHUNK * GT_BM * 4;
+    static constexpr int XS_OFF = STAGES * STAGE_BYTES;
+    static constexpr int BAR_OFF = XS_OFF + XS_BYTES;
+    static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(GP_THREADS) gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                               const __grid_constant__ CUtensorMap map_x,
+                                                               const GemmEpi e, int n_tokens, int n_features,
+                                                               int kb_total, int tiles_x, int n_tiles, int band) {
+    using S = PairSmem<BN, STAGES>;
+    constexpr int TMEM_COLS = 2 * BN;                              // 256 or 512
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + S::BAR_OFF;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + S::BAR_OFF + 8 * (2 * STAGES + 4));
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                          // 0: issues the MMAs
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 2 * GP_EPI_WARPS); }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == GP_EPI_WARPS + 1) tmem_alloc_pair(smem_u32((const void*)tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                            // the other block's barriers exist before anything arrives there
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    pdl_wait();
+
+    if (warp == GP_EPI_WARPS) {
+        if (lane == 0) {
+            uint32_t cnt = 0;                                      // k-blocks issued so far, over all tiles
+            for (int tile = pair; tile < n_tiles; tile += n_pairs) {
+                int fx, ty;
+                tile_place(tile, tiles_x, n_tiles, band, fx, ty);
+                const int f0 = fx * (2 * GT_BM) + (int)rank * GT_BM;
+                const int t0 = ty * BN + (int)rank * (BN / 2);
+                bool ok = true;
+                for (int i = 0; i < kb_total && ok; ++i, ++cnt) {
+                    const int s = cnt % STAGES;
+                    ok = mbar_wait_cluster(empty_bar(s), ((cnt / STAGES) & 1) ^ 1, abort_flag, &g_gemm_error);
+                    if (!ok) break;
+                    if (rank == 0) mbar_expect_tx(full_bar(s), 2 * S::STAGE_BYTES);
+                    const uint32_t a_dst = base + s * S::STAGE_BYTES;
+                    const uint32_t full0 = mapa_u32(full_bar(s), 0);
+                    tma_load_2d_pair(a_dst, &map_w, i * GT_BK, f0, full0);
+                    tma_load_2d_pair(a_dst + S::A_BYTES, &map_x, i * GT_BK, t0, full0);
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == GP_EPI_WARPS + 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = umma_idesc(2 * GT_BM, BN);
+            uint32_t cnt = 0, it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
+                const uint32_t acc = it & 1;
+                ok = mbar_wait_cluster(tempty_bar(acc), ((it >> 1) & 1) ^ 1, abort_flag, &g_gemm_error);   // both epilogues drained it
+                if (!ok) break;
+                tc_fence_after();
+                for (int i = 0; i < kb_total && ok; ++i, ++cnt) {
+                    const int s = cnt % STAGES;
+                    ok = mbar_wait_cluster(full_bar(s), (cnt / STAGES) & 1, abort_flag, &g_gemm_error);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * S::STAGE_BYTES;
+                    const uint64_t a_desc = umma_desc_kmajor(a_addr), b_desc = umma_desc_kmajor(a_addr + S::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < GT_BK / GT_UMMA_K; ++k)
+                        tc_mma_bf16_pair(tmem + acc * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    tc_commit_pair(empty_bar(s), 3u);
+                }
+                if (ok) tc_commit_pair(tfull_bar(acc), 3u);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps (of both blocks)
+        const int quarter = warp & 3, grp = warp >> 2;
+        float* xs = (float*)(gen_base + S::XS_OFF) + grp * (GP_CHUNK * GT_BM);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
+            int fx, ty;
+            tile_place(tile, tiles_x, n_tiles, band, fx, ty);
+            const int tx = fx * 2 + (int)rank, t0 = ty * BN;
+            const uint32_t acc = it & 1;
+            ok = mbar_wait_cluster(tfull_bar(acc), (it >> 1) & 1, abort_flag, &g_gemm_error);
+            if (!ok) break;
+            tc_fence_after();
+            persistent_tile_epilogue<BN, EPI>(e, tmem + acc * BN, xs, grp, quarter, lane, tx, t0, n_tokens, n_features);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));
+        }
+    }
+    // nobody leaves, and no tensor memory goes back, while the other block may still read this one's shared
+    // memory, count at its barriers or run MMAs into its accumulators
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == GP_EPI_WARPS + 1) tmem_dealloc_pair(tmem, TMEM_COLS);
 }
 
 // ------------------------------------------------- q/k/v projection of many tokens, tokens on the lanes
@@ -578,6 +741,16 @@ static int launch_qkv_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const
     return 0;
 }
 
+// Feature tiles per band of the persistent kernels' walk: as many as hold `g_gemm_band_mb` MB of the weight.
+static int g_gemm_band_mb = 32;
+extern "C" void idm_gemm_set_band_mb(int mb) { g_gemm_band_mb = mb < 1 ? 1 : mb; }
+static int tile_band(int tile_rows, int kb_total, int tiles_x) {
+    const long long tile_bytes = (long long)tile_rows * kb_total * GT_BK * 2;
+    long long band = ((long long)g_gemm_band_mb << 20) / tile_bytes;
+    if (band < 1) band = 1;
+    return band > tiles_x ? tiles_x : (int)band;
+}
+
 template <int BN, int STAGES, int EPI>
 static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
                              cudaStream_t stream) {
@@ -598,8 +771,43 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const
     const int n_tiles = tiles_x * tiles_y;
     const int grid = n_tiles < n_sm ? n_tiles : n_sm;
     idm_launch(gemm_persistent_kernel<BN, STAGES, EPI>, dim3(grid), dim3(GP_THREADS), S::TOTAL, stream, mw, mx, e, M, N,
-               kb_total, tiles_x, n_tiles);
+               kb_total, tiles_x, n_tiles, tile_band(GT_BM, kb_total, tiles_x));
     IDM_LAUNCH_CHECK("gemm_persistent");
+    return 0;
+}
+template <int BN, int STAGES, int EPI>
+static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
+                       cudaStream_t stream) {
+    using S = PairSmem<BN, STAGES>;
+    static bool configured = false;
+    static int n_sm = 0;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_pair_kernel<BN, STAGES, EPI>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        IDM_REQUIRE(err == cudaSuccess, "gemm: cannot get %d bytes of shared memory: %s", S::TOTAL,
+                    cudaGetErrorString(err));
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    const int tiles_x = (N + 2 * GT_BM - 1) / (2 * GT_BM), tiles_y = (M + BN - 1) / BN;
+    const int n_tiles = tiles_x * tiles_y;
+    const int pairs = n_tiles < n_sm / 2 ? n_tiles : n_sm / 2;
+    // (a cluster of two blocks along x: idm_launch_cluster puts the cluster along z, so the grid is [1, 1, 2 pairs]...)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(GP_THREADS); cfg.dynamicSmemBytes = S::TOTAL; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = idm_pdl_enabled() ? 2 : 1;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<BN, STAGES, EPI>, mw, mx, e, M, N, kb_total, tiles_x, n_tiles,
+                                         tile_band(2 * GT_BM, kb_total, tiles_x));
+    IDM_REQUIRE(err == cudaSuccess, "gemm_pair: launch failed: %s", cudaGetErrorString(err));
+    IDM_LAUNCH_CHECK("gemm_pair");
     return 0;
 }
 // ------------------------------------------------------------------- few tokens (up to 128)
@@ -1140,6 +1348,12 @@ static int launch_small(const void* x, const void* w, const GemmEpi& e, int M, i
 static int g_gemm_small_max = 128, g_gemm_small_tiles = 64;
 extern "C" void idm_gemm_set_small_max(int tokens) { g_gemm_small_max = tokens < 0 ? 0 : tokens > 128 ? 128 : tokens; }
 extern "C" void idm_gemm_set_small_tiles(int tiles) { g_gemm_small_tiles = tiles < 0 ? 0 : tiles; }
+// Whether products of many tokens may run on pairs of blocks (cta_group::2), and from how many tiles of 256 x 256 on.
+static int g_gemm_pair = 1, g_gemm_pair_tiles = 60;
+extern "C" void idm_gemm_set_pair(int on, int tiles) {
+    g_gemm_pair = on ? 1 : 0;
+    if (tiles > 0) g_gemm_pair_tiles = tiles;
+}
 // From how many tiles of 256 tokens on the persistent kernel takes those instead of tiles of 128 tokens.
 static int g_gemm_wide_tiles = 120;
 extern "C" void idm_gemm_set_wide_tiles(int tiles) { g_gemm_wide_tiles = tiles < 1 ? 1 : tiles; }
@@ -1179,6 +1393,16 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, int M, int N, int K
         if (make_map(&mw, w, N, K, GQ_BN)) return 1;
         if (make_map(&mx, x, M, K, GT_BM)) return 1;
         return launch_qkv_tokens(mw, mx, e, M, N, kb_total, stream);
+    }
+    // many tokens, a product that is stored or added to the stream, tiles enough for every pair of SMs: pairs of blocks
+    // on tiles of 256 features x 256 tokens (measured at 8B sizes, 6 208 tokens: o 168 -> 151 us, down 485 -> 442 us;
+    // at 32B sizes level; the SwiGLU product is as fast on single blocks once its walk stays in the L2, and products
+    // of 1 024 features have too few such tiles)
+    if (g_gemm_pair && (EPI == EPI_STORE || EPI == EPI_RESIDUAL) &&
+        (long long)((N + 2 * GT_BM - 1) / (2 * GT_BM)) * ((M + 255) / 256) >= g_gemm_pair_tiles) {
+        if (make_map(&mw, w, N, K, GT_BM)) return 1;
+        if (make_map(&mx, x, M, K, 128)) return 1;
+        return launch_pair<256, 6, EPI>(mw, mx, e, M, N, kb_total, stream);
     }
     // many tokens: the persistent kernel; 256-token tiles unless 128 fill more of the SMs
     const int tiles_x = (N + GT_BM - 1) / GT_BM;

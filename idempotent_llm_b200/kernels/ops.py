@@ -83,6 +83,8 @@ SIGNATURES = {
     "idm_gemm_set_small_max": (None, "i"),
     "idm_gemm_set_small_tiles": (None, "i"),
     "idm_gemm_set_wide_tiles": (None, "i"),
+    "idm_gemm_set_pair": (None, "ii"),
+    "idm_gemm_set_band_mb": (None, "i"),
     "idm_gemm_set_wide_from": (None, "i"),
     "idm_gemm_bf16": (c_int, "pppiiip"),
     "idm_gemm_bf16_residual": (c_int, "pppiiip"),
@@ -465,6 +467,21 @@ class Kernels:
             else:
                 self._check(self.lib.idm_gemm_bf16(_p(x), _p(w), _p(out), M, N, Kd, self._stream()))
         return out
+
+    def gemm_choices(self, pair: Optional[bool] = None, lanes_up_to_tiles: Optional[int] = None,
+                     band_mb: Optional[int] = None) -> None:
+        """Which kernel a product of many tokens takes (tests compare them bit for bit; measurements): ``pair``:
+        pairs of blocks on a tile where there are tiles enough, or never; ``lanes_up_to_tiles``: up to how many
+        tiles of the persistent kernels a step of more than 128 tokens stays on the kernel with the tokens on the
+        lanes; ``band_mb``: MB of the weight in a band of the persistent kernels' walk."""
+        if self.dtype != torch.bfloat16:
+            return
+        if pair is not None:
+            self.lib.idm_gemm_set_pair(1 if pair else 0, 0)
+        if lanes_up_to_tiles is not None:
+            self.lib.idm_gemm_set_small_tiles(int(lanes_up_to_tiles))
+        if band_mb is not None:
+            self.lib.idm_gemm_set_band_mb(int(band_mb))
 
     # ---- fused epilogues (bfloat16 only) ------------------------------------------------------------
     def gemm_residual(self, x, w, h) -> None:

@@ -522,6 +522,36 @@ def test_gemm_fused_store_and_residual(kernels, M, N, K_):
     assert K.gemm_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K_", [(2048, 2048, 512), (1500, 4000, 200), (777, 16000, 72), (300, 1024, 2048)])
+def test_every_way_to_make_a_product_of_many_tokens_gives_the_same_bits(kernels, M, N, K_):
+    """One block per tile, the two blocks of a cluster on one tile (cta_group::2), the kernel with the tokens on
+    the lanes taken beyond 128 tokens, and the tiles walked in bands of other widths: one chain per element in
+    all of them."""
+    K = kernels("bfloat16")
+    x, w = _randn(M, K_, seed=84).bfloat16().cuda(), _randn(N, K_, seed=85).bfloat16().cuda()
+    h0 = _randn(M, N, seed=86, scale=3.0).float().cuda()
+    ways = {"single blocks": dict(pair=False, lanes_up_to_tiles=0, band_mb=32),
+            "pairs of blocks": dict(pair=True, lanes_up_to_tiles=0, band_mb=32),
+            "tokens on the lanes": dict(pair=False, lanes_up_to_tiles=1 << 20, band_mb=32),
+            "narrow bands": dict(pair=True, lanes_up_to_tiles=0, band_mb=1)}
+    got = {}
+    try:
+        for name, how in ways.items():
+            K.gemm_choices(**how)
+            h = h0.clone()
+            K.gemm_residual(x, w, h)
+            got[name] = (K.gemm_store(x, w), h)
+    finally:
+        K.gemm_choices(pair=True, lanes_up_to_tiles=64, band_mb=32)
+    torch.cuda.synchronize()
+    assert K.gemm_status() == 0
+    ref = x.double().cpu() @ w.double().cpu().T
+    assert helpers.rel_err(got["single blocks"][0], ref) < 2e-5
+    for name in list(ways)[1:]:
+        assert torch.equal(got[name][0], got["single blocks"][0]), name
+        assert torch.equal(got[name][1], got["single blocks"][1]), name + " (added to the stream)"
+
+
 @pytest.mark.parametrize("M,inter,K_", [(1, 128, 64), (8, 3072, 1024), (7, 224, 96), (130, 136, 80), (2048, 288, 160),
                                         (1030, 2000, 192), (400, 600, 256)])
 def test_gemm_fused_swiglu(kernels, M, inter, K_):
