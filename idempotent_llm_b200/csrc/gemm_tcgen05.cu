@@ -588,7 +588,7 @@ __device__ __forceinline__ void qkv_tokens_head(const QkvArgs& a, uint32_t col0,
 __global__ void __launch_bounds__(GQ_THREADS) gemm_qkv_tokens_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                      const __grid_constant__ CUtensorMap map_x,
                                                                      const GemmEpi e, int n_tokens, int n_features,
-                                                                     int kb_total, int tiles_x, int n_tiles) {
+                                                                     int kb_total, int tiles_x, int n_tiles, int band) {
     using S = QkvTokensSmem;
     constexpr int STAGES = GQ_STAGES, BN = GQ_BN;
     constexpr int TMEM_COLS = 2 * BN;
@@ -622,7 +622,9 @@ __global__ void __launch_bounds__(GQ_THREADS) gemm_qkv_tokens_kernel(const __gri
         if (lane == 0) {
             uint32_t cnt = 0;
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-                const int f0 = (tile % tiles_x) * BN, t0 = (tile / tiles_x) * GT_BM;
+                int fx, ty;
+                tile_place(tile, tiles_x, n_tiles, band, fx, ty);
+                const int f0 = fx * BN, t0 = ty * GT_BM;
                 bool ok = true;
                 for (int i = 0; i < kb_total && ok; ++i, ++cnt) {
                     const int s = cnt % STAGES;
@@ -670,7 +672,9 @@ __global__ void __launch_bounds__(GQ_THREADS) gemm_qkv_tokens_kernel(const __gri
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-            const int tx = tile % tiles_x, f0 = tx * BN, t0 = (tile / tiles_x) * GT_BM;
+            int tx, ty;
+            tile_place(tile, tiles_x, n_tiles, band, tx, ty);
+            const int f0 = tx * BN, t0 = ty * GT_BM;
             const uint32_t acc = it & 1;
             const int t = t0 + quarter * 32 + lane;                // this thread's token
             const bool live = t < n_tokens;
@@ -719,6 +723,16 @@ __global__ void __launch_bounds__(GQ_THREADS) gemm_qkv_tokens_kernel(const __gri
     if (warp == GQ_EPI_WARPS + 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// Feature tiles per band of the persistent kernels' walk: as many as hold `g_gemm_band_mb` MB of the weight.
+static int g_gemm_band_mb = 32;
+extern "C" void idm_gemm_set_band_mb(int mb) { g_gemm_band_mb = mb < 1 ? 1 : mb; }
+static int tile_band(int tile_rows, int kb_total, int tiles_x) {
+    const long long tile_bytes = (long long)tile_rows * kb_total * GT_BK * 2;
+    long long band = ((long long)g_gemm_band_mb << 20) / tile_bytes;
+    if (band < 1) band = 1;
+    return band > tiles_x ? tiles_x : (int)band;
+}
+
 static int launch_qkv_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const GemmEpi& e, int M, int N, int kb_total,
                              cudaStream_t stream) {
     using S = QkvTokensSmem;
@@ -736,19 +750,9 @@ static int launch_qkv_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const
     const int n_tiles = tiles_x * tiles_y;
     const int grid = n_tiles < n_sm ? n_tiles : n_sm;
     idm_launch(gemm_qkv_tokens_kernel, dim3(grid), dim3(GQ_THREADS), S::TOTAL, stream, mw, mx, e, M, N, kb_total, tiles_x,
-               n_tiles);
+               n_tiles, tile_band(GQ_BN, kb_total, tiles_x));
     IDM_LAUNCH_CHECK("gemm_qkv_tokens");
     return 0;
-}
-
-// Feature tiles per band of the persistent kernels' walk: as many as hold `g_gemm_band_mb` MB of the weight.
-static int g_gemm_band_mb = 32;
-extern "C" void idm_gemm_set_band_mb(int mb) { g_gemm_band_mb = mb < 1 ? 1 : mb; }
-static int tile_band(int tile_rows, int kb_total, int tiles_x) {
-    const long long tile_bytes = (long long)tile_rows * kb_total * GT_BK * 2;
-    long long band = ((long long)g_gemm_band_mb << 20) / tile_bytes;
-    if (band < 1) band = 1;
-    return band > tiles_x ? tiles_x : (int)band;
 }
 
 template <int BN, int STAGES, int EPI>
