@@ -306,6 +306,12 @@ def main(argv=None) -> int:
     k.add_argument("--capacity", type=int, default=4096)
     k.add_argument("--tokens", type=int, default=8)
     k.add_argument("--reps", type=int, default=10)
+    k.add_argument("--pairs", type=int, choices=[0, 1], default=None,
+                   help="products of many tokens: pairs of blocks on a tile where there are tiles enough (1), or never (0)")
+    k.add_argument("--band-mb", type=int, default=None,
+                   help="products of many tokens: MB of the weight in a band of the tiles' walk (a huge value: no bands)")
+    k.add_argument("--lanes-up-to-tiles", type=int, default=None,
+                   help="more than 128 tokens stay on the kernel with the tokens on the lanes up to that many persistent tiles")
     k.set_defaults(fn=cmd_kernel_bench)
 
     p = sub.add_parser("replay", help="trace replay (same as bin/trace_run)", add_help=False)

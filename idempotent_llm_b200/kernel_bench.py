@@ -15,6 +15,9 @@ def run(args) -> int:
     from .kernels import Kernels
     cfg = preset(args.size)
     K = Kernels(torch.bfloat16, "cuda:0")
+    # which kernel a product of many tokens takes (defaults: what the library chooses by itself)
+    K.gemm_choices(pair=None if getattr(args, "pairs", None) is None else bool(args.pairs),
+                   band_mb=getattr(args, "band_mb", None), lanes_up_to_tiles=getattr(args, "lanes_up_to_tiles", None))
     n_q, n_kv, hd, H, I = (cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size,
                            cfg.intermediate_size)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
