@@ -1265,7 +1265,7 @@ static int small_slice(int N, int tbox, int unit, int token_tiles = 1) {
     const int sms = device_sms();
     int best = 0;
     long long best_cost = 0;
-    for (int bf = 16; bf <= 128; bf *= 2) {
+    for (int bf = 16; bf <= 128; bf += 16) {
         if (bf % unit) continue;
         const long long blocks = (long long)((N + bf - 1) / bf) * token_tiles;
         const long long cost = ((blocks + sms - 1) / sms) * (tbox + bf);
