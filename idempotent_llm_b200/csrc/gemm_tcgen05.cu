@@ -798,7 +798,7 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmE
     const int tiles_x = (N + 2 * GT_BM - 1) / (2 * GT_BM), tiles_y = (M + BN - 1) / BN;
     const int n_tiles = tiles_x * tiles_y;
     const int pairs = n_tiles < n_sm / 2 ? n_tiles : n_sm / 2;
-    // (a cluster of two blocks along x: idm_launch_cluster puts the cluster along z, so the grid is [1, 1, 2 pairs]...)
+    // a cluster of two blocks along x: blocks 2 p and 2 p + 1 are pair p
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(GP_THREADS); cfg.dynamicSmemBytes = S::TOTAL; cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -1402,11 +1402,12 @@ static int gemm_any(const void* x, const void* w, GemmEpi e, int M, int N, int K
     // on tiles of 256 features x 256 tokens (measured at 8B sizes, 6 208 tokens: o 168 -> 151 us, down 485 -> 442 us;
     // at 32B sizes level; the SwiGLU product is as fast on single blocks once its walk stays in the L2, and products
     // of 1 024 features have too few such tiles)
-    if (g_gemm_pair && (EPI == EPI_STORE || EPI == EPI_RESIDUAL) &&
-        (long long)((N + 2 * GT_BM - 1) / (2 * GT_BM)) * ((M + 255) / 256) >= g_gemm_pair_tiles) {
-        if (make_map(&mw, w, N, K, GT_BM)) return 1;
-        if (make_map(&mx, x, M, K, 128)) return 1;
-        return launch_pair<256, 6, EPI>(mw, mx, e, M, N, kb_total, stream);
+    if constexpr (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+        if (g_gemm_pair && (long long)((N + 2 * GT_BM - 1) / (2 * GT_BM)) * ((M + 255) / 256) >= g_gemm_pair_tiles) {
+            if (make_map(&mw, w, N, K, GT_BM)) return 1;
+            if (make_map(&mx, x, M, K, 128)) return 1;
+            return launch_pair<256, 6, EPI>(mw, mx, e, M, N, kb_total, stream);
+        }
     }
     // many tokens: the persistent kernel; 256-token tiles unless 128 fill more of the SMs
     const int tiles_x = (N + GT_BM - 1) / GT_BM;
