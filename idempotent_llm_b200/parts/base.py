@@ -44,7 +44,7 @@ the consumer adds them in ascending order.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, List
+from typing import Dict, List
 
 import torch
 
