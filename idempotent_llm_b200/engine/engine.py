@@ -171,7 +171,7 @@ class Engine:
         self.use_graph = use_graph and self.device.type == "cuda"
         self._graphs: Dict[object, _DecodeGraph] = {}    # by batch size, or (batch size, temperature, keys)
         self._graph_pool = None
-        self._pinned: Dict[int, torch.Tensor] = {}
+        self._pinned: Dict[int, list] = {}
         self.steps_run = 0
 
     # slots ------------------------------------------------------------------
@@ -286,17 +286,29 @@ class Engine:
         return picked, g.logits
 
     def _upload(self, host: torch.Tensor) -> torch.Tensor:
+        """A step's packed integers to the device through pinned memory.  The copy reads the pinned buffer when
+        the GPU gets to it, so a buffer is written again only after the event behind its last copy; two buffers
+        per size take turns, so that the host can pack the next step while the GPU is still on this one."""
         if self.device.type != "cuda":
             return host.to(self.device)
         n = host.numel()
         cap = 1 << max(6, (n - 1).bit_length())
-        pin = self._pinned.get(cap)
-        if pin is None:
-            pin = self._pinned[cap] = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+        ring = self._pinned.get(cap)
+        if ring is None:
+            ring = self._pinned[cap] = [0, [], []]               # whose turn, buffers, the events behind their last copies
+        turn, bufs, events = ring
+        if len(bufs) < 2:
+            bufs.append(torch.empty(cap, dtype=torch.int32, pin_memory=True))
+            events.append(torch.cuda.Event())
+            turn = len(bufs) - 1
         else:
-            torch.cuda.current_stream().synchronize()   # the previous upload from this buffer is done
+            events[turn].synchronize()                           # the last upload from this buffer is done
+        pin = bufs[turn]
         pin[:n].copy_(host)
-        return pin[:n].to(self.device, non_blocking=True)
+        dev = pin[:n].to(self.device, non_blocking=True)
+        events[turn].record()
+        ring[0] = (turn + 1) % 2
+        return dev
 
     def decode_session(self, slots: Sequence[int], first_tokens: Sequence[int], max_steps: int) -> DecodeSession:
         """A device-side greedy decode loop over ``slots`` (see ``DecodeSession``)."""
