@@ -235,8 +235,8 @@ def test_a_step_by_one_call_has_the_bits_of_its_calls_one_by_one(loaded, tmp_pat
         lm = idm.load(d, dtype="bfloat16", max_tokens=64 * 40, max_seqs=8)
         cfg, w = plain.read_model(d)
     eng, K = lm.engine, lm.model.rt.kernels
-    if not K.use_programs:
-        pytest.skip("step programs are switched off (IDM_PROGRAM=0)")
+    if not K.use_programs or K.attention_impl != "tcgen05":
+        pytest.skip("step programs are switched off by the environment (IDM_PROGRAM=0, IDM_FUSED=0 or IDM_ATTENTION=generic)")
     prog = lm.model.program(eng.cache)
     assert prog is not None and prog.n_calls == 2 + 7 * cfg["num_hidden_layers"] + 2
     V = cfg["vocab_size"]
